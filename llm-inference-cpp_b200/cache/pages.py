@@ -1,0 +1,140 @@
+"""Host-side bookkeeping of the cache: slots, pages, lengths.
+
+The reference keeps one ``KVCache`` object per sequence with a fixed capacity
+(include/llmi/model/transformer.hpp:29-45; src/model/transformer.cpp:182-190).
+Here many sequences share one pool: a *slot* stands for one live sequence, and
+its keys and values lie in *pages* of ``page_size`` positions taken from the pool
+as the sequence grows and given back when its slot is freed.  The errors keep the
+reference's meaning ("cache is full", src/model/transformer.cpp:208).
+
+This file is pure bookkeeping (no tensors): it can be tested without a GPU.
+"""
+from __future__ import annotations
+
+PAGE_SIZE = 64
+
+
+class CacheError(RuntimeError):
+    pass
+
+
+def pages_for(tokens: int, page_size: int = PAGE_SIZE) -> int:
+    return (tokens + page_size - 1) // page_size
+
+
+class SlotTable:
+    """Which slots are live.  A slot is handed out once until it is freed."""
+
+    def __init__(self, n_slots: int):
+        if n_slots <= 0:
+            raise CacheError("cache: needs at least one slot")
+        self.n_slots = n_slots
+        self._free = list(range(n_slots - 1, -1, -1))   # pop() hands out the lowest free slot
+        self._live = set()
+
+    def alloc(self) -> int:
+        if not self._free:
+            raise CacheError("cache is full: no free slot")
+        s = self._free.pop()
+        self._live.add(s)
+        return s
+
+    def free(self, slot: int) -> None:
+        if slot not in self._live:
+            raise CacheError(f"cache: slot {slot} is not live (freed twice or never allocated)")
+        self._live.remove(slot)
+        self._free.append(slot)
+        self._free.sort(reverse=True)
+
+    def is_live(self, slot: int) -> bool:
+        return slot in self._live
+
+    @property
+    def live(self) -> set:
+        return set(self._live)
+
+    @property
+    def n_free(self) -> int:
+        return len(self._free)
+
+
+class PagePool:
+    """Pages of one cache group: a free list and, per slot, the pages it holds in position order.
+
+    ``window`` > 0 means a query only needs the last ``window`` positions: pages that lie
+    wholly before the window of the next token are given back early and their table entries
+    become -1.
+    """
+
+    def __init__(self, n_pages: int, page_size: int = PAGE_SIZE, window: int = 0):
+        if n_pages <= 0:
+            raise CacheError("cache: needs at least one page")
+        self.n_pages = n_pages
+        self.page_size = page_size
+        self.window = window
+        self._free = list(range(n_pages - 1, -1, -1))
+        self._pages: dict[int, list[int]] = {}     # slot -> page ids by position (-1: released)
+        self._length: dict[int, int] = {}
+
+    # -- slots -----------------------------------------------------------------------------
+    def open(self, slot: int) -> None:
+        if slot in self._pages:
+            raise CacheError(f"cache: slot {slot} is already open in this group")
+        self._pages[slot] = []
+        self._length[slot] = 0
+
+    def close(self, slot: int) -> None:
+        if slot not in self._pages:
+            raise CacheError(f"cache: slot {slot} is not open in this group")
+        for p in self._pages.pop(slot):
+            if p >= 0:
+                self._free.append(p)
+        del self._length[slot]
+
+    # -- growth ----------------------------------------------------------------------------
+    def pages_needed(self, slot: int, n_new: int) -> int:
+        have = len(self._pages[slot])
+        return max(0, pages_for(self._length[slot] + n_new, self.page_size) - have)
+
+    def extend(self, slot: int, n_new: int) -> int:
+        """Make room for ``n_new`` more positions; returns the position of the first of them."""
+        if slot not in self._pages:
+            raise CacheError(f"cache: slot {slot} is not open in this group")
+        base = self._length[slot]
+        if self.window > 0:
+            self._release_before(slot, base - self.window + 1)
+        need = self.pages_needed(slot, n_new)
+        if need > len(self._free):
+            raise CacheError("cache is full")
+        for _ in range(need):
+            self._pages[slot].append(self._free.pop())
+        self._length[slot] = base + n_new
+        return base
+
+    def _release_before(self, slot: int, first_needed: int) -> None:
+        table = self._pages[slot]
+        for i in range(min(len(table), max(0, first_needed) // self.page_size)):
+            if table[i] >= 0:
+                self._free.append(table[i])
+                table[i] = -1
+
+    # -- views -----------------------------------------------------------------------------
+    def length(self, slot: int) -> int:
+        return self._length[slot]
+
+    def table(self, slot: int) -> list[int]:
+        return self._pages[slot]
+
+    @property
+    def n_free(self) -> int:
+        return len(self._free)
+
+    def check(self) -> None:
+        """Every page is free or held by exactly one slot; none is lost."""
+        seen = list(self._free)
+        for table in self._pages.values():
+            seen.extend(p for p in table if p >= 0)
+        if sorted(seen) != list(range(self.n_pages)):
+            lost = set(range(self.n_pages)) - set(seen)
+            dup = {p for p in seen if seen.count(p) > 1}
+            raise CacheError(f"cache: page accounting broken (lost {sorted(lost)}, held twice {sorted(dup)})")

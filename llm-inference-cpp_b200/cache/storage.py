@@ -1,0 +1,139 @@
+"""Device storage of the cache and the object a step function works with.
+
+A mixer says what it needs per sequence with a *request*:
+
+* :class:`KVRequest` — keys and values of every position (or of a window of them),
+  ``n_kv_heads × head_dim`` each.  Calls with equal requests share a *group*: one
+  page pool and one pair of tensors ``[calls, pages, kv_heads, page_size, head_dim]``
+  (one (page, kv head) tile is contiguous — head-major within the page, after the
+  reference's layout, include/llmi/model/transformer.hpp:39-44).
+* :class:`StateRequest` — a fixed-size state per sequence, ``[calls, slots, *shape]``,
+  zeroed when a slot is handed out.  The Llama architecture asks for none; the slab is
+  here so that a mixer with a recurrent state needs no change of the cache.
+
+Groups with different requests have storage and page pools of their own.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from .pages import PAGE_SIZE, CacheError, PagePool, SlotTable, pages_for
+
+
+@dataclass(frozen=True)
+class KVRequest:
+    n_kv_heads: int
+    head_dim: int
+    window: int = 0          # 0: all positions
+
+
+@dataclass(frozen=True)
+class StateRequest:
+    shape: tuple
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class CacheBinding:
+    """What one scheduled call holds of the cache: its group and its index inside the group."""
+    group: object
+    index: int
+    writes: bool = True      # False: the call reads another call's entries
+
+
+class KVGroup:
+    def __init__(self, request: KVRequest, n_calls: int, n_pages: int, page_size: int, dtype, device):
+        self.request = request
+        self.n_calls = n_calls
+        self.page_size = page_size
+        self.pool = PagePool(n_pages, page_size, request.window)
+        shape = (n_calls, n_pages, request.n_kv_heads, page_size, request.head_dim)
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
+
+    def bytes_per_token(self) -> int:
+        r = self.request
+        return 2 * self.n_calls * r.n_kv_heads * r.head_dim * self.k.element_size()
+
+
+class StateGroup:
+    def __init__(self, request: StateRequest, n_calls: int, n_slots: int, device):
+        self.request = request
+        self.n_calls = n_calls
+        self.data = torch.zeros((n_calls, n_slots, *request.shape), dtype=request.dtype, device=device)
+
+    def reset(self, slot: int) -> None:
+        self.data[:, slot].zero_()
+
+
+class SequenceCache:
+    """Slots, their lengths, and the groups' storage.  Sized by the most tokens held at once."""
+
+    def __init__(self, kv_requests, state_requests, max_tokens: int, max_positions: int, dtype, device,
+                 page_size: int = PAGE_SIZE, n_slots: int | None = None):
+        """``kv_requests`` / ``state_requests``: lists of (request, number of calls)."""
+        if max_tokens < page_size:
+            raise CacheError(f"cache: max_tokens must be at least one page ({page_size} tokens)")
+        self.page_size = page_size
+        self.max_positions = max_positions
+        n_pages = max_tokens // page_size
+        self.n_slots = n_slots if n_slots is not None else n_pages
+        self.slots = SlotTable(self.n_slots)
+        self.kv_groups = [KVGroup(r, n, n_pages, page_size, dtype, device) for r, n in kv_requests]
+        self.state_groups = [StateGroup(r, n, self.n_slots, device) for r, n in state_requests]
+        self.max_pages_per_seq = min(pages_for(max_positions, page_size), n_pages)
+        self._length: dict[int, int] = {}
+        self.device = device
+        self.dtype = dtype
+
+    # -- slots -----------------------------------------------------------------------------
+    def alloc_slot(self) -> int:
+        slot = self.slots.alloc()
+        for g in self.kv_groups:
+            g.pool.open(slot)
+        for g in self.state_groups:
+            g.reset(slot)
+        self._length[slot] = 0
+        return slot
+
+    def free_slot(self, slot: int) -> None:
+        self.slots.free(slot)          # raises on a slot that is not live
+        for g in self.kv_groups:
+            g.pool.close(slot)
+        del self._length[slot]
+
+    def length(self, slot: int) -> int:
+        if slot not in self._length:
+            raise CacheError(f"cache: slot {slot} is not live")
+        return self._length[slot]
+
+    # -- growth ----------------------------------------------------------------------------
+    def can_extend(self, wanted: dict) -> None:
+        """Raise unless every slot of ``wanted`` (slot → new tokens) fits, in every group."""
+        for slot, n_new in wanted.items():
+            if slot not in self._length:
+                raise CacheError(f"cache: slot {slot} is not live")
+            if self._length[slot] + n_new > self.max_positions:
+                raise CacheError("sequence longer than the model's context")
+        for g in self.kv_groups:
+            need = sum(g.pool.pages_needed(s, n) for s, n in wanted.items())
+            if need > g.pool.n_free and g.pool.window == 0:
+                raise CacheError("cache is full")
+
+    def extend(self, slot: int, n_new: int) -> int:
+        """Reserve room for ``n_new`` positions of a slot; returns its first new position."""
+        base = self._length[slot]
+        for g in self.kv_groups:
+            g.pool.extend(slot, n_new)
+        self._length[slot] = base + n_new
+        return base
+
+    # -- accounting ------------------------------------------------------------------------
+    def check(self) -> None:
+        for g in self.kv_groups:
+            g.pool.check()
+
+    def bytes_per_token(self) -> int:
+        return sum(g.bytes_per_token() for g in self.kv_groups)

@@ -1,0 +1,105 @@
+// Row-wise kernels: embedding gather, RMSNorm, SwiGLU gating.
+//
+// Formulas (reference, CPU): embedding row copy src/model/weight.cpp:39-45 and
+// src/model/transformer.cpp:214-217; RMSNorm src/model/kernels.cpp:115-120
+// (y = w * (x * scale), scale = 1/sqrt(mean(x^2) + eps)); SiLU gate
+// src/model/kernels.cpp:148 with src/model/transformer.cpp:290.
+#include "common.cuh"
+
+namespace llmi {
+
+// out[t, :] = float(table[ids[t], :]); a negative id (padding) gives a zero row.
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids, float* __restrict__ out,
+                             int width) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* o = out + (size_t)t * width;
+  if (id < 0) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = 0.f;
+    return;
+  }
+  const T* row = table + (size_t)id * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+// One block per output row.  x is the fp32 residual stream; `rows` (optional) picks the
+// input row of each output row, so the last norm runs only where logits are wanted.
+template <typename T>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ weight, T* __restrict__ out,
+                               const int32_t* __restrict__ rows, int width, float eps) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  T* o = out + (size_t)r * width;
+  if (src < 0) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<T>(0.f);
+    return;
+  }
+  const float* xr = x + (size_t)src * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = xr[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<T>(weight[i] * (xr[i] * scale));
+}
+
+// gate_up is [rows, 2*inner]: gate in the first half of a row, up in the second.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inner, size_t total) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / inner, c = i - r * inner;
+    const float g = to_f32(gate_up[r * 2 * inner + c]);
+    const float u = to_f32(gate_up[r * 2 * inner + inner + c]);
+    const float s = g / (1.0f + expf(-g));
+    out[i] = from_f32<T>(s * u);
+  }
+}
+
+}  // namespace llmi
+
+using namespace llmi;
+
+LLMI_EXPORT int llmi_embed(int dtype, const void* table, const int32_t* ids, float* out, int n_tokens, int width,
+                           cudaStream_t stream) {
+  if (n_tokens <= 0 || width <= 0) return LLMI_ERR_BAD_SIZE;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (dtype == LLMI_DTYPE_F32)
+    embed_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, width);
+  else if (dtype == LLMI_DTYPE_BF16)
+    embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, width);
+  else
+    return LLMI_ERR_BAD_DTYPE;
+  return launch_status();
+}
+
+LLMI_EXPORT int llmi_rmsnorm(int out_dtype, const float* x, const float* weight, void* out, const int32_t* rows,
+                             int n_rows, int width, float eps, cudaStream_t stream) {
+  if (n_rows <= 0 || width <= 0) return LLMI_ERR_BAD_SIZE;
+  const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  if (out_dtype == LLMI_DTYPE_F32)
+    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, weight, (float*)out, rows, width, eps);
+  else if (out_dtype == LLMI_DTYPE_BF16)
+    rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, weight, (__nv_bfloat16*)out, rows, width, eps);
+  else
+    return LLMI_ERR_BAD_DTYPE;
+  return launch_status();
+}
+
+LLMI_EXPORT int llmi_swiglu(int dtype, const void* gate_up, void* out, int n_rows, int inner, cudaStream_t stream) {
+  if (n_rows <= 0 || inner <= 0) return LLMI_ERR_BAD_SIZE;
+  const size_t total = (size_t)n_rows * inner;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == LLMI_DTYPE_F32)
+    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inner, total);
+  else if (dtype == LLMI_DTYPE_BF16)
+    swiglu_kernel<__nv_bfloat16>
+        <<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inner, total);
+  else
+    return LLMI_ERR_BAD_DTYPE;
+  return launch_status();
+}

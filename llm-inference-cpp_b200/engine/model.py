@@ -1,0 +1,131 @@
+"""The model as the engine sees it: parts in their run order, and one step function.
+
+``step`` is the successor of the reference's ``forward_cached``
+(src/model/transformer.cpp:192-306): it runs only the tokens it is given, from the
+cache that earlier steps left, and returns logits at the wanted places only — the
+final norm and the head run on those rows alone (the reference normalises all rows
+and multiplies the last, :298-305).  Unlike the reference it takes a batch of
+sequences with unequal lengths in one call.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.storage import CacheBinding, KVRequest, SequenceCache, StateRequest
+from ..parts.build import build_parts, expected_tensors
+from ..parts.spec import ModelSpec
+from .batch import SequenceStep, StepBuffers, plan_step
+from .runtime import Runtime
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, tensors: dict, dtype: torch.dtype, device="cuda:0", config=None):
+        self.spec = spec
+        self.config = config
+        self.rt = Runtime(dtype, device)
+        self.embedding, self.layers, self.final_norm, self.head = build_parts(spec, tensors, self.rt)
+        for call in spec.schedule:
+            if not (0 <= call.layer < len(self.layers)):
+                raise ValueError(f"schedule names layer {call.layer}, but the model has {len(self.layers)}")
+        for i, call in enumerate(spec.schedule):
+            if call.cache_of is not None and not (0 <= call.cache_of < len(spec.schedule)):
+                raise ValueError(f"schedule call {i} reads the cache of call {call.cache_of}, which does not exist")
+        self.buffers = StepBuffers(self.rt.device, self.rt)
+        self.parameter_count = sum(int(torch.tensor(d.shape).prod()) for d in expected_tensors(spec).values())
+
+    # -- sizes -----------------------------------------------------------------------------
+    @property
+    def dtype(self):
+        return self.rt.dtype
+
+    @property
+    def device(self):
+        return self.rt.device
+
+    @property
+    def vocab_size(self) -> int:
+        return self.spec.vocab_size
+
+    def weight_bytes(self) -> int:
+        """Bytes of every weight a step reads once (a tied table counts once)."""
+        total = self.embedding.weight_bytes() + self.head.weight_bytes()
+        used = {call.layer for call in self.spec.schedule}
+        for i in used:
+            blk = self.layers[i].block
+            for p in (blk.mixer, blk.ffn):
+                total += p.weight_bytes() if hasattr(p, "weight_bytes") else 0
+        return total
+
+    # -- cache -----------------------------------------------------------------------------
+    def new_cache(self, max_tokens: int, n_slots: int | None = None) -> SequenceCache:
+        """A cache for at most ``max_tokens`` live tokens (each sequence rounded up to whole pages).
+
+        Scheduled calls with equal cache requests share a group; a call that reads another
+        call's cache gets that call's place in the group and writes nothing.
+        """
+        requests = [self.layers[c.layer].mixer.cache_request() for c in self.spec.schedule]
+        kv_groups: dict = {}
+        state_groups: dict = {}
+        place = []
+        for i, (call, req) in enumerate(zip(self.spec.schedule, requests)):
+            if call.cache_of is not None:
+                place.append(None)
+                continue
+            table = kv_groups if isinstance(req, KVRequest) else state_groups if isinstance(req, StateRequest) else None
+            if table is None:
+                place.append(("none", None, 0))
+                continue
+            table.setdefault(req, [])
+            place.append(("kv" if table is kv_groups else "state", req, len(table[req])))
+            table[req].append(i)
+        cache = SequenceCache([(r, len(c)) for r, c in kv_groups.items()],
+                              [(r, len(c)) for r, c in state_groups.items()],
+                              max_tokens, self.spec.max_positions, self.rt.dtype, self.rt.device, n_slots=n_slots)
+        kv_index = {r: g for r, g in zip(kv_groups, cache.kv_groups)}
+        st_index = {r: g for r, g in zip(state_groups, cache.state_groups)}
+        bindings = []
+        for i, call in enumerate(self.spec.schedule):
+            src = place[i] if call.cache_of is None else place[call.cache_of]
+            if src is None:
+                raise ValueError(f"schedule call {i} reads the cache of call {call.cache_of}, which has none of its own")
+            kind, req, idx = src
+            if call.cache_of is not None and requests[i] != req:
+                raise ValueError(f"schedule call {i} cannot read the cache of call {call.cache_of}: their needs differ")
+            group = kv_index[req] if kind == "kv" else st_index[req] if kind == "state" else None
+            bindings.append(CacheBinding(group, idx, writes=call.cache_of is None))
+        cache.bindings = bindings
+        cache.owner = self
+        return cache
+
+    # -- the step --------------------------------------------------------------------------
+    def step(self, cache: SequenceCache, seqs, pad_seqs_to: int = 0, pad_pages_to: int = 0) -> torch.Tensor:
+        """Run the given tokens of the given sequences; fp32 logits ``[wanted, vocab]`` in entry order.
+
+        ``seqs``: :class:`SequenceStep` items (slot, next tokens, wanted places).  The returned
+        tensor is scratch: it is valid until the next step.
+        """
+        if getattr(cache, "owner", None) is not self:
+            raise ValueError("step: cache was not created by this model")
+        ctx = plan_step(cache, seqs, self.spec.vocab_size, self.buffers, pad_seqs_to, pad_pages_to)
+        self._last_h2d = ctx.h2d_bytes
+        return self.run(ctx, cache)
+
+    def run(self, ctx, cache) -> torch.Tensor:
+        """The device work of a step for an uploaded context (what a recorded graph replays)."""
+        x = self.embedding.forward(ctx.token_ids, ctx)
+        for call, binding in zip(self.spec.schedule, cache.bindings):
+            self.layers[call.layer].block.forward(x, ctx, binding)
+        if ctx.n_want == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
+        h = self.final_norm.forward(x, rows=ctx.want_rows, scratch_name="final_norm_out")
+        return self.head.forward(h)
+
+    def step_and_choose(self, cache, seqs, sampler, streams=None, use_graphs: bool = True):
+        """One step followed by the choice of one token per wanted row; returns the ids on the host."""
+        logits = self.step(cache, seqs)
+        ids = sampler.choose(logits, streams)
+        return ids.cpu()
+
+    @property
+    def last_h2d_bytes(self) -> int:
+        return getattr(self, "_last_h2d", 0)

@@ -1,0 +1,2 @@
+"""Architectures this library knows; importing the package registers them."""
+from . import llama  # noqa: F401

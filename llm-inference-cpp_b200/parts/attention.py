@@ -1,0 +1,71 @@
+"""Mixer parts.  ``gqa``: causal grouped-query attention over the cache.
+
+Formulas: q, k, v projections with optional biases (src/model/transformer.cpp:245-250;
+src/model/model.cpp:145-152); query head hh reads kv head hh / (heads / kv_heads)
+(src/model/transformer.cpp:264); scores scaled by 1/sqrt(head_dim) after the dot (:235, :271);
+causal by position (:270); softmax and weighted sum (:273-280); output projection without
+bias added to the residual stream (:283-284).  The three projections are stored as one
+matrix [q; k; v] so that one product serves them.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..cache.storage import KVRequest
+from ..ops import kernels
+from .registry import TensorDecl, get_part, part
+
+
+@part("mixer", "gqa")
+class GQAttention:
+    """params: ``width``, ``n_heads``, ``n_kv_heads``, ``head_dim``, ``bias`` (q/k/v), ``window`` (0: all),
+    ``scale`` (default 1/sqrt(head_dim)), ``position`` (a PartSpec of the position family)."""
+
+    @classmethod
+    def declare(cls, spec):
+        p = spec.params
+        q, kv, w = p["n_heads"] * p["head_dim"], p["n_kv_heads"] * p["head_dim"], p["width"]
+        d = {"q_proj.weight": TensorDecl((q, w)), "k_proj.weight": TensorDecl((kv, w)),
+             "v_proj.weight": TensorDecl((kv, w)), "o_proj.weight": TensorDecl((w, q))}
+        if p.get("bias", False):
+            d.update({"q_proj.bias": TensorDecl((q,), "bias"), "k_proj.bias": TensorDecl((kv,), "bias"),
+                      "v_proj.bias": TensorDecl((kv,), "bias")})
+        return d
+
+    def __init__(self, spec, tensors, rt, **_):
+        p = spec.params
+        self.rt = rt
+        self.width = int(p["width"])
+        self.n_heads, self.n_kv_heads, self.head_dim = int(p["n_heads"]), int(p["n_kv_heads"]), int(p["head_dim"])
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError("gqa: n_heads must be a multiple of n_kv_heads")
+        self.window = int(p.get("window", 0))
+        self.scale = float(p.get("scale", 1.0 / math.sqrt(self.head_dim)))
+        self.w_qkv = rt.to_compute(torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
+                                              tensors["v_proj.weight"]], dim=0))
+        self.b_qkv = None
+        if p.get("bias", False):
+            self.b_qkv = rt.to_f32(torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]]))
+        self.w_o = rt.to_compute(tensors["o_proj.weight"])
+        pos_spec = p["position"]
+        self.position = get_part("position", pos_spec.kind)(pos_spec, {}, rt)
+
+    def cache_request(self):
+        return KVRequest(self.n_kv_heads, self.head_dim, self.window)
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o))
+
+    def forward(self, h, x, ctx, binding) -> None:
+        T = h.shape[0]
+        nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        qkv = self.rt.scratch("qkv", (T, (nh + 2 * nkv) * hd))
+        kernels.linear(h, self.w_qkv, qkv, self.b_qkv)
+        self.position.rotate_and_store(qkv, ctx, binding, nh, nkv, hd)
+        attn = self.rt.scratch("attn_out", (T, nh * hd))
+        g = binding.group
+        kernels.attention(qkv, attn, g.k[binding.index], g.v[binding.index], ctx, ctx.pages_of(g), g.page_size,
+                          nh, nkv, hd, self.scale, self.window)
+        kernels.linear(attn, self.w_o, x, None, kernels.OUT_ADD_F32)

@@ -1,0 +1,62 @@
+"""From a ModelSpec and named tensors to live parts, and the table of tensors a spec expects.
+
+The reference lists its expected tensors in one function for its one model
+(src/model/model.cpp:135-162).  Here every part declares its own tensors under
+its prefix, and the table of a model is the union over its parts, in the order
+the parts appear.
+"""
+from __future__ import annotations
+
+from . import attention, block, embedding, feedforward, norm, position  # noqa: F401  (register the built-in parts)
+from .registry import TensorDecl, get_part
+from .spec import ModelSpec, PartSpec
+
+
+def _part_specs(spec: ModelSpec):
+    yield "embedding", spec.embedding
+    for layer in spec.layers:
+        yield "norm", layer.mixer_norm
+        yield "mixer", layer.mixer
+        yield "norm", layer.ffn_norm
+        yield "ffn", layer.ffn
+    yield "norm", spec.final_norm
+    yield "head", spec.head
+
+
+def expected_tensors(spec: ModelSpec) -> dict:
+    """Full tensor name -> TensorDecl for everything the model reads from its weight file."""
+    out: dict[str, TensorDecl] = {}
+    for family, ps in _part_specs(spec):
+        for local, decl in get_part(family, ps.kind).declare(ps).items():
+            name = ps.prefix + local
+            if name in out and out[name].shape != decl.shape:
+                raise ValueError(f"tensor {name} is declared twice with different shapes")
+            out[name] = decl
+    return out
+
+
+def _make(family: str, ps: PartSpec, tensors: dict, rt, **context):
+    cls = get_part(family, ps.kind)
+    local = {name: tensors[ps.prefix + name] for name in cls.declare(ps)}
+    return cls(ps, local, rt, **context)
+
+
+class BuiltLayer:
+    def __init__(self, block_part, mixer):
+        self.block = block_part
+        self.mixer = mixer
+
+
+def build_parts(spec: ModelSpec, tensors: dict, rt):
+    """-> (embedding, [BuiltLayer], final_norm, head)."""
+    emb = _make("embedding", spec.embedding, tensors, rt)
+    layers = []
+    for ls in spec.layers:
+        mixer_norm = _make("norm", ls.mixer_norm, tensors, rt)
+        mixer = _make("mixer", ls.mixer, tensors, rt)
+        ffn_norm = _make("norm", ls.ffn_norm, tensors, rt)
+        ffn = _make("ffn", ls.ffn, tensors, rt)
+        layers.append(BuiltLayer(get_part("block", ls.block)(mixer_norm, mixer, ffn_norm, ffn), mixer))
+    final_norm = _make("norm", spec.final_norm, tensors, rt)
+    head = _make("head", spec.head, tensors, rt, embedding=emb)
+    return emb, layers, final_norm, head

@@ -1,0 +1,67 @@
+"""Embedding and output-head parts.
+
+``token_table``: x[t] = E[token[t]], no scaling (src/model/transformer.cpp:214-217).
+``linear_head``: logits = h · Wᵀ with W the head matrix, or the embedding table when tied
+(src/model/transformer.cpp:301-305); logits are fp32.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels
+from .registry import TensorDecl, part
+
+
+@part("embedding", "token_table")
+class TokenTable:
+    """params: ``vocab``, ``width``.  tensors: ``weight [vocab, width]``."""
+
+    @classmethod
+    def declare(cls, spec):
+        return {"weight": TensorDecl((spec.params["vocab"], spec.params["width"]), "table")}
+
+    def __init__(self, spec, tensors, rt, **_):
+        self.rt = rt
+        self.vocab, self.width = int(spec.params["vocab"]), int(spec.params["width"])
+        self.weight = rt.to_compute(tensors["weight"])
+
+    def table(self):
+        return self.weight
+
+    def weight_bytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
+
+    def forward(self, token_ids, ctx):
+        x = self.rt.scratch("residual", (token_ids.shape[0], self.width), torch.float32)
+        kernels.embed(self.weight, token_ids, x)
+        return x
+
+
+@part("head", "linear_head")
+class LinearHead:
+    """params: ``vocab``, ``width``, ``tied``.  tensors: ``weight [vocab, width]`` unless tied."""
+
+    @classmethod
+    def declare(cls, spec):
+        if spec.params.get("tied", False):
+            return {}
+        return {"weight": TensorDecl((spec.params["vocab"], spec.params["width"]))}
+
+    def __init__(self, spec, tensors, rt, embedding=None, **_):
+        self.rt = rt
+        self.vocab, self.width = int(spec.params["vocab"]), int(spec.params["width"])
+        self.tied = bool(spec.params.get("tied", False))
+        if self.tied:
+            if embedding is None:
+                raise ValueError("linear_head: a tied head needs the embedding part")
+            self.weight = embedding.table()
+        else:
+            self.weight = rt.to_compute(tensors["weight"])
+
+    def weight_bytes(self) -> int:
+        return 0 if self.tied else self.weight.numel() * self.weight.element_size()
+
+    def forward(self, h_rows):
+        logits = self.rt.scratch("logits", (h_rows.shape[0], self.vocab), torch.float32)
+        kernels.linear(h_rows, self.weight, logits, None, kernels.OUT_STORE_F32)
+        return logits

@@ -1,0 +1,37 @@
+"""Feed-forward parts.  ``swiglu``: x += (silu(h·Wgᵀ) ⊙ (h·Wuᵀ))·Wdᵀ, no biases
+(src/model/transformer.cpp:288-292; silu(z) = z / (1 + exp(-z)), src/model/kernels.cpp:148).
+Gate and up are stored as one matrix [gate; up] so that one product serves both."""
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels
+from .registry import TensorDecl, part
+
+
+@part("ffn", "swiglu")
+class SwiGLU:
+    """params: ``width``, ``inner``."""
+
+    @classmethod
+    def declare(cls, spec):
+        w, f = spec.params["width"], spec.params["inner"]
+        return {"gate_proj.weight": TensorDecl((f, w)), "up_proj.weight": TensorDecl((f, w)),
+                "down_proj.weight": TensorDecl((w, f))}
+
+    def __init__(self, spec, tensors, rt, **_):
+        self.rt = rt
+        self.width, self.inner = int(spec.params["width"]), int(spec.params["inner"])
+        self.w_gate_up = rt.to_compute(torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0))
+        self.w_down = rt.to_compute(tensors["down_proj.weight"])
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
+
+    def forward(self, h, x, ctx) -> None:
+        T = h.shape[0]
+        gate_up = self.rt.scratch("ffn_gate_up", (T, 2 * self.inner))
+        kernels.linear(h, self.w_gate_up, gate_up)
+        act = self.rt.scratch("ffn_act", (T, self.inner))
+        kernels.swiglu(gate_up, act)
+        kernels.linear(act, self.w_down, x, None, kernels.OUT_ADD_F32)

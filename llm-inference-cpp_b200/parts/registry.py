@@ -1,0 +1,60 @@
+"""Registries of part kinds, one per family, and the interface each family keeps.
+
+Families and what the engine calls on their members (``rt`` is the
+:class:`~..engine.runtime.Runtime`, ``ctx`` the step's
+:class:`~..engine.batch.StepContext`, ``x`` the fp32 residual stream
+``[tokens, width]``, ``h`` a normalised copy of it in the compute type):
+
+``norm``       ``forward(x, rows=None) -> h``
+``position``   ``at_embedding(x, ctx)`` (may add to ``x``; default nothing) and
+               ``rotate_and_store(qkv, ctx, binding, n_heads, n_kv_heads, head_dim)``
+               for mixers that keep keys and values
+``mixer``      ``cache_request() -> KVRequest | StateRequest | None`` and
+               ``forward(h, x, ctx, binding)``: adds its output to ``x``
+``ffn``        ``forward(h, x, ctx)``: adds its output to ``x``
+``block``      ``forward(x, ctx, binding)``: one layer's arrangement of the above
+``embedding``  ``forward(token_ids, ctx) -> x`` and ``table()`` (for a tied head)
+``head``       ``forward(h_rows) -> logits fp32 [rows, vocab]``
+
+Every member also has ``declare(spec) -> {local tensor name: TensorDecl}`` (a
+classmethod: what it reads from the weight file under ``spec.prefix``) and is
+constructed as ``cls(spec, tensors, rt, **context)`` with its declared tensors.
+No part knows which model it is in.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+FAMILIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head")
+_PARTS: dict[str, dict[str, type]] = {f: {} for f in FAMILIES}
+
+
+@dataclass(frozen=True)
+class TensorDecl:
+    shape: tuple
+    role: str = "matrix"     # "matrix" | "norm_scale" | "bias" | "table": how random weights draw it
+
+
+def register_part(family: str, kind: str, cls: type, *, replace: bool = False) -> None:
+    if family not in _PARTS:
+        raise ValueError(f"unknown part family {family!r}; families are {FAMILIES}")
+    if kind in _PARTS[family] and not replace:
+        raise ValueError(f"{family} part {kind!r} is already registered")
+    _PARTS[family][kind] = cls
+
+
+def get_part(family: str, kind: str) -> type:
+    try:
+        return _PARTS[family][kind]
+    except KeyError:
+        known = ", ".join(sorted(_PARTS.get(family, {}))) or "none"
+        raise KeyError(f"no {family} part of kind {kind!r} is registered (known: {known})") from None
+
+
+def part(family: str, kind: str):
+    """Class decorator: ``@part("mixer", "gqa")``."""
+    def deco(cls):
+        register_part(family, kind, cls)
+        cls.family, cls.kind = family, kind
+        return cls
+    return deco

@@ -1,0 +1,56 @@
+"""Descriptions of a model as data: which part runs where, with which sizes.
+
+An architecture turns its typed configuration into a :class:`ModelSpec`.  The
+builder (``parts.build``) turns a ModelSpec plus named tensors into live parts.
+Nothing below names a model: a part is a *kind* (a key of the part registries),
+its *params* (sizes and constants) and the *prefix* of its tensor names.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    kind: str                       # key in the registry of its family
+    params: dict = field(default_factory=dict)
+    prefix: str = ""                # tensor names of the part start with this
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """One layer: an arrangement (``block``) of a mixer and a feed-forward with their norms."""
+    block: str                      # arrangement, e.g. "prenorm"
+    mixer_norm: PartSpec
+    mixer: PartSpec
+    ffn_norm: PartSpec
+    ffn: PartSpec
+
+
+@dataclass(frozen=True)
+class ScheduleEntry:
+    """One call in the order layers run.
+
+    ``layer`` indexes ``ModelSpec.layers``; the same layer may be named twice.
+    ``cache_of`` names the schedule position whose cache this call reads instead
+    of keeping one of its own (None: its own).  A call that reads another call's
+    cache writes nothing into it.
+    """
+    layer: int
+    cache_of: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    architecture: str
+    vocab_size: int
+    width: int
+    max_positions: int
+    embedding: PartSpec
+    layers: tuple
+    schedule: tuple
+    final_norm: PartSpec
+    head: PartSpec
+    stop_ids: tuple = ()
+    extra: Any = None
