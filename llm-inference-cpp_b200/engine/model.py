@@ -98,7 +98,8 @@ class Model:
         return cache
 
     # -- the step --------------------------------------------------------------------------
-    def step(self, cache: SequenceCache, seqs, pad_seqs_to: int = 0, pad_pages_to: int = 0) -> torch.Tensor:
+    def step(self, cache: SequenceCache, seqs, pad_seqs_to: int = 0, pad_pages_to: int = 0,
+             trace: list | None = None) -> torch.Tensor:
         """Run the given tokens of the given sequences; fp32 logits ``[wanted, vocab]`` in entry order.
 
         ``seqs``: :class:`SequenceStep` items (slot, next tokens, wanted places).  The returned
@@ -108,13 +109,24 @@ class Model:
             raise ValueError("step: cache was not created by this model")
         ctx = plan_step(cache, seqs, self.spec.vocab_size, self.buffers, pad_seqs_to, pad_pages_to)
         self._last_h2d = ctx.h2d_bytes
-        return self.run(ctx, cache)
+        return self.run(ctx, cache, trace)
 
-    def run(self, ctx, cache) -> torch.Tensor:
-        """The device work of a step for an uploaded context (what a recorded graph replays)."""
+    def run(self, ctx, cache, trace: list | None = None) -> torch.Tensor:
+        """The device work of a step for an uploaded context (what a recorded graph replays).
+
+        ``trace``, when given, receives copies of the residual stream after the embedding and
+        after every scheduled call, and the final norm of all rows — the states of the
+        reference's ForwardTrace (include/llmi/model/transformer.hpp:14-19).
+        """
         x = self.embedding.forward(ctx.token_ids, ctx)
+        if trace is not None:
+            trace.append(x.clone())
         for call, binding in zip(self.spec.schedule, cache.bindings):
             self.layers[call.layer].block.forward(x, ctx, binding)
+            if trace is not None:
+                trace.append(x.clone())
+        if trace is not None:
+            trace.append(self.final_norm.forward(x, scratch_name="trace_norm_out").float().clone())
         if ctx.n_want == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
         h = self.final_norm.forward(x, rows=ctx.want_rows, scratch_name="final_norm_out")

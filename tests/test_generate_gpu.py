@@ -1,0 +1,133 @@
+"""Generation through the Python entry point and the command line (GPU)."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import plain_llama as P
+from conftest import ROOT, TINY_CONFIGS
+
+pytestmark = pytest.mark.gpu
+STORAGE = {"float32": "F32", "bfloat16": "BF16"}
+
+
+def prompts_for(name, lens, seed=21):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, TINY_CONFIGS[name]["vocab_size"], n).tolist() for n in lens]
+
+
+def plain_greedy_with_margin(cfg, w, prompt, n):
+    """Greedy ids from the plain implementation and the smallest top-2 logit margin on the way."""
+    toks, out, margin = list(prompt), [], np.inf
+    for _ in range(n):
+        logits = P.forward(cfg, w, toks)[-1]
+        top = np.sort(logits)[-2:]
+        margin = min(margin, float(top[1] - top[0]))
+        out.append(int(np.argmax(logits)))
+        toks.append(out[-1])
+    return out, margin
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,lens,n_new", [("A", [5, 9, 17], 8), ("B", [1, 12, 30, 64], 16)])
+def test_greedy_generation_matches_plain(model_dirs, name, lens, n_new, dtype):
+    import llmi_b200 as L
+    d = model_dirs(name, STORAGE[dtype])
+    cfg, w = P.read_model(d)
+    model = L.load(d, dtype)
+    prompts = prompts_for(name, lens)
+    got = L.generate(model, prompts, max_new=n_new, ignore_eos=True)
+    for p, g in zip(prompts, got):
+        ref, margin = plain_greedy_with_margin(cfg, w, p, n_new)
+        if dtype == "float32" or margin > 0.05:     # a near-tie may legitimately flip under bf16 rounding
+            assert g == ref
+        assert len(g) == n_new
+
+
+def test_stop_tokens_early_ends_and_batches_in_turn(model_dirs):
+    import llmi_b200 as L
+    d = model_dirs("B", "F32")
+    cfg, w = P.read_model(d)
+    model = L.load(d, "float32")
+    prompts = prompts_for("B", [3, 20, 7, 40, 11, 2, 64])
+    free = L.generate(model, prompts, max_new=12, ignore_eos=True)
+    # stop ids chosen from tokens that really are generated (tests/transformer_test.cpp:393-396)
+    stop = {free[0][2], free[3][5]}
+    per = [12, 12, 5, 12, 1, 12, 0]
+    cache = model.new_cache(64 * 4)                  # room for about three sequences: several batches, slots reused
+    got, info = L.generate(model, prompts, max_new=per, stop_ids=sorted(stop), cache=cache, max_batch=3, return_details=True)
+    assert info["batches"] >= 3
+    for g, f, n, fin in zip(got, free, per, info["finish"]):
+        cut = next((i + 1 for i, t in enumerate(f[:n]) if t in stop), n)
+        assert g == f[:cut]                           # the stop token is kept; nothing after it
+        assert fin == ("stop" if g and g[-1] in stop else "length")
+    cache.check()
+    assert not cache.slots.live
+    # default stop ids come from the configuration's eos_token_id
+    eos = L.generate(model, prompts[:2], max_new=12)
+    for g, f in zip(eos, free[:2]):
+        cut = next((i + 1 for i, t in enumerate(f) if t in cfg["eos_token_id"]), 12)
+        assert g == f[:cut]
+
+
+def test_sampling_is_reproducible_and_independent_of_batch_mates(model_dirs):
+    import llmi_b200 as L
+    d = model_dirs("B", "F32")
+    model = L.load(d, "float32")
+    prompts = prompts_for("B", [1, 12, 30, 64])
+    sp = L.SamplingParams(temperature=0.8, top_k=50, top_p=0.95, seed=5)
+    a = L.generate(model, prompts, max_new=16, ignore_eos=True, sampling=sp)
+    b = L.generate(model, prompts, max_new=16, ignore_eos=True, sampling=sp)
+    assert a == b
+    c = L.generate(model, prompts, max_new=16, ignore_eos=True, sampling=L.SamplingParams(0.8, 50, 0.95, seed=6))
+    assert a != c
+    alone = L.generate(model, prompts[:1], max_new=16, ignore_eos=True, sampling=sp)
+    assert alone[0] == a[0]
+    # temperature 0 is greedy
+    assert L.generate(model, prompts, max_new=4, ignore_eos=True, sampling=L.SamplingParams(0.0, 50, 0.5, seed=9)) == \
+        L.generate(model, prompts, max_new=4, ignore_eos=True)
+
+
+def test_sampled_tokens_follow_the_plain_sampler(model_dirs):
+    """With the same uniform numbers the device sampler picks what the plain sampler picks."""
+    import llmi_b200 as L
+    from llmi_b200.sampling import UniformStream
+    d = model_dirs("B", "F32")
+    cfg, w = P.read_model(d)
+    model = L.load(d, "float32")
+    prompt = prompts_for("B", [12])[0]
+    sp = L.SamplingParams(temperature=0.8, top_k=0, top_p=1.0, seed=3)
+    got = L.generate(model, [prompt], max_new=16, ignore_eos=True, sampling=sp)[0]
+    stream = UniformStream(3, 0)
+    toks = list(prompt)
+    for g in got:
+        logits = P.forward(cfg, w, toks)[-1]
+        u = stream.next()
+        p = P.sampling_probabilities(logits, 0.8)
+        cum = np.cumsum(p)
+        near_edge = np.min(np.abs(cum - u)) < 1e-5
+        assert near_edge or P.sample(logits, 0.8, 0, 1.0, u) == g
+        toks.append(g)
+
+
+def test_command_line(model_dirs):
+    d = model_dirs("A", "F32")
+    cfg, w = P.read_model(d)
+    prompt = prompts_for("A", [9])[0]
+    cli = os.path.join(ROOT, "bin", "llmi-generate")
+    r = subprocess.run([sys.executable, cli, d, "--ids", ",".join(map(str, prompt)), "--max-new", "8", "--ignore-eos",
+                        "--json", "--dtype", "fp32"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["prompt_ids"] == prompt
+    assert out["generated_ids"] == P.generate_greedy(cfg, w, prompt, 8)
+    assert {"load_seconds", "generate_seconds", "weight_bytes"} <= set(out)
+    r = subprocess.run([sys.executable, cli, d, "--max-new", "4"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 2 and "give --prompt or --ids" in r.stderr
+    r = subprocess.run([sys.executable, cli, d, "--ids", "1,x"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 2
+    r = subprocess.run([sys.executable, cli, d, "--ids", "1", "--bogus"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 2

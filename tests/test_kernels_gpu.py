@@ -1,0 +1,252 @@
+"""Each kernel alone against a plain fp32/fp64 PyTorch statement of the same operation, at sizes
+other than the engine's test models (GPU)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 1e-5, "bfloat16": 1e-2}
+
+
+def K():
+    from llmi_b200.ops import kernels
+    return kernels
+
+
+def rel(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(dtype):
+    table = torch.randn(301, 72, device="cuda").to(DT[dtype])
+    ids = torch.tensor([5, 300, 0, -1, 17], dtype=torch.int32, device="cuda")
+    out = torch.full((5, 72), 7.0, device="cuda")
+    K().embed(table, ids, out)
+    ref = table.float()[ids.clamp_min(0).long()]
+    ref[3] = 0
+    assert torch.equal(out, ref)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width,eps", [(72, 1e-5), (2048, 1e-6), (1000, 1e-3), (7, 1e-5)])
+def test_rmsnorm(dtype, width, eps):
+    x = torch.randn(9, width, device="cuda") * 3
+    w = 1 + 0.1 * torch.randn(width, device="cuda")
+    out = torch.empty(9, width, device="cuda", dtype=DT[dtype])
+    K().rmsnorm(x, w, out, eps)
+    xd = x.double()
+    ref = w.double() * (xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + float(np.float32(eps))))
+    assert rel(out, ref) < (1e-6 if dtype == "float32" else 5e-3)
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device="cuda")
+    out2 = torch.empty(3, width, device="cuda", dtype=DT[dtype])
+    K().rmsnorm(x, w, out2, eps, rows)
+    assert torch.equal(out2, out[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K_", [(1, 200, 72), (5, 64, 64), (70, 129, 1000), (130, 40, 17), (64, 384, 120)])
+def test_linear_simt_modes(dtype, M, N, K_):
+    k = K()
+    x = torch.randn(M, K_, device="cuda").to(DT[dtype])
+    w = (torch.randn(N, K_, device="cuda") * 0.1).to(DT[dtype])
+    b = torch.randn(N, device="cuda")
+    ref = x.double() @ w.double().T
+    y = torch.empty(M, N, device="cuda", dtype=DT[dtype])
+    k.linear_simt(x, w, y, None, k.OUT_STORE)
+    assert rel(y, ref) < (1e-5 if dtype == "float32" else 6e-3)
+    y32 = torch.empty(M, N, device="cuda")
+    k.linear_simt(x, w, y32, b, k.OUT_STORE_F32)
+    assert rel(y32, ref + b.double()) < 1e-5
+    acc = torch.randn(M, N, device="cuda")
+    before = acc.clone()
+    k.linear_simt(x, w, acc, None, k.OUT_ADD_F32)
+    assert rel(acc, before.double() + ref) < 1e-5
+    # a strided input (columns of a wider matrix) and a batch that is cut differently give the same rows
+    wide = torch.randn(M, K_ + 24, device="cuda").to(DT[dtype])
+    y1 = torch.empty(M, N, device="cuda")
+    k.linear_simt(wide[:, :K_], w, y1, None, k.OUT_STORE_F32)
+    y2 = torch.empty(1, N, device="cuda")
+    k.linear_simt(wide[M - 1:M, :K_].contiguous(), w, y2, None, k.OUT_STORE_F32)
+    assert torch.equal(y1[M - 1:], y2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu(dtype):
+    gu = (torch.randn(11, 2 * 77, device="cuda") * 4).to(DT[dtype])
+    out = torch.empty(11, 77, device="cuda", dtype=DT[dtype])
+    K().swiglu(gu, out)
+    g, u = gu[:, :77].double(), gu[:, 77:].double()
+    assert rel(out, g / (1 + torch.exp(-g)) * u) < (1e-6 if dtype == "float32" else 5e-3)
+
+
+def paged(n_pages, nkv, hd, dtype, page=64):
+    k = torch.full((n_pages, nkv, page, hd), float("nan"), device="cuda", dtype=DT[dtype])
+    return k, k.clone()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(6, 2, 48, 48), (5, 5, 16, 16), (4, 1, 80, 32), (3, 3, 24, 0)])
+def test_rope_store(dtype, nh, nkv, hd, rot):
+    k = K()
+    T = 7
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device="cuda").to(DT[dtype])
+    orig = qkv.clone()
+    pos = torch.tensor([0, 1, 63, 64, 130, 5, 2], dtype=torch.int32, device="cuda")
+    seq = torch.tensor([0, 0, 0, 0, 0, 1, -1], dtype=torch.int32, device="cuda")
+    pages = torch.tensor([[4, 2, 7], [1, -1, -1]], dtype=torch.int32, device="cuda")
+    kc, vc = paged(8, nkv, hd, dtype)
+    inv = torch.from_numpy(P.rope_inv_freq(rot, 12345.0)).cuda() if rot else None
+    k.rope_store(qkv, inv, rot, seq, pos, pages, 64, kc, vc, nh, nkv, hd, True)
+    o = orig.double().cpu().numpy()
+    for t in range(T):
+        if int(seq[t]) < 0:
+            assert torch.equal(qkv[t], orig[t])
+            continue
+        q = o[t, :nh * hd].reshape(1, nh, hd)
+        kk = o[t, nh * hd:(nh + nkv) * hd].reshape(1, nkv, hd)
+        vv = o[t, (nh + nkv) * hd:].reshape(nkv, hd)
+        if rot:
+            invn = P.rope_inv_freq(rot, 12345.0)
+            q = np.concatenate([P.rope(q[..., :rot], [int(pos[t])], invn), q[..., rot:]], -1)
+            kk = np.concatenate([P.rope(kk[..., :rot], [int(pos[t])], invn), kk[..., rot:]], -1)
+        page = int(pages[int(seq[t]), int(pos[t]) // 64])
+        tol = 2e-6 if dtype == "float32" else 5e-3
+        assert rel(qkv[t, :nh * hd].reshape(nh, hd), torch.from_numpy(q[0])) < tol
+        assert rel(kc[page, :, int(pos[t]) % 64], torch.from_numpy(kk[0])) < tol
+        assert torch.equal(vc[page, :, int(pos[t]) % 64].double().cpu(), torch.from_numpy(vv))
+    assert int(torch.isfinite(kc.float()).sum()) == 6 * nkv * hd        # nothing else was written
+
+
+def plain_attention_rows(q, keys, vals, group, scale, window):
+    """q [nh, hd] at the last position of keys/vals [n, nkv, hd]."""
+    out = np.zeros_like(q)
+    n = keys.shape[0]
+    lo = max(0, n - window) if window > 0 else 0
+    for h in range(q.shape[0]):
+        s = (keys[lo:, h // group] @ q[h]) * scale
+        out[h] = P.softmax(s) @ vals[lo:, h // group]
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(6, 2, 48, 0), (5, 1, 24, 0), (4, 4, 128, 0), (2, 2, 16, 0),
+                                               (6, 3, 32, 100), (3, 1, 256, 0)])
+def test_attention_generic_ragged(dtype, nh, nkv, hd, window):
+    """Tokens of three sequences at scattered positions, pages in scrambled order."""
+    k = K()
+    rng = np.random.default_rng(0)
+    lens = [1, 150, 333]
+    n_pages = 12
+    kc, vc = paged(n_pages, nkv, hd, dtype)
+    perm = rng.permutation(n_pages).tolist()
+    pages = torch.full((3, 6), -1, dtype=torch.int32)
+    store = []
+    for s, n in enumerate(lens):
+        keys = torch.randn(n, nkv, hd).to(DT[dtype])
+        vals = torch.randn(n, nkv, hd).to(DT[dtype])
+        store.append((keys, vals))
+        for p in range((n + 63) // 64):
+            pg = perm.pop()
+            pages[s, p] = pg
+            m = min(64, n - 64 * p)
+            kc[pg, :, :m] = keys[64 * p:64 * p + m].transpose(0, 1).cuda()
+            vc[pg, :, :m] = vals[64 * p:64 * p + m].transpose(0, 1).cuda()
+    toks = [(0, 0), (1, 0), (1, 63), (1, 64), (1, 149), (2, 332), (2, 100), (-1, 0), (2, 31), (2, 32)]
+    T = len(toks)
+    q = torch.randn(T, nh * hd + 8).to(DT[dtype]).cuda()
+    out = torch.empty(T, nh * hd, device="cuda", dtype=DT[dtype])
+    seq = torch.tensor([t[0] for t in toks], dtype=torch.int32, device="cuda")
+    pos = torch.tensor([t[1] for t in toks], dtype=torch.int32, device="cuda")
+    scale = 1 / math.sqrt(hd)
+    k.attention_generic(q[:, :nh * hd], out, kc, vc, seq, pos, pages.cuda(), 64, nh, nkv, hd, scale, window)
+    for t, (s, p) in enumerate(toks):
+        if s < 0:
+            assert (out[t] == 0).all()
+            continue
+        keys, vals = store[s]
+        ref = plain_attention_rows(q[t, :nh * hd].double().cpu().numpy().reshape(nh, hd), keys[:p + 1].double().numpy(),
+                                   vals[:p + 1].double().numpy(), nh // nkv, scale, window)
+        assert rel(out[t].reshape(nh, hd), torch.from_numpy(ref)) < (2e-6 if dtype == "float32" else 1e-2), (t, s, p)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_far_key_and_window_edge(dtype):
+    """One key among hundreds is made to dominate: the output must be its value — unless a window
+    excludes it by exactly one position."""
+    k = K()
+    nh = nkv = 2
+    hd = 32
+    n = 700
+    kc, vc = paged(12, nkv, hd, dtype)
+    keys = torch.randn(n, nkv, hd) * 0.1
+    vals = torch.randn(n, nkv, hd)
+    q = torch.randn(1, nh * hd) * 0.1
+    far = 3
+    keys[far, 0] = 40 * q[0, :hd] / q[0, :hd].norm() ** 2 * math.sqrt(hd)      # score 40 for head 0 at key 3
+    keys, vals, q = keys.to(DT[dtype]), vals.to(DT[dtype]), q.to(DT[dtype]).cuda()
+    pages = torch.arange(11, dtype=torch.int32).flip(0).reshape(1, 11).contiguous()
+    for p in range(11):
+        m = min(64, n - 64 * p)
+        kc[int(pages[0, p]), :, :m] = keys[64 * p:64 * p + m].transpose(0, 1).cuda()
+        vc[int(pages[0, p]), :, :m] = vals[64 * p:64 * p + m].transpose(0, 1).cuda()
+    seq = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pos = torch.tensor([n - 1], dtype=torch.int32, device="cuda")
+    out = torch.empty(1, nh * hd, device="cuda", dtype=DT[dtype])
+    scale = 1 / math.sqrt(hd)
+    k.attention_generic(q, out, kc, vc, seq, pos, pages.cuda(), 64, nh, nkv, hd, scale, 0)
+    assert rel(out[0, :hd], vals[far, 0]) < 2e-2                  # head 0 sees the far key
+    for window, sees in ((n - far, True), (n - far - 1, False)):  # the window's edge, one position either way
+        k.attention_generic(q, out, kc, vc, seq, pos, pages.cuda(), 64, nh, nkv, hd, scale, window)
+        ref = plain_attention_rows(q.double().cpu().numpy().reshape(nh, hd), keys.double().numpy(), vals.double().numpy(),
+                                   1, scale, window)
+        assert rel(out.reshape(nh, hd), torch.from_numpy(ref)) < (2e-6 if dtype == "float32" else 1e-2)
+        assert (rel(out[0, :hd], vals[far, 0]) < 2e-2) == sees
+
+
+def test_argmax_first_maximum():
+    x = torch.randn(5, 1003, device="cuda")
+    x[0, 17] = x[0, 900] = 50.0
+    x[1, 1002] = 60.0
+    x[2] = -3.0
+    out = torch.empty(5, dtype=torch.int32, device="cuda")
+    K().argmax(x, out)
+    assert out.tolist() == [17, 1002, 0, int(x[3].argmax()), int(x[4].argmax())]
+
+
+@pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 1.0), (0.8, 40, 1.0), (0.7, 0, 0.9), (1.5, 10, 0.3),
+                                                     (0.3, 1, 1.0), (1.0, 0, 0.001), (2.0, 5000, 0.95)])
+def test_sample_matches_plain(temperature, top_k, top_p):
+    torch.manual_seed(1)
+    V = 3001
+    logits = torch.randn(8, V, device="cuda") * 2.5
+    logits[3, 100] = logits[3, 2000] = logits[3, 7] = 9.0          # exact ties at the top
+    u = torch.tensor([0.0001, 0.2, 0.5, 0.6, 0.77, 0.9, 0.999, 0.31], dtype=torch.float64, device="cuda")
+    out = torch.empty(8, dtype=torch.int32, device="cuda")
+    K().sample(logits, temperature, top_k, top_p, u, torch.empty(8, V, device="cuda"), out)
+    ref = [P.sample(logits[i].cpu().numpy(), temperature, top_k, top_p, float(u[i])) for i in range(8)]
+    assert out.tolist() == ref
+    for i, tok in enumerate(out.tolist()):                      # draws stay in the filtered set
+        assert P.sampling_probabilities(logits[i].cpu().numpy(), temperature, top_k, top_p)[tok] > 0
+
+
+def test_sample_distribution():
+    """Many draws from one row follow the filtered distribution."""
+    torch.manual_seed(2)
+    V, n = 50, 4000
+    row = torch.randn(V) * 2
+    logits = row.repeat(n, 1).cuda()
+    u = torch.rand(n, dtype=torch.float64, device="cuda")
+    out = torch.empty(n, dtype=torch.int32, device="cuda")
+    K().sample(logits, 0.9, 12, 0.92, u, torch.empty(n, V, device="cuda"), out)
+    p = P.sampling_probabilities(row.numpy(), 0.9, 12, 0.92)
+    freq = np.bincount(out.cpu().numpy(), minlength=V) / n
+    assert set(np.nonzero(freq)[0]) <= set(np.nonzero(p)[0])
+    assert np.abs(freq - p).max() < 0.03

@@ -1,0 +1,166 @@
+"""The engine against the plain implementation, however the work is cut (GPU)."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import helpers as H
+import plain_llama as P
+from conftest import ROOT, TINY_CONFIGS
+
+pytestmark = pytest.mark.gpu
+
+STORAGE = {"float32": "F32", "bfloat16": "BF16"}
+LENGTHS = {"A": [5, 9, 17, 40, 100, 128], "B": [1, 12, 30, 64, 65, 200], "C": [3, 33, 64, 129, 300, 700]}
+
+
+def make_requests(name, seed=11):
+    rng = np.random.default_rng(seed)
+    v = TINY_CONFIGS[name]["vocab_size"]
+    return {f"r{i}": rng.integers(0, v, n).tolist() for i, n in enumerate(LENGTHS[name])}
+
+
+@pytest.fixture(scope="module")
+def loaded(model_dirs):
+    import llmi_b200 as L
+    cache = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in cache:
+            d = model_dirs(name, STORAGE[dtype])
+            cfg, w = P.read_model(d)
+            reqs = make_requests(name)
+            refs = {r: P.forward(cfg, w, t) for r, t in reqs.items()}
+            cache[(name, dtype)] = (L.load(d, dtype), reqs, refs, d)
+        return cache[(name, dtype)]
+    return get
+
+
+def check(got, refs, dtype):
+    assert set(got) == set(refs)
+    for r in refs:
+        assert got[r].shape == refs[r].shape
+        assert np.isfinite(got[r]).all(), f"{r}: non-finite logits (something outside the sequence was read)"
+        assert H.rel_to_max(got[r], refs[r]) < H.TOL[dtype], r
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_whole_requests(loaded, name, dtype):
+    model, reqs, refs, _ = loaded(name, dtype)
+    steps, most = H.trace_whole(reqs)
+    check(H.collect(steps, H.replay(model, steps, most), model.vocab_size), refs, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_last_32_tokens_one_by_one(loaded, name, dtype):
+    model, reqs, refs, _ = loaded(name, dtype)
+    steps, most = H.trace_last_decoded(reqs, 32)
+    check(H.collect(steps, H.replay(model, steps, most), model.vocab_size), refs, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_unequal_batches_one_after_another(loaded, name, dtype):
+    model, reqs, refs, _ = loaded(name, dtype)
+    rng = np.random.default_rng(3)
+    prompt_lens = {r: int(rng.integers(1, len(t) + 1)) for r, t in reqs.items()}
+    prompt_lens["r0"] = len(reqs["r0"])            # one request is all prompt and ends at once
+    steps, most = H.trace_batches(reqs, 3, prompt_lens)
+    # the cache is sized for one batch: the second batch can only run in the first one's slots and pages
+    check(H.collect(steps, H.replay(model, steps, most), model.vocab_size), refs, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(loaded, dtype):
+    """A one-token prompt followed by hundreds of single-token steps: the first tokens of a sequence
+    (positions 0, 1, 2 with one, two, three keys) and decoding across many page borders."""
+    model, reqs, refs, _ = loaded("C", dtype)
+    toks = reqs["r5"]
+    steps, most = H.trace_last_decoded({"r5": toks}, n_last=len(toks) - 1)
+    got = H.collect(steps, H.replay(model, steps, most), model.vocab_size)
+    check(got, {"r5": refs["r5"]}, dtype)
+    assert H.rel_to_max(got["r5"][:3], refs["r5"][:3]) < H.TOL[dtype]
+
+
+def test_cutting_does_not_change_fp32_logits_beyond_rounding(loaded):
+    model, reqs, refs, _ = loaded("C", "float32")
+    s1, m1 = H.trace_whole(reqs)
+    s2, m2 = H.trace_last_decoded(reqs, 32)
+    a = H.collect(s1, H.replay(model, s1, m1), model.vocab_size)
+    b = H.collect(s2, H.replay(model, s2, m2), model.vocab_size)
+    for r in reqs:
+        assert H.rel_to_max(a[r], b[r].astype(np.float64)) < 2e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(loaded, tmp_path, dtype):
+    """bin/trace_run as a user calls it: a subprocess, steps on standard input, files out."""
+    model, reqs, refs, d = loaded("A", dtype)
+    sub = {r: reqs[r] for r in ("r1", "r2", "r3")}
+    steps, most = H.trace_batches(sub, 3, {"r1": 4, "r2": 17, "r3": 9})
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype,
+                        "--out", str(out), "--max-tokens", str(most)],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    outs = []
+    for s in steps:
+        n = sum(len(e["want"]) for e in s["entries"])
+        f = out / f"{s['step']}.f32"
+        outs.append(np.fromfile(f, dtype="<f4").reshape(n, -1) if n else None)
+        assert f.exists() == bool(n)
+    check(H.collect(steps, outs, model.vocab_size), {r: refs[r] for r in sub}, dtype)
+
+
+def test_step_errors(loaded):
+    import llmi_b200 as L
+    from llmi_b200.cache import CacheError
+    model, reqs, _, _ = loaded("A", "float32")
+    cache = model.new_cache(128)
+    s = cache.alloc_slot()
+    with pytest.raises(L.StepError, match="out of range"):
+        model.step(cache, [L.SequenceStep(s, [model.vocab_size], [0])])
+    with pytest.raises(L.StepError, match="no tokens"):
+        model.step(cache, [L.SequenceStep(s, [], [])])
+    with pytest.raises(L.StepError, match="twice"):
+        model.step(cache, [L.SequenceStep(s, [1], [0]), L.SequenceStep(s, [2], [0])])
+    with pytest.raises(CacheError, match="not live"):
+        model.step(cache, [L.SequenceStep(s + 1, [1], [0])])
+    with pytest.raises(CacheError, match="context"):
+        model.step(cache, [L.SequenceStep(s, [1] * 129, [0])])
+    s2 = cache.alloc_slot()
+    model.step(cache, [L.SequenceStep(s, [1] * 64, [63])])
+    with pytest.raises(CacheError, match="full"):
+        model.step(cache, [L.SequenceStep(s2, [1] * 65, [0])])
+    assert cache.length(s2) == 0                       # a refused step reserves nothing
+    model.step(cache, [L.SequenceStep(s2, [1] * 64, [0])])
+    with pytest.raises(L.StepError, match="all start|continue"):
+        model.step(cache, [L.SequenceStep(s, [1, 2], [0])])
+    other = model.new_cache(64)
+    with pytest.raises(ValueError, match="not created"):
+        L.load(loaded("A", "float32")[3], "float32").step(other, [L.SequenceStep(0, [1], [0])])
+    cache.free_slot(s)
+    cache.free_slot(s2)
+    cache.check()
+
+
+def test_causality(loaded):
+    """Changing a later token leaves the logits of earlier positions bit-identical
+    (tests/transformer_test.cpp:201-218)."""
+    import llmi_b200 as L
+    model, reqs, _, _ = loaded("A", "float32")
+    cache = model.new_cache(128)
+    toks = list(reqs["r2"])
+    outs = []
+    for variant in (toks, toks[:9] + [(toks[9] + 1) % 256] + toks[10:]):
+        s = cache.alloc_slot()
+        outs.append(model.step(cache, [L.SequenceStep(s, variant, list(range(len(variant))))]).cpu().numpy().copy())
+        cache.free_slot(s)
+    assert (outs[0][:9] == outs[1][:9]).all()
+    assert not (outs[0][9:] == outs[1][9:]).all()
