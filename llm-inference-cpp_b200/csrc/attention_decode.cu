@@ -1,0 +1,340 @@
+// Decode attention: one new token per sequence attends over its sequence's cache pages (bf16).
+//
+// Reference loop: src/model/transformer.cpp:263-282 with T = 1 (scores over s = 0..pos, softmax,
+// weighted sum of values; kv head = query head / group).  A decode step reads every cached key and
+// value exactly once and does a handful of FLOPs per byte, so the kernel is built around HBM:
+//
+//  * the cache keeps one (page, kv head) tile of 64 positions contiguous, so a tile of K or V is ONE
+//    bulk copy (cp.async.bulk, 64*head_dim*2 bytes) into a ring of shared-memory stages, completed on
+//    mbarriers; a producer warp keeps the ring full while four consumer warps compute;
+//  * the positions of a sequence are cut into splits of `pages_per_split` pages (a function of
+//    position only) and a block works on one (split, kv head, sequence); all `G` query heads that
+//    share the kv head use the tile while it is in shared memory;
+//  * each block leaves (max, sum, weighted values) of its split in a workspace and takes a ticket;
+//    the block that takes a sequence-head's last ticket merges the splits in split order and writes
+//    the output.  Nothing waits for another block.
+//
+// Softmax runs in fp32 with a running maximum; the merge order is fixed, so a sequence's result does
+// not depend on its batch-mates.  `window` > 0 keeps keys pos-window+1..pos.
+#include <math.h>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace llmi {
+
+constexpr int DEC_PAGE = 64;          // positions per cache page (the cache's page size)
+constexpr int DEC_CONSUMERS = 4;      // consumer warps; each takes 16 keys of a page
+constexpr int DEC_THREADS = (DEC_CONSUMERS + 1) * 32;
+
+struct DecodeParams {
+  const __nv_bfloat16* q;   // [tokens, >= n_heads*HD], row pitch ldq
+  long ldq;
+  __nv_bfloat16* out;       // [tokens, n_heads*HD], row pitch ldo
+  long ldo;
+  const __nv_bfloat16* k_cache;
+  const __nv_bfloat16* v_cache;
+  const int32_t* seq_pages;   // [n_seqs, pages_stride]
+  const int32_t* seq_kv_len;  // [n_seqs] length after this step (0: padding)
+  const int32_t* seq_q_start; // [n_seqs] row of the sequence's token
+  int pages_stride;
+  int n_kv_heads;
+  float scale;
+  int window;
+  int pages_per_split;
+  int max_splits;            // gridDim.x
+  float* partials;           // [n_seqs, n_kv_heads, max_splits, G, HD + 2]
+  int* tickets;              // [n_seqs * n_kv_heads], zero between launches
+  int* error_flag;
+};
+
+template <int HD>
+struct DecCfg {
+  static constexpr int TILE_BYTES = DEC_PAGE * HD * 2;
+  static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  static constexpr int STAGES = HD <= 64 ? 4 : (HD <= 128 ? 4 : 3);
+  static constexpr int LPR = HD / 8;          // lanes per key row (16 bytes each)
+  static constexpr int RPI = 32 / LPR;        // rows per warp instruction
+  static constexpr int NI = 16 / RPI;         // instructions per warp per page (16 keys per warp)
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 128 /*align*/ + 128 /*barriers*/;
+};
+
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& raw, float* f) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 v = __bfloat1622float2(p[e]);
+    f[2 * e] = v.x;
+    f[2 * e + 1] = v.y;
+  }
+}
+
+template <int HD, int G>
+__global__ void __launch_bounds__(DEC_THREADS)
+attention_decode_kernel(DecodeParams p) {
+  using C = DecCfg<HD>;
+  static_assert(C::LPR >= 2 && C::LPR <= 32 && C::NI >= 1, "head size not supported by this layout");
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ float s_m[DEC_CONSUMERS][G], s_l[DEC_CONSUMERS][G];
+  __shared__ float s_acc[DEC_CONSUMERS][G][HD];
+  __shared__ int s_last;
+
+  const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_len = p.seq_kv_len[seq];
+  if (kv_len <= 0) return;                                   // padding sequence
+  const int pos = kv_len - 1;
+  const int lo = (p.window > 0 && kv_len - p.window > 0) ? kv_len - p.window : 0;
+  const int first_page = lo / DEC_PAGE, last_page = pos / DEC_PAGE;
+  const int first_split = first_page / p.pages_per_split, last_split = last_page / p.pages_per_split;
+  if (split < first_split || split > last_split) return;     // nothing of this sequence in this split
+  const int n_parts = last_split - first_split + 1;
+  const int pg0 = max(first_page, split * p.pages_per_split);
+  const int pg1 = min(last_page + 1, (split + 1) * p.pages_per_split);
+  const int n_pages = pg1 - pg0;
+
+  const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
+  const uint32_t bars = base + C::STAGES * C::STAGE_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), DEC_CONSUMERS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  const int32_t* pages = p.seq_pages + (size_t)seq * p.pages_stride;
+  if (warp == DEC_CONSUMERS) {
+    // producer
+    if (lane == 0) {
+      for (int i = 0; i < n_pages; ++i) {
+        const int s = i % C::STAGES;
+        if (i >= C::STAGES && !mbar_wait(empty_bar(s), ((i / C::STAGES) - 1) & 1, p.error_flag, 11)) break;
+        const size_t tile = ((size_t)pages[pg0 + i] * p.n_kv_heads + kvh) * (size_t)(DEC_PAGE * HD);
+        mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+        bulk_load(base + s * C::STAGE_BYTES, p.k_cache + tile, C::TILE_BYTES, full_bar(s));
+        bulk_load(base + s * C::STAGE_BYTES + C::TILE_BYTES, p.v_cache + tile, C::TILE_BYTES, full_bar(s));
+      }
+    }
+  } else {
+    // consumers: lane = (row group r, 16-byte chunk c) of a key row
+    const int c = lane % C::LPR, r = lane / C::LPR;
+    const int tok = p.seq_q_start[seq];
+    float q[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(p.q + (size_t)tok * p.ldq + (size_t)(kvh * G + g) * HD + c * 8);
+      bf16x8_to_f32(raw, q[g]);
+    }
+    float m[G], l[G], acc[G][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      m[g] = -INFINITY;
+      l[g] = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+    }
+    bool ok = true;
+    for (int i = 0; i < n_pages && ok; ++i) {
+      const int s = i % C::STAGES;
+      ok = mbar_wait(full_bar(s), (i / C::STAGES) & 1, p.error_flag, 12);
+      if (!ok) break;
+      const uint32_t k_tile = base + s * C::STAGE_BYTES, v_tile = k_tile + C::TILE_BYTES;
+      const int page_pos0 = (pg0 + i) * DEC_PAGE;
+      float sc[C::NI][G];
+      float pmax[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) pmax[g] = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < C::NI; ++j) {
+        const int row = warp * 16 + j * C::RPI + r;
+        uint4 raw;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                     : "r"(k_tile + (uint32_t)(row * HD + c * 8) * 2));
+        float kf[8];
+        bf16x8_to_f32(raw, kf);
+        const int kpos = page_pos0 + row;
+        const bool valid = kpos >= lo && kpos <= pos;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float d = 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) d = fmaf(q[g][e], kf[e], d);
+#pragma unroll
+          for (int o = 1; o < C::LPR; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+          sc[j][g] = valid ? d * p.scale : -INFINITY;
+          pmax[g] = fmaxf(pmax[g], sc[j][g]);
+        }
+      }
+      float corr[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int o = C::LPR; o < 32; o <<= 1) pmax[g] = fmaxf(pmax[g], __shfl_xor_sync(0xffffffffu, pmax[g], o));
+        const float m_new = fmaxf(m[g], pmax[g]);
+        corr[g] = (m_new == -INFINITY) ? 1.f : expf(m[g] - m_new);
+        m[g] = m_new;
+        l[g] *= corr[g];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[g][e] *= corr[g];
+      }
+#pragma unroll
+      for (int j = 0; j < C::NI; ++j) {
+        const int row = warp * 16 + j * C::RPI + r;
+        uint4 raw;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                     : "r"(v_tile + (uint32_t)(row * HD + c * 8) * 2));
+        float vf[8];
+        bf16x8_to_f32(raw, vf);
+        const int kpos = page_pos0 + row;
+        if (kpos < lo || kpos > pos) {   // whatever lies outside the sequence's positions counts as zero
+#pragma unroll
+          for (int e = 0; e < 8; ++e) vf[e] = 0.f;
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float pr = (sc[j][g] == -INFINITY) ? 0.f : expf(sc[j][g] - m[g]);
+          l[g] += pr;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pr, vf[e], acc[g][e]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar(s));
+    }
+    // fold the row groups of the warp: lanes with the same chunk c hold the same totals afterwards
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+      for (int o = C::LPR; o < 32; o <<= 1) {
+        l[g] += __shfl_xor_sync(0xffffffffu, l[g], o);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], o);
+      }
+      if (r == 0) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s_acc[warp][g][c * 8 + e] = acc[g][e];
+        if (c == 0) {
+          s_m[warp][g] = m[g];
+          s_l[warp][g] = l[g];
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // merge the four consumer warps (fixed order), then either finish or leave a partial
+  const int tok = p.seq_q_start[seq];
+  float* part = p.partials + ((((size_t)seq * p.n_kv_heads + kvh) * p.max_splits + (split - first_split)) * G) * (HD + 2);
+  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+    const int g = idx / HD, d = idx - g * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_CONSUMERS; ++w) M = fmaxf(M, s_m[w][g]);
+    float L = 0.f, A = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_CONSUMERS; ++w) {
+      const float f = (s_m[w][g] == -INFINITY) ? 0.f : expf(s_m[w][g] - M);
+      L += s_l[w][g] * f;
+      A += s_acc[w][g][d] * f;
+    }
+    if (n_parts == 1) {
+      p.out[(size_t)tok * p.ldo + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(A / L);
+    } else {
+      part[g * (HD + 2) + d] = A;
+      if (d == 0) {
+        part[g * (HD + 2) + HD] = M;
+        part[g * (HD + 2) + HD + 1] = L;
+      }
+    }
+  }
+  if (n_parts == 1) return;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(&p.tickets[seq * p.n_kv_heads + kvh], 1) == n_parts - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float* parts = p.partials + (((size_t)seq * p.n_kv_heads + kvh) * p.max_splits) * G * (HD + 2);
+  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+    const int g = idx / HD, d = idx - g * HD;
+    float M = -INFINITY;
+    for (int z = 0; z < n_parts; ++z) M = fmaxf(M, __ldcg(&parts[((size_t)z * G + g) * (HD + 2) + HD]));
+    float L = 0.f, A = 0.f;
+    for (int z = 0; z < n_parts; ++z) {
+      const float* pz = parts + ((size_t)z * G + g) * (HD + 2);
+      const float mz = __ldcg(&pz[HD]);
+      const float f = (mz == -INFINITY) ? 0.f : expf(mz - M);
+      L += __ldcg(&pz[HD + 1]) * f;
+      A += __ldcg(&pz[d]) * f;
+    }
+    p.out[(size_t)tok * p.ldo + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(A / L);
+  }
+  if (threadIdx.x == 0) p.tickets[seq * p.n_kv_heads + kvh] = 0;
+}
+
+template <int HD, int G>
+int launch_decode(const DecodeParams& p, int n_seqs, cudaStream_t stream) {
+  using C = DecCfg<HD>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             C::SMEM_BYTES) != cudaSuccess)
+      return LLMI_ERR_LAUNCH;
+    configured = true;
+  }
+  dim3 grid(p.max_splits, p.n_kv_heads, n_seqs);
+  attention_decode_kernel<HD, G><<<grid, DEC_THREADS, C::SMEM_BYTES, stream>>>(p);
+  return launch_status();
+}
+
+}  // namespace llmi
+
+using namespace llmi;
+
+// 1 if the (head size, group size) pair has a compiled decode kernel.
+LLMI_EXPORT int llmi_attention_decode_supported(int head_dim, int group) {
+  if (head_dim == 64 || head_dim == 128) return group == 1 || group == 2 || group == 3 || group == 4 || group == 8;
+  if (head_dim == 32) return group == 1 || group == 2 || group == 4;
+  return 0;
+}
+
+// Floats of workspace for n_seqs sequences of at most max_pages pages each.
+LLMI_EXPORT long llmi_attention_decode_workspace(int n_seqs, int n_heads, int head_dim, int max_pages,
+                                                 int pages_per_split) {
+  const long splits = (max_pages + pages_per_split - 1) / pages_per_split;
+  return (long)n_seqs * n_heads * splits * (head_dim + 2);
+}
+
+LLMI_EXPORT int llmi_attention_decode(const void* q, long ldq, void* out, long ldo, const void* k_cache,
+                                      const void* v_cache, const int32_t* seq_pages, int pages_stride,
+                                      const int32_t* seq_kv_len, const int32_t* seq_q_start, int n_seqs, int n_heads,
+                                      int n_kv_heads, int head_dim, float scale, int window, int max_pages,
+                                      int pages_per_split, float* partials, long partials_floats, int* tickets,
+                                      int n_tickets, int* error_flag, cudaStream_t stream) {
+  if (n_seqs <= 0 || n_heads <= 0 || n_kv_heads <= 0 || max_pages <= 0 || pages_per_split <= 0) return LLMI_ERR_BAD_SIZE;
+  if (n_heads % n_kv_heads) return LLMI_ERR_BAD_SIZE;
+  const int group = n_heads / n_kv_heads;
+  if (!llmi_attention_decode_supported(head_dim, group)) return LLMI_ERR_UNSUPPORTED;
+  if (((uintptr_t)q & 15) || (ldq & 7) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15)) return LLMI_ERR_ALIGN;
+  if (n_seqs > 65535 || n_kv_heads > 65535) return LLMI_ERR_BAD_SIZE;
+  const int splits = (max_pages + pages_per_split - 1) / pages_per_split;
+  if (llmi_attention_decode_workspace(n_seqs, n_heads, head_dim, max_pages, pages_per_split) > partials_floats ||
+      (long)n_seqs * n_kv_heads > n_tickets)
+    return LLMI_ERR_BAD_SIZE;
+  DecodeParams p{(const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)k_cache,
+                 (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads, scale,
+                 window, pages_per_split, splits, partials, tickets, error_flag};
+#define LLMI_DEC(HD, G) \
+  if (head_dim == HD && group == G) return launch_decode<HD, G>(p, n_seqs, stream)
+  LLMI_DEC(64, 1); LLMI_DEC(64, 2); LLMI_DEC(64, 3); LLMI_DEC(64, 4); LLMI_DEC(64, 8);
+  LLMI_DEC(128, 1); LLMI_DEC(128, 2); LLMI_DEC(128, 3); LLMI_DEC(128, 4); LLMI_DEC(128, 8);
+  LLMI_DEC(32, 1); LLMI_DEC(32, 2); LLMI_DEC(32, 4);
+#undef LLMI_DEC
+  return LLMI_ERR_UNSUPPORTED;
+}

@@ -1,0 +1,351 @@
+// y = x · Wᵀ on the 5th-generation tensor cores (tcgen05), bf16 inputs, fp32 accumulation in TMEM.
+//
+// The reference's matmul is a loop of dot products over weight rows (src/model/kernels.cpp:97-113),
+// W stored [out, in] (include/llmi/model/kernels.hpp:15-17).  Here the same product is tiled for
+// sm_100a: the WEIGHT tile is the 128-row operand of the MMA (out features on TMEM lanes) and the
+// ACTIVATION tile is the N operand (16..256 tokens on TMEM columns), so that one kernel serves a
+// 2,048-token prefill and a 1-token decode step alike: for few tokens the weights still stream
+// through full 128-row MMAs and the step is bound by HBM, not by the token count.
+//
+//   warp 0      : TMA producer — cp.async.bulk.tensor tiles of W [128 x 64] and x [BN x 64] into a
+//                 ring of shared-memory stages (128-byte swizzle), completion on mbarriers
+//   warp 1      : allocates TMEM; one thread issues tcgen05.mma (4 per stage, K = 16 each) and
+//                 tcgen05.commit to hand stages back and to signal the finished accumulator
+//   warps 2..5  : epilogue — tcgen05.ld the accumulator (one TMEM lane quadrant per warp), add bias,
+//                 and store / add into the output, which is token-major [tokens, out]
+//
+// Split-K: when a product has too few output tiles to fill the GPU (decode: o_proj, down_proj), the
+// k range is cut over gridDim.z.  Each CTA writes its fp32 partial tile to a workspace and takes a
+// ticket; the CTA that takes the last ticket of a tile adds the partials in split order and runs
+// the epilogue.  Nothing waits for another CTA, and the order of additions is fixed.
+//
+// Every wait on an mbarrier is bounded: after about a second it records an error code in
+// *error_flag and the CTA unwinds (frees TMEM, exits) instead of hanging.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace llmi {
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int TC_THREADS = 192;
+
+constexpr int OUT_STORE = 0, OUT_STORE_F32 = 1, OUT_ADD_F32 = 2;
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 bytes apart,
+// 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);   // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                        // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset
+  d |= (uint64_t)1 << 46;                        // version
+  d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN>
+struct TcConfig {
+  static constexpr int A_BYTES = TC_BM * TC_BK * 2;
+  static constexpr int B_BYTES = BN * TC_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+};
+
+struct TcParams {
+  int m_out, n_tok, k;      // W [m_out, k], x [n_tok, k]
+  void* out;                // [n_tok, m_out] row pitch ldo (elements)
+  long ldo;
+  const float* bias;        // [m_out] or null
+  int mode;
+  int splits;               // gridDim.z
+  float* workspace;         // [splits][tiles][BN][128] fp32 when splits > 1
+  int* tickets;             // [tiles], zero before and after the launch
+  int* error_flag;
+};
+
+template <int BN>
+__device__ __forceinline__ void tc_epilogue_store(const TcParams& p, float* v, int m, int n_base, int n_valid) {
+  // v: 16 consecutive tokens (n_base..) of out feature m
+  if (m >= p.m_out) return;
+  const float b = p.bias ? p.bias[m] : 0.f;
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    if (c >= n_valid) break;
+    const float val = v[c] + b;
+    const size_t idx = (size_t)(n_base + c) * p.ldo + m;
+    if (p.mode == OUT_STORE) ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(val);
+    else if (p.mode == OUT_STORE_F32) ((float*)p.out)[idx] = val;
+    else ((float*)p.out)[idx] += val;
+  }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
+  using C = TcConfig<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + C::STAGES * C::STAGE_BYTES;          // full[STAGES], empty[STAGES], accum, tmem slot
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+  const uint32_t accum_bar = bars + 8u * (2 * C::STAGES);
+  const uint32_t tmem_slot = accum_bar + 8u;
+  __shared__ int s_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * BN;
+  const int kblocks = (p.k + TC_BK - 1) / TC_BK;
+  const int per = (kblocks + p.splits - 1) / p.splits;
+  const int kb0 = blockIdx.z * per;
+  const int kb1 = min(kblocks, kb0 + per);
+  const int nkb = max(0, kb1 - kb0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(C::TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  uint32_t tmem_d;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_d) : "r"(tmem_slot));
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % C::STAGES;
+        if (i >= C::STAGES && !mbar_wait(empty_bar(s), ((i / C::STAGES) - 1) & 1, p.error_flag, 1)) break;
+        mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+        const uint32_t a_dst = base + s * C::STAGE_BYTES;
+        tma_load_2d(a_dst, &map_w, (kb0 + i) * TC_BK, m0, full_bar(s));
+        tma_load_2d(a_dst + C::A_BYTES, &map_x, (kb0 + i) * TC_BK, n0, full_bar(s));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // instruction descriptor: D fp32, A and B bf16, both K-major, N = BN, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % C::STAGES;
+        ok = mbar_wait(full_bar(s), (i / C::STAGES) & 1, p.error_flag, 2);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = base + s * C::STAGE_BYTES;
+        const uint64_t a_desc = umma_desc(a_addr), b_desc = umma_desc(a_addr + C::A_BYTES);
+#pragma unroll
+        for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
+          // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
+          umma_bf16(tmem_d, a_desc + 2 * k4, b_desc + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+        }
+        umma_commit(empty_bar(s));
+      }
+      umma_commit(accum_bar);
+    }
+  } else {
+    // epilogue warps: TMEM lane quadrant = warp % 4
+    const int quad = warp & 3;
+    const int m = m0 + quad * 32 + lane;
+    const uint32_t t_base = tmem_d + ((uint32_t)(quad * 32) << 16);
+    const bool ok = nkb > 0 ? mbar_wait(accum_bar, 0, p.error_flag, 3) : true;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+    const int n_tiles = gridDim.x * gridDim.y;
+    if (p.splits == 1) {
+      if (ok) {
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          if (n0 + c0 >= p.n_tok) break;
+          float v[16];
+          tmem_ld16(t_base + c0, v);
+          tc_epilogue_store<BN>(p, v, m, n0 + c0, p.n_tok - (n0 + c0));
+        }
+      }
+    } else {
+      float* ws = p.workspace + ((size_t)blockIdx.z * n_tiles + tile) * (BN * TC_BM);
+      if (ok) {
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          if (n0 + c0 >= p.n_tok) break;
+          float v[16];
+          if (nkb > 0) tmem_ld16(t_base + c0, v);
+          else {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) v[c] = 0.f;
+          }
+#pragma unroll
+          for (int c = 0; c < 16; ++c) ws[(c0 + c) * TC_BM + quad * 32 + lane] = v[c];
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+      if (threadIdx.x == 64) s_last = (atomicAdd(&p.tickets[tile], 1) == p.splits - 1);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (s_last) {
+        __threadfence();
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          if (n0 + c0 >= p.n_tok) break;
+          float v[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) v[c] = 0.f;
+          for (int z = 0; z < p.splits; ++z) {
+            const float* src = p.workspace + ((size_t)z * n_tiles + tile) * (BN * TC_BM);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) v[c] += __ldcg(&src[(c0 + c) * TC_BM + quad * 32 + lane]);
+          }
+          tc_epilogue_store<BN>(p, v, m, n0 + c0, p.n_tok - (n0 + c0));
+        }
+        if (threadIdx.x == 64) p.tickets[tile] = 0;
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(C::TMEM_COLS));
+  }
+}
+
+// ------------------------------------------------------------------------------------------- host
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+
+// A [rows, k] bf16 matrix with row pitch ld (elements), tiles of [box_rows, 64], 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* ptr, long rows, long k, long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return LLMI_ERR_DRIVER;
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LLMI_OK : LLMI_ERR_DRIVER;
+}
+
+template <int BN>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, dim3 grid, cudaStream_t stream) {
+  using C = TcConfig<BN>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+      return LLMI_ERR_LAUNCH;
+    configured = true;
+  }
+  gemm_tc_kernel<BN><<<grid, TC_THREADS, C::SMEM_BYTES, stream>>>(mw, mx, p);
+  return launch_status();
+}
+
+}  // namespace llmi
+
+using namespace llmi;
+
+// How many k-splits a product of this shape gets (a function of the shape only).
+LLMI_EXPORT int llmi_gemm_tc_splits(int n_tok, int m_out, int k) {
+  const int bn = n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : n_tok <= 128 ? 128 : 256;
+  const long tiles = (long)((m_out + TC_BM - 1) / TC_BM) * ((n_tok + bn - 1) / bn);
+  const int kblocks = (k + TC_BK - 1) / TC_BK;
+  if (tiles >= 96 || kblocks < 8) return 1;
+  int s = (int)((148 * 2 + tiles - 1) / tiles);
+  if (s > kblocks / 4) s = kblocks / 4;
+  if (s > 16) s = 16;
+  return s < 1 ? 1 : s;
+}
+
+// Bytes of fp32 workspace and number of int tickets the product needs (both 0 without split-K).
+LLMI_EXPORT long llmi_gemm_tc_workspace(int n_tok, int m_out, int k, int* n_tickets) {
+  const int s = llmi_gemm_tc_splits(n_tok, m_out, k);
+  const int bn = n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : n_tok <= 128 ? 128 : 256;
+  const long tiles = (long)((m_out + TC_BM - 1) / TC_BM) * ((n_tok + bn - 1) / bn);
+  if (n_tickets) *n_tickets = s > 1 ? (int)tiles : 0;
+  return s > 1 ? (long)s * tiles * bn * TC_BM * 4 : 0;
+}
+
+// y[n_tok, m_out] (mode) = x[n_tok, k] · w[m_out, k]ᵀ + bias; bf16 inputs; pitches in elements.
+// Requirements (else LLMI_ERR_ALIGN): x, w 16-byte aligned; ldx, ldw multiples of 8 elements.
+LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, const float* bias, void* y, long ldy,
+                             int n_tok, int m_out, int k, int mode, float* workspace, long workspace_bytes,
+                             int* tickets, int n_tickets, int* error_flag, cudaStream_t stream) {
+  if (n_tok <= 0 || m_out <= 0 || k <= 0) return LLMI_ERR_BAD_SIZE;
+  if (mode < 0 || mode > 2) return LLMI_ERR_UNSUPPORTED;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (ldw & 7)) return LLMI_ERR_ALIGN;
+  const int bn = n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : n_tok <= 128 ? 128 : 256;
+  int need_tickets = 0;
+  const long need_ws = llmi_gemm_tc_workspace(n_tok, m_out, k, &need_tickets);
+  int splits = llmi_gemm_tc_splits(n_tok, m_out, k);
+  if (splits > 1 && (need_ws > workspace_bytes || need_tickets > n_tickets || !workspace || !tickets)) splits = 1;
+  CUtensorMap mw, mx;
+  int rc = make_map(&mw, w, m_out, k, ldw, TC_BM);
+  if (rc != LLMI_OK) return rc;
+  rc = make_map(&mx, x, n_tok, k, ldx, bn);
+  if (rc != LLMI_OK) return rc;
+  TcParams p{m_out, n_tok, k, y, ldy, bias, mode, splits, workspace, tickets, error_flag};
+  dim3 grid((m_out + TC_BM - 1) / TC_BM, (n_tok + bn - 1) / bn, splits);
+  if (grid.y > 65535) return LLMI_ERR_BAD_SIZE;
+  switch (bn) {
+    case 16: return launch_tc<16>(mw, mx, p, grid, stream);
+    case 32: return launch_tc<32>(mw, mx, p, grid, stream);
+    case 64: return launch_tc<64>(mw, mx, p, grid, stream);
+    case 128: return launch_tc<128>(mw, mx, p, grid, stream);
+    default: return launch_tc<256>(mw, mx, p, grid, stream);
+  }
+}

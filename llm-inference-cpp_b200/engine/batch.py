@@ -123,7 +123,8 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
     n_real = len(seqs)
     n_seqs = max(n_real, pad_seqs_to) if decode else n_real
     n_tokens = sum(len(s.tokens) for s in seqs) + (n_seqs - n_real)
-    n_want = sum(len(s.want) for s in seqs)
+    n_want_real = sum(len(s.want) for s in seqs)
+    n_want = n_want_real + (n_seqs - n_real if pad_seqs_to else 0)   # a padded step also wants its padding rows
     kv_lens = [b + len(s.tokens) for b, s in zip(bases, seqs)]
     max_kv = max(kv_lens)
 
@@ -171,6 +172,9 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
         qstart[i] = t
         kvlen[i] = 0
         sslot[i] = -1
+        if pad_seqs_to:
+            want[w] = t
+            w += 1
         t += 1
     qstart[n_seqs] = t
     for g, start, P in page_layout:
@@ -183,6 +187,7 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
 
     ctx = StepContext()
     ctx.n_tokens, ctx.n_seqs, ctx.n_want = n_tokens, n_seqs, n_want
+    ctx.n_want_real = n_want_real
     ctx.n_real_seqs = n_real
     ctx.max_q_len = max(len(s.tokens) for s in seqs)
     ctx.max_kv_len = max_kv

@@ -1,0 +1,67 @@
+"""Recorded decode steps: one CUDA graph per (batch bucket, page-table bucket, choice).
+
+A decode step of a small model is a few hundred short kernels; launched one by one from
+Python, the launches cost more than the kernels.  A step's device work depends on the host
+only through the index arrays of :mod:`batch` — and those live at fixed addresses in one
+device block — so the whole step (embedding … head … choice of the next token) is recorded
+once per shape and replayed: the host writes the index block, copies it, and launches one
+graph.  Batches are padded up to a power of two of sequences and page tables to a power of
+two of pages; padding sequences have index -1 and are skipped by every kernel, so padding
+changes no result.  A graph holds raw addresses: it is dropped when a scratch buffer it
+uses is reallocated (``Runtime.generation``) or when it was recorded for another cache.
+"""
+from __future__ import annotations
+
+import torch
+
+
+def bucket(n: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b
+
+
+class DecodeGraphs:
+    def __init__(self, model):
+        self.model = model
+        self.graphs = {}
+        self.replays = 0
+        self.kernels_per_graph = {}
+
+    def step(self, cache, seqs, sampler, streams=None):
+        """A decode step (one token per sequence) followed by the choice; returns device int32 ids
+        of the real sequences (valid until the next step)."""
+        from .batch import plan_step
+        m = self.model
+        n_real = len(seqs)
+        B = bucket(n_real)
+        need_pages = max((cache.length(s.slot) + 1 + cache.page_size - 1) // cache.page_size for s in seqs)
+        P = max(need_pages, min(bucket(need_pages), cache.max_pages_per_seq))
+        ctx = plan_step(cache, seqs, m.spec.vocab_size, m.buffers, pad_seqs_to=B, pad_pages_to=P)
+        m._last_h2d = ctx.h2d_bytes
+        sampler.prepare(B, streams)
+        choice = (sampler.params.temperature, sampler.params.top_k, sampler.params.top_p)
+        key = (B, P, choice, id(cache), m.rt.generation, m.buffers.dev.data_ptr())
+        entry = self.graphs.get(key)
+        if entry is None:
+            # first time for this shape: run it plainly (this also sizes every scratch buffer), then record
+            ids = sampler.launch(m.run(ctx, cache), B)
+            key = (B, P, choice, id(cache), m.rt.generation, m.buffers.dev.data_ptr())
+            if key not in self.graphs:
+                from ..ops import kernels
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                before = kernels.launch_count()
+                with torch.cuda.graph(g):
+                    rec_ids = sampler.launch(m.run(ctx, cache), B)
+                self.kernels_per_graph[key] = kernels.launch_count() - before
+                kernels.launch_count(-(kernels.launch_count() - before))   # recording launches nothing
+                self.graphs[key] = (g, rec_ids)
+            return ids[:n_real]
+        g, rec_ids = entry
+        g.replay()
+        self.replays += 1
+        from ..ops import kernels
+        kernels.launch_count(self.kernels_per_graph[key])
+        return rec_ids[:n_real]

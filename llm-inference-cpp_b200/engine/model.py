@@ -31,6 +31,7 @@ class Model:
             if call.cache_of is not None and not (0 <= call.cache_of < len(spec.schedule)):
                 raise ValueError(f"schedule call {i} reads the cache of call {call.cache_of}, which does not exist")
         self.buffers = StepBuffers(self.rt.device, self.rt)
+        self._graphs = None
         self.parameter_count = sum(int(torch.tensor(d.shape).prod()) for d in expected_tensors(spec).values())
 
     # -- sizes -----------------------------------------------------------------------------
@@ -134,6 +135,11 @@ class Model:
 
     def step_and_choose(self, cache, seqs, sampler, streams=None, use_graphs: bool = True):
         """One step followed by the choice of one token per wanted row; returns the ids on the host."""
+        if use_graphs and all(len(s.tokens) == 1 for s in seqs) and all(s.want == [0] for s in seqs):
+            if self._graphs is None:
+                from .graphs import DecodeGraphs
+                self._graphs = DecodeGraphs(self)
+            return self._graphs.step(cache, seqs, sampler, streams).cpu()
         logits = self.step(cache, seqs)
         ids = sampler.choose(logits, streams)
         return ids.cpu()

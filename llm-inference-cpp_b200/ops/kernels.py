@@ -33,7 +33,20 @@ class KernelError(RuntimeError):
     pass
 
 
+_launches = 0
+
+
+def launch_count(add: int = 0) -> int:
+    """Kernels of this library launched so far in this process (``add`` adjusts it: a graph replay
+    adds the kernels it holds)."""
+    global _launches
+    _launches += add
+    return _launches
+
+
 def _check(name: str, code: int) -> None:
+    global _launches
+    _launches += 1
     if code != 0:
         raise KernelError(f"{name}: {_ERRORS.get(code, f'error {code}')}")
 
@@ -68,8 +81,11 @@ def lib():
     l = library.load()
     if not _configured:
         for name in ("llmi_embed", "llmi_rmsnorm", "llmi_swiglu", "llmi_linear_simt", "llmi_rope_store",
-                     "llmi_attention_generic", "llmi_argmax", "llmi_sample"):
+                     "llmi_attention_generic", "llmi_argmax", "llmi_sample", "llmi_gemm_tc", "llmi_gemm_tc_splits",
+                     "llmi_attention_decode", "llmi_attention_decode_supported"):
             getattr(l, name).restype = c_int
+        l.llmi_gemm_tc_workspace.restype = c_long
+        l.llmi_attention_decode_workspace.restype = c_long
         _configured = True
     return l
 
@@ -122,9 +138,72 @@ def linear_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch
         c_long(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(mode), _stream()))
 
 
+class _TcScratch:
+    """Per-device scratch of the tensor-core product: split-K partial tiles, tile tickets (zero between
+    launches) and an error word that a bounded wait sets instead of hanging."""
+    WORKSPACE_BYTES = 32 << 20
+    N_TICKETS = 4096
+    N_ATTN_TICKETS = 1 << 16
+
+    def __init__(self, device):
+        self.workspace = torch.empty(self.WORKSPACE_BYTES // 4, dtype=torch.float32, device=device)
+        self.tickets = torch.zeros(self.N_TICKETS, dtype=torch.int32, device=device)
+        self.attn_tickets = torch.zeros(self.N_ATTN_TICKETS, dtype=torch.int32, device=device)
+        self.error = torch.zeros(1, dtype=torch.int32, device=device)
+
+
+_tc_scratch: dict = {}
+
+
+def tc_scratch(device) -> _TcScratch:
+    key = torch.device(device).index or 0
+    if key not in _tc_scratch:
+        _tc_scratch[key] = _TcScratch(device)
+    return _tc_scratch[key]
+
+
+def check_device_errors(device) -> None:
+    """Raise if a kernel's bounded wait gave up since the last check (synchronises the device)."""
+    sc = _tc_scratch.get(torch.device(device).index or 0)
+    if sc is not None:
+        code = int(sc.error.item())
+        if code:
+            sc.error.zero_()
+            raise KernelError(f"a bounded wait inside a kernel timed out (code {code}); results are invalid")
+
+
+def gemm_tc_eligible(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
+            mode: int = OUT_STORE) -> None:
+    """out (mode) x·wᵀ + bias on the tcgen05 tensor cores; bf16 inputs, fp32 accumulation."""
+    _need_cuda(x, w, out, bias)
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N) and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    assert out.dtype == (torch.bfloat16 if mode == OUT_STORE else torch.float32)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == N
+    sc = tc_scratch(x.device)
+    _check("gemm_tc", lib().llmi_gemm_tc(
+        _ptr(x), c_long(x.stride(0)), _ptr(w), c_long(w.stride(0)), _ptr(bias), _ptr(out), c_long(out.stride(0)),
+        c_int(M), c_int(N), c_int(K), c_int(mode), _ptr(sc.workspace), c_long(sc.WORKSPACE_BYTES), _ptr(sc.tickets),
+        c_int(sc.N_TICKETS), _ptr(sc.error), _stream()))
+
+
+_FORCE_SIMT = __import__("os").environ.get("LLMI_LINEAR", "") == "simt"
+
+
 def linear(x, w, out, bias=None, mode: int = OUT_STORE) -> None:
-    """The matrix product of the step: picks the kernel for the type and shape."""
-    linear_simt(x, w, out, bias, mode)
+    """The matrix product of the step: the tensor-core kernel for bf16 operands it can take (16-byte
+    aligned rows), the fp32 FMA kernel for the 32-bit path and for everything else."""
+    if not _FORCE_SIMT and gemm_tc_eligible(x, w):
+        gemm_tc(x, w, out, bias, mode)
+    else:
+        linear_simt(x, w, out, bias, mode)
 
 
 def rope_store(qkv: torch.Tensor, inv_freq: torch.Tensor | None, rotary_dim: int, tok_seq, tok_pos, seq_pages,
@@ -176,8 +255,55 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, u
                                        _ptr(probs_scratch), _ptr(out), _stream()))
 
 
+DECODE_PAGES_PER_SPLIT = 4     # a split of the decode kernel covers 256 positions, whatever the batch
+
+
+def attention_decode_supported(head_dim: int, group: int) -> bool:
+    return bool(lib().llmi_attention_decode_supported(c_int(head_dim), c_int(group)))
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start,
+                     n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int, partials: torch.Tensor,
+                     pages_per_split: int = DECODE_PAGES_PER_SPLIT) -> None:
+    """One token per sequence over its cache pages (bf16, page size 64), split over positions.
+
+    ``partials``: fp32 scratch of at least ``attention_decode_workspace(...)`` floats.
+    """
+    _need_cuda(q, out, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start, partials)
+    S, P = seq_pages.shape
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.shape[-2] == 64 and partials.dtype == torch.float32
+    sc = tc_scratch(q.device)
+    _check("attention_decode", lib().llmi_attention_decode(
+        _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(seq_pages),
+        c_int(seq_pages.stride(0)), _ptr(seq_kv_len), _ptr(seq_q_start), c_int(S), c_int(n_heads), c_int(n_kv_heads),
+        c_int(head_dim), c_float(scale), c_int(window), c_int(P), c_int(pages_per_split), _ptr(partials),
+        c_long(partials.numel()), _ptr(sc.attn_tickets), c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), _stream()))
+
+
+def attention_decode_workspace(n_seqs: int, n_heads: int, head_dim: int, max_pages: int,
+                               pages_per_split: int = DECODE_PAGES_PER_SPLIT) -> int:
+    return int(lib().llmi_attention_decode_workspace(c_int(n_seqs), c_int(n_heads), c_int(head_dim), c_int(max_pages),
+                                                     c_int(pages_per_split)))
+
+
+_FORCE_GENERIC_ATTENTION = __import__("os").environ.get("LLMI_ATTENTION", "") == "generic"
+
+
 def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_pages, page_size: int, n_heads: int,
-              n_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
-    """Attention of a step's tokens over the cache; q is the first n_heads*head_dim columns of ``qkv``."""
+              n_kv_heads: int, head_dim: int, scale: float, window: int = 0, rt=None) -> None:
+    """Attention of a step's tokens over the cache; q is the first n_heads*head_dim columns of ``qkv``.
+
+    A decode step in bf16 with a head size the split kernel has goes to it; everything else (the
+    32-bit path, prefill for now, other head sizes) goes to the generic kernel.
+    """
+    if (ctx.decode and qkv.dtype == torch.bfloat16 and page_size == 64 and rt is not None and not _FORCE_GENERIC_ATTENTION
+            and seq_pages.shape[0] * n_kv_heads <= _TcScratch.N_ATTN_TICKETS
+            and attention_decode_supported(head_dim, n_heads // n_kv_heads)):
+        S, P = seq_pages.shape
+        partials = rt.scratch("attn_partials", (attention_decode_workspace(S, n_heads, head_dim, P),), torch.float32)
+        attention_decode(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_kv_len, ctx.seq_q_start, n_heads, n_kv_heads,
+                         head_dim, scale, window, partials)
+        return
     attention_generic(qkv, out, k_cache, v_cache, ctx.tok_seq, ctx.tok_pos, seq_pages, page_size, n_heads,
                       n_kv_heads, head_dim, scale, window)

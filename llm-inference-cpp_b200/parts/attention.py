@@ -67,5 +67,5 @@ class GQAttention:
         attn = self.rt.scratch("attn_out", (T, nh * hd))
         g = binding.group
         kernels.attention(qkv, attn, g.k[binding.index], g.v[binding.index], ctx, ctx.pages_of(g), g.page_size,
-                          nh, nkv, hd, self.scale, self.window)
+                          nh, nkv, hd, self.scale, self.window, rt=self.rt)
         kernels.linear(attn, self.w_o, x, None, kernels.OUT_ADD_F32)

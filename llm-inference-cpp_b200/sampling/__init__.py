@@ -52,24 +52,36 @@ class Sampler:
         self.rt = rt
         self._u_host = None
 
-    def choose(self, logits: torch.Tensor, streams=None) -> torch.Tensor:
-        """logits fp32 [R, V] -> int32 [R] on the device.  ``streams``: one UniformStream per row
-        (only read when sampling)."""
+    def prepare(self, n_rows: int, streams=None) -> None:
+        """Host side of a choice: draw one uniform number per real row and copy them to the device.
+        (Kept apart from ``launch`` so that the launch can be recorded in a CUDA graph.)"""
+        if self.params.greedy:
+            return
+        if streams is None or len(streams) > n_rows:
+            raise ValueError("sampling needs one uniform stream per row")
+        if self._u_host is None or self._u_host.numel() < n_rows:
+            self._u_host = torch.empty(max(n_rows, 64), dtype=torch.float64, pin_memory=True)
+        u_np = self._u_host.numpy()
+        u_np[:n_rows] = 0.5
+        for i, s in enumerate(streams):
+            u_np[i] = s.next()
+        u_dev = self.rt.scratch("sample_uniforms", (max(n_rows, 64),), torch.float64)
+        u_dev[:n_rows].copy_(self._u_host[:n_rows], non_blocking=True)
+
+    def launch(self, logits: torch.Tensor, n_rows: int | None = None) -> torch.Tensor:
+        """Device side of a choice: logits fp32 [R, V] -> int32 [R] (scratch, valid until the next call)."""
         R, V = logits.shape
-        out = self.rt.scratch("sampled_ids", (R,), torch.int32)
+        out = self.rt.scratch("sampled_ids", (max(R, 64),), torch.int32)[:R]
         p = self.params
         if p.greedy:
             kernels.argmax(logits, out)
             return out
-        if streams is None or len(streams) != R:
-            raise ValueError("sampling needs one uniform stream per row")
-        if self._u_host is None or self._u_host.numel() < R:
-            self._u_host = torch.empty(max(R, 64), dtype=torch.float64, pin_memory=True)
-        u_np = self._u_host.numpy()
-        for i, s in enumerate(streams):
-            u_np[i] = s.next()
-        u_dev = self.rt.scratch("sample_uniforms", (R,), torch.float64)
-        u_dev.copy_(self._u_host[:R], non_blocking=False)
+        u_dev = self.rt.scratch("sample_uniforms", (max(R, 64),), torch.float64)
         probs = self.rt.scratch("sample_probs", (R, V), torch.float32)
         kernels.sample(logits, float(p.temperature), int(p.top_k), float(p.top_p), u_dev, probs, out)
         return out
+
+    def choose(self, logits: torch.Tensor, streams=None) -> torch.Tensor:
+        """logits fp32 [R, V] -> int32 [R] on the device; ``streams``: one UniformStream per row."""
+        self.prepare(logits.shape[0], streams)
+        return self.launch(logits)

@@ -250,3 +250,47 @@ def test_sample_distribution():
     freq = np.bincount(out.cpu().numpy(), minlength=V) / n
     assert set(np.nonzero(freq)[0]) <= set(np.nonzero(p)[0])
     assert np.abs(freq - p).max() < 0.03
+
+
+@pytest.mark.parametrize("n_tok,m_out,k", [(1, 200, 72), (5, 64, 64), (16, 128, 64), (17, 384, 120), (70, 129, 1000),
+                                           (300, 520, 136), (64, 2048, 8192), (8, 256, 4096), (1000, 136, 264)])
+def test_gemm_tc_all_modes(n_tok, m_out, k):
+    """The tcgen05 product against fp64 on ragged shapes, with and without split-K."""
+    kk = K()
+    torch.manual_seed(n_tok + m_out + k)
+    x = torch.randn(n_tok, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(m_out, k, device="cuda") * 0.05).to(torch.bfloat16)
+    b = torch.randn(m_out, device="cuda")
+    ref = x.double() @ w.double().T
+    y32 = torch.full((n_tok, m_out), float("nan"), device="cuda")
+    kk.gemm_tc(x, w, y32, None, kk.OUT_STORE_F32)
+    assert rel(y32, ref) < 2e-5
+    y = torch.empty(n_tok, m_out, device="cuda", dtype=torch.bfloat16)
+    kk.gemm_tc(x, w, y, b, kk.OUT_STORE)
+    assert rel(y, ref + b.double()) < 6e-3
+    acc = torch.randn(n_tok, m_out, device="cuda")
+    before = acc.clone()
+    kk.gemm_tc(x, w, acc, None, kk.OUT_ADD_F32)
+    assert rel(acc, before.double() + ref) < 2e-5
+    # the same rows whatever else is in the call (a row's value does not depend on the batch)
+    y1 = torch.empty(1, m_out, device="cuda")
+    kk.gemm_tc(x[n_tok - 1:], w, y1, None, kk.OUT_STORE_F32)
+    if kk.lib().llmi_gemm_tc_splits(n_tok, m_out, k) == kk.lib().llmi_gemm_tc_splits(1, m_out, k):
+        assert torch.equal(y1, y32[n_tok - 1:])
+    else:
+        assert rel(y1, y32[n_tok - 1:]) < 1e-5
+    kk.check_device_errors("cuda:0")
+    assert int(kk.tc_scratch("cuda:0").tickets.abs().sum()) == 0
+
+
+def test_gemm_tc_strided_input_and_refusals():
+    kk = K()
+    wide = torch.randn(40, 64 + 2 * 64, device="cuda").to(torch.bfloat16)
+    w = torch.randn(96, 64, device="cuda").to(torch.bfloat16)
+    y = torch.empty(40, 96, device="cuda")
+    kk.gemm_tc(wide[:, 64:128], w, y, None, kk.OUT_STORE_F32)
+    assert rel(y, wide[:, 64:128].double() @ w.double().T) < 2e-5
+    assert not kk.gemm_tc_eligible(torch.empty(4, 20, device="cuda", dtype=torch.bfloat16), w)       # pitch of 40 bytes
+    with pytest.raises(kk.KernelError, match="aligned"):
+        kk.gemm_tc(torch.empty(4, 20, device="cuda", dtype=torch.bfloat16), torch.empty(8, 20, device="cuda", dtype=torch.bfloat16),
+                   torch.empty(4, 8, device="cuda"), None, kk.OUT_STORE_F32)
