@@ -10,7 +10,9 @@
 //  * the positions of a sequence are cut into splits of `pages_per_split` pages (a function of
 //    position only) and a block works on one (split, kv head, sequence); all `G` query heads that
 //    share the kv head use the tile while it is in shared memory;
-//  * each block leaves (max, sum, weighted values) of its split in a workspace and takes a ticket;
+//  * the grid is persistent (as many blocks as fit on the device); a block walks through its items and
+//    its copy ring runs on across items, so HBM stays busy while an item is merged and written;
+//  * each item leaves (max, sum, weighted values) of its split in a workspace and takes a ticket;
 //    the block that takes a sequence-head's last ticket merges the splits in split order and writes
 //    the output.  Nothing waits for another block.
 //
@@ -69,9 +71,12 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4& raw, float* f) {
   }
 }
 
+// Work is cut into items (sequence, kv head, split).  The grid is persistent: block b takes items
+// b, b + gridDim.x, ... and its ring of stages runs on across item borders, so the copies of the
+// next item are in flight while the current item is merged and written.
 template <int HD, int G>
 __global__ void __launch_bounds__(DEC_THREADS)
-attention_decode_kernel(DecodeParams p) {
+attention_decode_kernel(DecodeParams p, int n_items) {
   using C = DecCfg<HD>;
   static_assert(C::LPR >= 2 && C::LPR <= 32 && C::NI >= 1, "head size not supported by this layout");
   extern __shared__ uint8_t smem_raw[];
@@ -79,20 +84,7 @@ attention_decode_kernel(DecodeParams p) {
   __shared__ float s_acc[DEC_CONSUMERS][G][HD];
   __shared__ int s_last;
 
-  const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kv_len = p.seq_kv_len[seq];
-  if (kv_len <= 0) return;                                   // padding sequence
-  const int pos = kv_len - 1;
-  const int lo = (p.window > 0 && kv_len - p.window > 0) ? kv_len - p.window : 0;
-  const int first_page = lo / DEC_PAGE, last_page = pos / DEC_PAGE;
-  const int first_split = first_page / p.pages_per_split, last_split = last_page / p.pages_per_split;
-  if (split < first_split || split > last_split) return;     // nothing of this sequence in this split
-  const int n_parts = last_split - first_split + 1;
-  const int pg0 = max(first_page, split * p.pages_per_split);
-  const int pg1 = min(last_page + 1, (split + 1) * p.pages_per_split);
-  const int n_pages = pg1 - pg0;
-
   const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
   const uint32_t bars = base + C::STAGES * C::STAGE_BYTES;
   auto full_bar = [&](int s) { return bars + 8u * s; };
@@ -106,22 +98,55 @@ attention_decode_kernel(DecodeParams p) {
   }
   __syncthreads();
 
-  const int32_t* pages = p.seq_pages + (size_t)seq * p.pages_stride;
+  // An item's page range; false if the item is empty (padding sequence, or a split outside the sequence).
+  auto item_range = [&](int item, int& seq, int& kvh, int& split, int& lo, int& pos, int& pg0, int& n_pages,
+                        int& first_split, int& n_parts) -> bool {
+    split = item % p.max_splits;
+    const int sh = item / p.max_splits;
+    kvh = sh % p.n_kv_heads;
+    seq = sh / p.n_kv_heads;
+    const int kv_len = p.seq_kv_len[seq];
+    if (kv_len <= 0) return false;
+    pos = kv_len - 1;
+    lo = (p.window > 0 && kv_len - p.window > 0) ? kv_len - p.window : 0;
+    const int first_page = lo / DEC_PAGE, last_page = pos / DEC_PAGE;
+    first_split = first_page / p.pages_per_split;
+    const int last_split = last_page / p.pages_per_split;
+    if (split < first_split || split > last_split) return false;
+    n_parts = last_split - first_split + 1;
+    pg0 = max(first_page, split * p.pages_per_split);
+    n_pages = min(last_page + 1, (split + 1) * p.pages_per_split) - pg0;
+    return true;
+  };
+
+  int it = 0;   // pages handled so far by this block: the ring position, the same in producer and consumers
   if (warp == DEC_CONSUMERS) {
-    // producer
     if (lane == 0) {
-      for (int i = 0; i < n_pages; ++i) {
-        const int s = i % C::STAGES;
-        if (i >= C::STAGES && !mbar_wait(empty_bar(s), ((i / C::STAGES) - 1) & 1, p.error_flag, 11)) break;
-        const size_t tile = ((size_t)pages[pg0 + i] * p.n_kv_heads + kvh) * (size_t)(DEC_PAGE * HD);
-        mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
-        bulk_load(base + s * C::STAGE_BYTES, p.k_cache + tile, C::TILE_BYTES, full_bar(s));
-        bulk_load(base + s * C::STAGE_BYTES + C::TILE_BYTES, p.v_cache + tile, C::TILE_BYTES, full_bar(s));
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        int seq, kvh, split, lo, pos, pg0, n_pages, first_split, n_parts;
+        if (!item_range(item, seq, kvh, split, lo, pos, pg0, n_pages, first_split, n_parts)) continue;
+        const int32_t* pages = p.seq_pages + (size_t)seq * p.pages_stride;
+        for (int i = 0; i < n_pages; ++i, ++it) {
+          const int s = it % C::STAGES;
+          if (it >= C::STAGES && !mbar_wait(empty_bar(s), ((it / C::STAGES) - 1) & 1, p.error_flag, 11)) { ok = false; break; }
+          const size_t tile = ((size_t)pages[pg0 + i] * p.n_kv_heads + kvh) * (size_t)(DEC_PAGE * HD);
+          mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+          bulk_load(base + s * C::STAGE_BYTES, p.k_cache + tile, C::TILE_BYTES, full_bar(s));
+          bulk_load(base + s * C::STAGE_BYTES + C::TILE_BYTES, p.v_cache + tile, C::TILE_BYTES, full_bar(s));
+        }
       }
     }
-  } else {
-    // consumers: lane = (row group r, 16-byte chunk c) of a key row
-    const int c = lane % C::LPR, r = lane / C::LPR;
+    return;
+  }
+
+  // consumers: lane = (row group r, 16-byte chunk c) of a key row
+  const int c = lane % C::LPR, r = lane / C::LPR;
+  const int ctid = threadIdx.x;   // 0..127
+  bool ok = true;
+  for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    int seq, kvh, split, lo, pos, pg0, n_pages, first_split, n_parts;
+    if (!item_range(item, seq, kvh, split, lo, pos, pg0, n_pages, first_split, n_parts)) continue;
     const int tok = p.seq_q_start[seq];
     float q[G][8];
 #pragma unroll
@@ -137,10 +162,9 @@ attention_decode_kernel(DecodeParams p) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
     }
-    bool ok = true;
-    for (int i = 0; i < n_pages && ok; ++i) {
-      const int s = i % C::STAGES;
-      ok = mbar_wait(full_bar(s), (i / C::STAGES) & 1, p.error_flag, 12);
+    for (int i = 0; i < n_pages; ++i, ++it) {
+      const int s = it % C::STAGES;
+      ok = mbar_wait(full_bar(s), (it / C::STAGES) & 1, p.error_flag, 12);
       if (!ok) break;
       const uint32_t k_tile = base + s * C::STAGE_BYTES, v_tile = k_tile + C::TILE_BYTES;
       const int page_pos0 = (pg0 + i) * DEC_PAGE;
@@ -170,17 +194,16 @@ attention_decode_kernel(DecodeParams p) {
           pmax[g] = fmaxf(pmax[g], sc[j][g]);
         }
       }
-      float corr[G];
 #pragma unroll
       for (int g = 0; g < G; ++g) {
 #pragma unroll
         for (int o = C::LPR; o < 32; o <<= 1) pmax[g] = fmaxf(pmax[g], __shfl_xor_sync(0xffffffffu, pmax[g], o));
         const float m_new = fmaxf(m[g], pmax[g]);
-        corr[g] = (m_new == -INFINITY) ? 1.f : expf(m[g] - m_new);
+        const float corr = (m_new == -INFINITY) ? 1.f : expf(m[g] - m_new);
         m[g] = m_new;
-        l[g] *= corr[g];
+        l[g] *= corr;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[g][e] *= corr[g];
+        for (int e = 0; e < 8; ++e) acc[g][e] *= corr;
       }
 #pragma unroll
       for (int j = 0; j < C::NI; ++j) {
@@ -207,6 +230,7 @@ attention_decode_kernel(DecodeParams p) {
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(s));
     }
+    if (!ok) break;
     // fold the row groups of the warp: lanes with the same chunk c hold the same totals afterwards
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -225,57 +249,59 @@ attention_decode_kernel(DecodeParams p) {
         }
       }
     }
-  }
-  __syncthreads();
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // the four consumer warps
 
-  // merge the four consumer warps (fixed order), then either finish or leave a partial
-  const int tok = p.seq_q_start[seq];
-  float* part = p.partials + ((((size_t)seq * p.n_kv_heads + kvh) * p.max_splits + (split - first_split)) * G) * (HD + 2);
-  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
-    const int g = idx / HD, d = idx - g * HD;
-    float M = -INFINITY;
+    // merge the four consumer warps (fixed order), then either finish or leave a partial
+    float* part = p.partials + ((((size_t)seq * p.n_kv_heads + kvh) * p.max_splits + (split - first_split)) * G) * (HD + 2);
+    for (int idx = ctid; idx < G * HD; idx += DEC_CONSUMERS * 32) {
+      const int g = idx / HD, d = idx - g * HD;
+      float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < DEC_CONSUMERS; ++w) M = fmaxf(M, s_m[w][g]);
-    float L = 0.f, A = 0.f;
+      for (int w = 0; w < DEC_CONSUMERS; ++w) M = fmaxf(M, s_m[w][g]);
+      float L = 0.f, A = 0.f;
 #pragma unroll
-    for (int w = 0; w < DEC_CONSUMERS; ++w) {
-      const float f = (s_m[w][g] == -INFINITY) ? 0.f : expf(s_m[w][g] - M);
-      L += s_l[w][g] * f;
-      A += s_acc[w][g][d] * f;
-    }
-    if (n_parts == 1) {
-      p.out[(size_t)tok * p.ldo + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(A / L);
-    } else {
-      part[g * (HD + 2) + d] = A;
-      if (d == 0) {
-        part[g * (HD + 2) + HD] = M;
-        part[g * (HD + 2) + HD + 1] = L;
+      for (int w = 0; w < DEC_CONSUMERS; ++w) {
+        const float f = (s_m[w][g] == -INFINITY) ? 0.f : expf(s_m[w][g] - M);
+        L += s_l[w][g] * f;
+        A += s_acc[w][g][d] * f;
+      }
+      if (n_parts == 1) {
+        p.out[(size_t)tok * p.ldo + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(A / L);
+      } else {
+        part[g * (HD + 2) + d] = A;
+        if (d == 0) {
+          part[g * (HD + 2) + HD] = M;
+          part[g * (HD + 2) + HD + 1] = L;
+        }
       }
     }
-  }
-  if (n_parts == 1) return;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) s_last = (atomicAdd(&p.tickets[seq * p.n_kv_heads + kvh], 1) == n_parts - 1);
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  const float* parts = p.partials + (((size_t)seq * p.n_kv_heads + kvh) * p.max_splits) * G * (HD + 2);
-  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
-    const int g = idx / HD, d = idx - g * HD;
-    float M = -INFINITY;
-    for (int z = 0; z < n_parts; ++z) M = fmaxf(M, __ldcg(&parts[((size_t)z * G + g) * (HD + 2) + HD]));
-    float L = 0.f, A = 0.f;
-    for (int z = 0; z < n_parts; ++z) {
-      const float* pz = parts + ((size_t)z * G + g) * (HD + 2);
-      const float mz = __ldcg(&pz[HD]);
-      const float f = (mz == -INFINITY) ? 0.f : expf(mz - M);
-      L += __ldcg(&pz[HD + 1]) * f;
-      A += __ldcg(&pz[d]) * f;
+    if (n_parts > 1) {
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ctid == 0) s_last = (atomicAdd(&p.tickets[seq * p.n_kv_heads + kvh], 1) == n_parts - 1);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (s_last) {
+        __threadfence();
+        const float* parts = p.partials + (((size_t)seq * p.n_kv_heads + kvh) * p.max_splits) * G * (HD + 2);
+        for (int idx = ctid; idx < G * HD; idx += DEC_CONSUMERS * 32) {
+          const int g = idx / HD, d = idx - g * HD;
+          float M = -INFINITY;
+          for (int z = 0; z < n_parts; ++z) M = fmaxf(M, __ldcg(&parts[((size_t)z * G + g) * (HD + 2) + HD]));
+          float L = 0.f, A = 0.f;
+          for (int z = 0; z < n_parts; ++z) {
+            const float* pz = parts + ((size_t)z * G + g) * (HD + 2);
+            const float mz = __ldcg(&pz[HD]);
+            const float f = (mz == -INFINITY) ? 0.f : expf(mz - M);
+            L += __ldcg(&pz[HD + 1]) * f;
+            A += __ldcg(&pz[d]) * f;
+          }
+          p.out[(size_t)tok * p.ldo + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(A / L);
+        }
+        if (ctid == 0) p.tickets[seq * p.n_kv_heads + kvh] = 0;
+      }
     }
-    p.out[(size_t)tok * p.ldo + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(A / L);
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // s_m / s_acc / s_last are free for the next item
   }
-  if (threadIdx.x == 0) p.tickets[seq * p.n_kv_heads + kvh] = 0;
 }
 
 template <int HD, int G>
@@ -288,8 +314,20 @@ int launch_decode(const DecodeParams& p, int n_seqs, cudaStream_t stream) {
       return LLMI_ERR_LAUNCH;
     configured = true;
   }
-  dim3 grid(p.max_splits, p.n_kv_heads, n_seqs);
-  attention_decode_kernel<HD, G><<<grid, DEC_THREADS, C::SMEM_BYTES, stream>>>(p);
+  const long n_items = (long)n_seqs * p.n_kv_heads * p.max_splits;
+  if (n_items > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
+  static int resident = 0;   // blocks of this kernel that fit on the device at once
+  if (!resident) {
+    int per_sm = 0, sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<HD, G>, DEC_THREADS,
+                                                      C::SMEM_BYTES) != cudaSuccess || per_sm < 1)
+      per_sm = 1;
+    resident = per_sm * (sms > 0 ? sms : 148);
+  }
+  const int grid = (int)(n_items < resident ? n_items : resident);
+  attention_decode_kernel<HD, G><<<grid, DEC_THREADS, C::SMEM_BYTES, stream>>>(p, (int)n_items);
   return launch_status();
 }
 
@@ -322,7 +360,6 @@ LLMI_EXPORT int llmi_attention_decode(const void* q, long ldq, void* out, long l
   const int group = n_heads / n_kv_heads;
   if (!llmi_attention_decode_supported(head_dim, group)) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)q & 15) || (ldq & 7) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15)) return LLMI_ERR_ALIGN;
-  if (n_seqs > 65535 || n_kv_heads > 65535) return LLMI_ERR_BAD_SIZE;
   const int splits = (max_pages + pages_per_split - 1) / pages_per_split;
   if (llmi_attention_decode_workspace(n_seqs, n_heads, head_dim, max_pages, pages_per_split) > partials_floats ||
       (long)n_seqs * n_kv_heads > n_tickets)

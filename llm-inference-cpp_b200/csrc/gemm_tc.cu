@@ -82,7 +82,10 @@ struct TcConfig {
   static constexpr int A_BYTES = TC_BM * TC_BK * 2;
   static constexpr int B_BYTES = BN * TC_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+  // few-token tiles stream weights: 4 stages per CTA and 2-3 CTAs per SM keep more bytes in flight and
+  // hide each CTA's start-up behind its neighbours; large tiles are compute-bound and take the whole SM
+  static constexpr int STAGES = BN <= 64 ? 4 : (BN == 128 ? 6 : 4);
+  static constexpr int CTAS_PER_SM = BN <= 32 ? 3 : (BN == 64 ? 2 : 1);
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
 };
@@ -97,6 +100,7 @@ struct TcParams {
   float* workspace;         // [splits][tiles][BN][128] fp32 when splits > 1
   int* tickets;             // [tiles], zero before and after the launch
   int* error_flag;
+  int w_tiled;              // weights stored as contiguous [m tile][k block][128][64] tiles
 };
 
 template <int BN>
@@ -104,19 +108,29 @@ __device__ __forceinline__ void tc_epilogue_store(const TcParams& p, float* v, i
   // v: 16 consecutive tokens (n_base..) of out feature m
   if (m >= p.m_out) return;
   const float b = p.bias ? p.bias[m] : 0.f;
+  if (p.mode == OUT_ADD_F32) {
+    // read the 16 old values together (one round trip instead of sixteen), then add and store
+    float old[16];
+    float* o = (float*)p.out + (size_t)n_base * p.ldo + m;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) old[c] = c < n_valid ? o[(size_t)c * p.ldo] : 0.f;
+#pragma unroll
+    for (int c = 0; c < 16; ++c)
+      if (c < n_valid) o[(size_t)c * p.ldo] = old[c] + (v[c] + b);
+    return;
+  }
 #pragma unroll
   for (int c = 0; c < 16; ++c) {
     if (c >= n_valid) break;
     const float val = v[c] + b;
     const size_t idx = (size_t)(n_base + c) * p.ldo + m;
     if (p.mode == OUT_STORE) ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(val);
-    else if (p.mode == OUT_STORE_F32) ((float*)p.out)[idx] = val;
-    else ((float*)p.out)[idx] += val;
+    else ((float*)p.out)[idx] = val;
   }
 }
 
 template <int BN>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
   using C = TcConfig<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -137,6 +151,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int nkb = max(0, kb1 - kb0);
 
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
@@ -161,7 +177,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (i >= C::STAGES && !mbar_wait(empty_bar(s), ((i / C::STAGES) - 1) & 1, p.error_flag, 1)) break;
         mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
         const uint32_t a_dst = base + s * C::STAGE_BYTES;
-        tma_load_2d(a_dst, &map_w, (kb0 + i) * TC_BK, m0, full_bar(s));
+        if (p.w_tiled) tma_load_2d(a_dst, &map_w, 0, (blockIdx.x * kblocks + kb0 + i) * TC_BM, full_bar(s));
+        else tma_load_2d(a_dst, &map_w, (kb0 + i) * TC_BK, m0, full_bar(s));
         tma_load_2d(a_dst + C::A_BYTES, &map_x, (kb0 + i) * TC_BK, n0, full_bar(s));
       }
     }
@@ -230,10 +247,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           float v[16];
 #pragma unroll
           for (int c = 0; c < 16; ++c) v[c] = 0.f;
-          for (int z = 0; z < p.splits; ++z) {
-            const float* src = p.workspace + ((size_t)z * n_tiles + tile) * (BN * TC_BM);
+          // partials in split order, four splits' loads in flight at a time
+          const size_t zs = (size_t)n_tiles * (BN * TC_BM);
+          const float* src0 = p.workspace + (size_t)tile * (BN * TC_BM) + c0 * TC_BM + quad * 32 + lane;
+          int z = 0;
+          for (; z + 4 <= p.splits; z += 4) {
+            float t[4][16];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) v[c] += __ldcg(&src[(c0 + c) * TC_BM + quad * 32 + lane]);
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+              for (int c = 0; c < 16; ++c) t[u][c] = __ldcg(src0 + (z + u) * zs + c * TC_BM);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+              for (int c = 0; c < 16; ++c) v[c] += t[u][c];
+          }
+          for (; z < p.splits; ++z) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) v[c] += __ldcg(src0 + z * zs + c * TC_BM);
           }
           tc_epilogue_store<BN>(p, v, m, n0 + c0, p.n_tok - (n0 + c0));
         }
@@ -299,13 +330,18 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, d
 
 using namespace llmi;
 
-// How many k-splits a product of this shape gets (a function of the shape only).
+static int tc_bn(int n_tok) { return n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : n_tok <= 128 ? 128 : 256; }
+static int tc_ctas_per_sm(int bn) { return bn <= 32 ? 3 : (bn == 64 ? 2 : 1); }
+
+// How many k-splits a product of this shape gets (a function of the shape only): enough blocks to
+// fill every SM's resident slots once, each with at least four k-blocks to stream.
 LLMI_EXPORT int llmi_gemm_tc_splits(int n_tok, int m_out, int k) {
-  const int bn = n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : n_tok <= 128 ? 128 : 256;
+  const int bn = tc_bn(n_tok);
   const long tiles = (long)((m_out + TC_BM - 1) / TC_BM) * ((n_tok + bn - 1) / bn);
   const int kblocks = (k + TC_BK - 1) / TC_BK;
-  if (tiles >= 96 || kblocks < 8) return 1;
-  int s = (int)((148 * 2 + tiles - 1) / tiles);
+  const long slots = 148L * tc_ctas_per_sm(bn);
+  if (tiles * 2 > slots || kblocks < 8) return 1;
+  int s = (int)(slots / tiles);
   if (s > kblocks / 4) s = kblocks / 4;
   if (s > 16) s = 16;
   return s < 1 ? 1 : s;
@@ -314,7 +350,7 @@ LLMI_EXPORT int llmi_gemm_tc_splits(int n_tok, int m_out, int k) {
 // Bytes of fp32 workspace and number of int tickets the product needs (both 0 without split-K).
 LLMI_EXPORT long llmi_gemm_tc_workspace(int n_tok, int m_out, int k, int* n_tickets) {
   const int s = llmi_gemm_tc_splits(n_tok, m_out, k);
-  const int bn = n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : n_tok <= 128 ? 128 : 256;
+  const int bn = tc_bn(n_tok);
   const long tiles = (long)((m_out + TC_BM - 1) / TC_BM) * ((n_tok + bn - 1) / bn);
   if (n_tickets) *n_tickets = s > 1 ? (int)tiles : 0;
   return s > 1 ? (long)s * tiles * bn * TC_BM * 4 : 0;
@@ -322,23 +358,28 @@ LLMI_EXPORT long llmi_gemm_tc_workspace(int n_tok, int m_out, int k, int* n_tick
 
 // y[n_tok, m_out] (mode) = x[n_tok, k] · w[m_out, k]ᵀ + bias; bf16 inputs; pitches in elements.
 // Requirements (else LLMI_ERR_ALIGN): x, w 16-byte aligned; ldx, ldw multiples of 8 elements.
-LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, const float* bias, void* y, long ldy,
-                             int n_tok, int m_out, int k, int mode, float* workspace, long workspace_bytes,
+// w_tiled != 0: w is not [m_out, k] row-major but the same matrix cut into contiguous tiles,
+// [ceil(m_out/128)][ceil(k/64)][128][64] with zero padding (ldw is ignored): one weight tile is then one
+// contiguous 16 KB read, which is what a decode step's weight stream wants from HBM.
+LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, int w_tiled, const float* bias, void* y,
+                             long ldy, int n_tok, int m_out, int k, int mode, float* workspace, long workspace_bytes,
                              int* tickets, int n_tickets, int* error_flag, cudaStream_t stream) {
   if (n_tok <= 0 || m_out <= 0 || k <= 0) return LLMI_ERR_BAD_SIZE;
   if (mode < 0 || mode > 2) return LLMI_ERR_UNSUPPORTED;
-  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (ldw & 7)) return LLMI_ERR_ALIGN;
-  const int bn = n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : n_tok <= 128 ? 128 : 256;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (!w_tiled && (ldw & 7))) return LLMI_ERR_ALIGN;
+  const int bn = tc_bn(n_tok);
   int need_tickets = 0;
   const long need_ws = llmi_gemm_tc_workspace(n_tok, m_out, k, &need_tickets);
   int splits = llmi_gemm_tc_splits(n_tok, m_out, k);
   if (splits > 1 && (need_ws > workspace_bytes || need_tickets > n_tickets || !workspace || !tickets)) splits = 1;
   CUtensorMap mw, mx;
-  int rc = make_map(&mw, w, m_out, k, ldw, TC_BM);
+  const long m_tiles = (m_out + TC_BM - 1) / TC_BM, k_blocks = (k + TC_BK - 1) / TC_BK;
+  int rc = w_tiled ? make_map(&mw, w, m_tiles * k_blocks * TC_BM, TC_BK, TC_BK, TC_BM)
+                   : make_map(&mw, w, m_out, k, ldw, TC_BM);
   if (rc != LLMI_OK) return rc;
   rc = make_map(&mx, x, n_tok, k, ldx, bn);
   if (rc != LLMI_OK) return rc;
-  TcParams p{m_out, n_tok, k, y, ldy, bias, mode, splits, workspace, tickets, error_flag};
+  TcParams p{m_out, n_tok, k, y, ldy, bias, mode, splits, workspace, tickets, error_flag, w_tiled};
   dim3 grid((m_out + TC_BM - 1) / TC_BM, (n_tok + bn - 1) / bn, splits);
   if (grid.y > 65535) return LLMI_ERR_BAD_SIZE;
   switch (bn) {

@@ -16,56 +16,50 @@
 namespace llmi {
 
 constexpr int MAX_HALF = 256;
+constexpr int ROPE_WARPS = 4;
 
+// One warp per (token, head): heads 0..n_heads-1 are query heads (rotated in place), heads
+// n_heads..n_heads+n_kv-1 are key heads (rotated into the cache) together with their value heads.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(ROPE_WARPS * 32)
 rope_store_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ inv_freq, int rotary_dim,
                   const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos, PagedKV kv,
-                  T* __restrict__ k_cache, T* __restrict__ v_cache, int n_heads, int write_kv) {
-  __shared__ float cs[MAX_HALF], sn[MAX_HALF];
-  const int t = blockIdx.x;
+                  T* __restrict__ k_cache, T* __restrict__ v_cache, int n_heads, int write_kv, long n_items) {
+  const long item = (long)blockIdx.x * ROPE_WARPS + (threadIdx.x >> 5);
+  if (item >= n_items) return;
+  const int lane = threadIdx.x & 31;
+  const int per_tok = n_heads + kv.n_kv_heads;
+  const int t = (int)(item / per_tok), j = (int)(item - (long)t * per_tok);
   const int seq = tok_seq[t];
   if (seq < 0) return;
   const int pos = tok_pos[t];
-  const int hd = kv.head_dim, nkv = kv.n_kv_heads;
-  const int half = rotary_dim / 2;
-  for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    const float angle = (float)pos * inv_freq[i];
-    float s, c;
-    sincosf(angle, &s, &c);
-    cs[i] = c;
-    sn[i] = s;
-  }
-  __syncthreads();
-
+  const int hd = kv.head_dim, half = rotary_dim / 2;
   T* row = qkv + (size_t)t * ld;
-  // q heads, in place
-  for (int idx = threadIdx.x; idx < n_heads * half; idx += blockDim.x) {
-    const int h = idx / half, i = idx - h * half;
-    T* p = row + (size_t)h * hd;
-    const float a = to_f32(p[i]), b = to_f32(p[i + half]);
-    p[i] = from_f32<T>(a * cs[i] - b * sn[i]);
-    p[i + half] = from_f32<T>(b * cs[i] + a * sn[i]);
+  if (j < n_heads) {
+    T* p = row + (size_t)j * hd;
+    for (int i = lane; i < half; i += 32) {
+      float s, c;
+      sincosf((float)pos * inv_freq[i], &s, &c);
+      const float a = to_f32(p[i]), b = to_f32(p[i + half]);
+      p[i] = from_f32<T>(a * c - b * s);
+      p[i + half] = from_f32<T>(b * c + a * s);
+    }
+    return;
   }
   if (!write_kv) return;
-
-  const T* krow = row + (size_t)n_heads * hd;
-  const T* vrow = krow + (size_t)nkv * hd;
-  for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
-    const int h = idx / hd, d = idx - h * hd;
-    const size_t dst = kv_row_offset(kv, seq, pos, h) + d;
-    float kval;
-    if (d < half) {
-      kval = to_f32(krow[h * hd + d]) * cs[d] - to_f32(krow[h * hd + d + half]) * sn[d];
-    } else if (d < rotary_dim) {
-      const int i = d - half;
-      kval = to_f32(krow[h * hd + d]) * cs[i] + to_f32(krow[h * hd + i]) * sn[i];
-    } else {
-      kval = to_f32(krow[h * hd + d]);
-    }
-    k_cache[dst] = from_f32<T>(kval);
-    v_cache[dst] = vrow[h * hd + d];
+  const int h = j - n_heads;
+  const T* ksrc = row + (size_t)(n_heads + h) * hd;
+  const T* vsrc = row + (size_t)(n_heads + kv.n_kv_heads + h) * hd;
+  const size_t dst = kv_row_offset(kv, seq, pos, h);
+  for (int i = lane; i < half; i += 32) {
+    float s, c;
+    sincosf((float)pos * inv_freq[i], &s, &c);
+    const float a = to_f32(ksrc[i]), b = to_f32(ksrc[i + half]);
+    k_cache[dst + i] = from_f32<T>(a * c - b * s);
+    k_cache[dst + i + half] = from_f32<T>(b * c + a * s);
   }
+  for (int d = rotary_dim + lane; d < hd; d += 32) k_cache[dst + d] = ksrc[d];
+  for (int d = lane; d < hd; d += 32) v_cache[dst + d] = vsrc[d];
 }
 
 }  // namespace llmi
@@ -79,13 +73,17 @@ LLMI_EXPORT int llmi_rope_store(int dtype, void* qkv, long ld, const float* inv_
   if (n_tokens <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || page_size <= 0) return LLMI_ERR_BAD_SIZE;
   if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1) || rotary_dim / 2 > MAX_HALF) return LLMI_ERR_BAD_SIZE;
   PagedKV kv{seq_pages, pages_stride, page_size, n_kv_heads, head_dim};
+  const long n_items = (long)n_tokens * (n_heads + n_kv_heads);
+  const long blocks = (n_items + ROPE_WARPS - 1) / ROPE_WARPS;
+  if (blocks > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
   if (dtype == LLMI_DTYPE_F32)
-    rope_store_kernel<float><<<n_tokens, 128, 0, stream>>>((float*)qkv, ld, inv_freq, rotary_dim, tok_seq, tok_pos, kv,
-                                                           (float*)k_cache, (float*)v_cache, n_heads, write_kv);
+    rope_store_kernel<float><<<(unsigned)blocks, ROPE_WARPS * 32, 0, stream>>>(
+        (float*)qkv, ld, inv_freq, rotary_dim, tok_seq, tok_pos, kv, (float*)k_cache, (float*)v_cache, n_heads, write_kv,
+        n_items);
   else if (dtype == LLMI_DTYPE_BF16)
-    rope_store_kernel<__nv_bfloat16><<<n_tokens, 128, 0, stream>>>(
+    rope_store_kernel<__nv_bfloat16><<<(unsigned)blocks, ROPE_WARPS * 32, 0, stream>>>(
         (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, tok_seq, tok_pos, kv, (__nv_bfloat16*)k_cache,
-        (__nv_bfloat16*)v_cache, n_heads, write_kv);
+        (__nv_bfloat16*)v_cache, n_heads, write_kv, n_items);
   else
     return LLMI_ERR_BAD_DTYPE;
   return launch_status();

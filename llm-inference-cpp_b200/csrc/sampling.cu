@@ -30,9 +30,20 @@ argmax_kernel(const float* __restrict__ logits, long ld, int vocab, int32_t* __r
   const float* row = logits + (size_t)blockIdx.x * ld;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = row[i];
-    if (bi == 0x7fffffff || v > bv) { bv = v; bi = i; }  // ascending i: the first maximum stays
+  if ((vocab & 3) == 0 && (((uintptr_t)row) & 15) == 0) {
+    const float4* r4 = reinterpret_cast<const float4*>(row);
+    for (int i = threadIdx.x; i < (vocab >> 2); i += blockDim.x) {   // ascending i: the first maximum stays
+      const float4 v = r4[i];
+      if (bi == 0x7fffffff || v.x > bv) { bv = v.x; bi = 4 * i; }
+      if (v.y > bv) { bv = v.y; bi = 4 * i + 1; }
+      if (v.z > bv) { bv = v.z; bi = 4 * i + 2; }
+      if (v.w > bv) { bv = v.w; bi = 4 * i + 3; }
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float v = row[i];
+      if (bi == 0x7fffffff || v > bv) { bv = v; bi = i; }
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {

@@ -12,7 +12,12 @@ uses is reallocated (``Runtime.generation``) or when it was recorded for another
 """
 from __future__ import annotations
 
+import os
+
 import torch
+
+# LLMI_GRAPHS=0 runs every decode step launch by launch (for profilers that want single kernels).
+RECORD = os.environ.get("LLMI_GRAPHS", "1") != "0"
 
 
 def bucket(n: int) -> int:
@@ -48,7 +53,7 @@ class DecodeGraphs:
             # first time for this shape: run it plainly (this also sizes every scratch buffer), then record
             ids = sampler.launch(m.run(ctx, cache), B)
             key = (B, P, choice, id(cache), m.rt.generation, m.buffers.dev.data_ptr())
-            if key not in self.graphs:
+            if RECORD and key not in self.graphs:
                 from ..ops import kernels
                 torch.cuda.synchronize()
                 g = torch.cuda.CUDAGraph()

@@ -294,3 +294,20 @@ def test_gemm_tc_strided_input_and_refusals():
     with pytest.raises(kk.KernelError, match="aligned"):
         kk.gemm_tc(torch.empty(4, 20, device="cuda", dtype=torch.bfloat16), torch.empty(8, 20, device="cuda", dtype=torch.bfloat16),
                    torch.empty(4, 8, device="cuda"), None, kk.OUT_STORE_F32)
+
+
+@pytest.mark.parametrize("n_tok,m_out,k", [(3, 200, 72), (64, 2048, 8192), (300, 520, 136), (8, 384, 2048)])
+def test_gemm_tc_tiled_weights(n_tok, m_out, k):
+    """The same product with the weight matrix stored as contiguous 128x64 tiles."""
+    kk = K()
+    x = torch.randn(n_tok, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(m_out, k, device="cuda") * 0.05).to(torch.bfloat16)
+    tiled = kk.TiledMatrix(w)
+    assert torch.equal(tiled.dense(), w)
+    a = torch.empty(n_tok, m_out, device="cuda")
+    b = torch.empty(n_tok, m_out, device="cuda")
+    kk.gemm_tc(x, w, a, None, kk.OUT_STORE_F32)
+    kk.gemm_tc(x, tiled, b, None, kk.OUT_STORE_F32)
+    assert torch.equal(a, b)
+    assert rel(b, x.double() @ w.double().T) < 2e-5
+    kk.check_device_errors("cuda:0")
