@@ -27,7 +27,7 @@ namespace llmi {
 
 constexpr int DEC_PAGE = 64;          // positions per cache page (the cache's page size)
 constexpr int DEC_CONSUMERS = 4;      // consumer warps; each takes 16 keys of a page
-constexpr int DEC_THREADS = (DEC_CONSUMERS + 1) * 32;
+constexpr int DEC_THREADS = (DEC_CONSUMERS + 2) * 32;   // + producer warp + epilogue warp
 
 struct DecodeParams {
   const __nv_bfloat16* q;   // [tokens, >= n_heads*HD], row pitch ldq
@@ -58,7 +58,7 @@ struct DecCfg {
   static constexpr int LPR = HD / 8;          // lanes per key row (16 bytes each)
   static constexpr int RPI = 32 / LPR;        // rows per warp instruction
   static constexpr int NI = 16 / RPI;         // instructions per warp per page (16 keys per warp)
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 128 /*align*/ + 128 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 128 /*align*/ + 8 * (2 * STAGES + 4) + 64 /*barriers*/;
 };
 
 __device__ __forceinline__ void bf16x8_to_f32(const uint4& raw, float* f) {
@@ -71,9 +71,16 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4& raw, float* f) {
   }
 }
 
+struct DecItem {
+  int seq, kvh, part, n_parts, lo, pos, pg0, n_pages, tok;
+};
+
 // Work is cut into items (sequence, kv head, split).  The grid is persistent: block b takes items
-// b, b + gridDim.x, ... and its ring of stages runs on across item borders, so the copies of the
-// next item are in flight while the current item is merged and written.
+// b, b + gridDim.x, ... and its ring of stages runs on across item borders.  Four consumer warps
+// share an item's pages (16 keys of a page each); a producer warp keeps the ring full; an epilogue
+// warp takes a finished item's merged (max, sum, values) from shared memory and does the slow,
+// latency-bound part — partial to the workspace, fence, ticket, and the final merge if it drew the
+// last ticket — while the consumers are already on the next item.
 template <int HD, int G>
 __global__ void __launch_bounds__(DEC_THREADS)
 attention_decode_kernel(DecodeParams p, int n_items) {
@@ -82,55 +89,67 @@ attention_decode_kernel(DecodeParams p, int n_items) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ float s_m[DEC_CONSUMERS][G], s_l[DEC_CONSUMERS][G];
   __shared__ float s_acc[DEC_CONSUMERS][G][HD];
-  __shared__ int s_last;
+  __shared__ float r_buf[2][G][HD + 2];     // merged results on their way to the epilogue warp
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
   const uint32_t bars = base + C::STAGES * C::STAGE_BYTES;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+  auto rfull_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + b); };
+  auto rempty_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + 2 + b); };
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), DEC_CONSUMERS);
     }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(rfull_bar(b), 1);
+      mbar_init(rempty_bar(b), 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  pdl_wait();   // q and the newest cache entries come from the kernels before
 
-  // An item's page range; false if the item is empty (padding sequence, or a split outside the sequence).
-  auto item_range = [&](int item, int& seq, int& kvh, int& split, int& lo, int& pos, int& pg0, int& n_pages,
-                        int& first_split, int& n_parts) -> bool {
-    split = item % p.max_splits;
-    const int sh = item / p.max_splits;
-    kvh = sh % p.n_kv_heads;
-    seq = sh / p.n_kv_heads;
-    const int kv_len = p.seq_kv_len[seq];
-    if (kv_len <= 0) return false;
-    pos = kv_len - 1;
-    lo = (p.window > 0 && kv_len - p.window > 0) ? kv_len - p.window : 0;
-    const int first_page = lo / DEC_PAGE, last_page = pos / DEC_PAGE;
-    first_split = first_page / p.pages_per_split;
-    const int last_split = last_page / p.pages_per_split;
-    if (split < first_split || split > last_split) return false;
-    n_parts = last_split - first_split + 1;
-    pg0 = max(first_page, split * p.pages_per_split);
-    n_pages = min(last_page + 1, (split + 1) * p.pages_per_split) - pg0;
-    return true;
+  // The first non-empty item at or after `item` in this block's sequence of items (stride gridDim.x);
+  // returns n_items when there is none.  Every warp role walks the same sequence.
+  auto next_item = [&](int item, DecItem& d) -> int {
+    for (; item < n_items; item += gridDim.x) {
+      const int split = item % p.max_splits;
+      const int sh = item / p.max_splits;
+      d.kvh = sh % p.n_kv_heads;
+      d.seq = sh / p.n_kv_heads;
+      const int kv_len = p.seq_kv_len[d.seq];
+      if (kv_len <= 0) continue;                                   // padding sequence
+      d.pos = kv_len - 1;
+      d.lo = (p.window > 0 && kv_len - p.window > 0) ? kv_len - p.window : 0;
+      const int first_page = d.lo / DEC_PAGE, last_page = d.pos / DEC_PAGE;
+      const int first_split = first_page / p.pages_per_split, last_split = last_page / p.pages_per_split;
+      if (split < first_split || split > last_split) continue;     // nothing of the sequence in this split
+      d.part = split - first_split;
+      d.n_parts = last_split - first_split + 1;
+      d.pg0 = max(first_page, split * p.pages_per_split);
+      d.n_pages = min(last_page + 1, (split + 1) * p.pages_per_split) - d.pg0;
+      d.tok = p.seq_q_start[d.seq];
+      return item;
+    }
+    return n_items;
   };
 
-  int it = 0;   // pages handled so far by this block: the ring position, the same in producer and consumers
   if (warp == DEC_CONSUMERS) {
+    // ---- producer ----
     if (lane == 0) {
+      int it = 0;
+      DecItem d;
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-        int seq, kvh, split, lo, pos, pg0, n_pages, first_split, n_parts;
-        if (!item_range(item, seq, kvh, split, lo, pos, pg0, n_pages, first_split, n_parts)) continue;
-        const int32_t* pages = p.seq_pages + (size_t)seq * p.pages_stride;
-        for (int i = 0; i < n_pages; ++i, ++it) {
+      for (int item = next_item(blockIdx.x, d); item < n_items && ok; item = next_item(item + gridDim.x, d)) {
+        const int32_t* pages = p.seq_pages + (size_t)d.seq * p.pages_stride;
+        for (int i = 0; i < d.n_pages; ++i, ++it) {
           const int s = it % C::STAGES;
           if (it >= C::STAGES && !mbar_wait(empty_bar(s), ((it / C::STAGES) - 1) & 1, p.error_flag, 11)) { ok = false; break; }
-          const size_t tile = ((size_t)pages[pg0 + i] * p.n_kv_heads + kvh) * (size_t)(DEC_PAGE * HD);
+          const size_t tile = ((size_t)pages[d.pg0 + i] * p.n_kv_heads + d.kvh) * (size_t)(DEC_PAGE * HD);
           mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
           bulk_load(base + s * C::STAGE_BYTES, p.k_cache + tile, C::TILE_BYTES, full_bar(s));
           bulk_load(base + s * C::STAGE_BYTES + C::TILE_BYTES, p.v_cache + tile, C::TILE_BYTES, full_bar(s));
@@ -140,20 +159,100 @@ attention_decode_kernel(DecodeParams p, int n_items) {
     return;
   }
 
-  // consumers: lane = (row group r, 16-byte chunk c) of a key row
+  if (warp == DEC_CONSUMERS + 1) {
+    // ---- epilogue warp: items cut into several splits pass through here ----
+    int n_split_items = 0;
+    DecItem d;
+    for (int item = next_item(blockIdx.x, d); item < n_items; item = next_item(item + gridDim.x, d)) {
+      if (d.n_parts == 1) continue;
+      const int b = n_split_items & 1;
+      if (!mbar_wait(rfull_bar(b), (n_split_items >> 1) & 1, p.error_flag, 13)) return;
+      ++n_split_items;
+      float* part = p.partials + ((((size_t)d.seq * p.n_kv_heads + d.kvh) * p.max_splits + d.part) * G) * (HD + 2);
+      for (int i = lane; i < G * (HD + 2); i += 32) part[i] = (&r_buf[b][0][0])[i];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(rempty_bar(b));      // the consumers may fill this buffer again
+      __threadfence();
+      __syncwarp();
+      int last = 0;
+      if (lane == 0) last = (atomicAdd(&p.tickets[d.seq * p.n_kv_heads + d.kvh], 1) == d.n_parts - 1);
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (!last) continue;
+      __threadfence();
+      // The final merge, in split order.  Lane z holds split z's (max, sum); the weights go round by
+      // shuffle, and the values of four splits are loaded together, so the merge costs a few round
+      // trips to L2 rather than one per split.
+      const float* parts = p.partials + (((size_t)d.seq * p.n_kv_heads + d.kvh) * p.max_splits) * G * (HD + 2);
+      constexpr int DPL = (HD + 31) / 32;   // output dims per lane
+      for (int g = 0; g < G; ++g) {
+        float M = -INFINITY;
+        for (int z = lane; z < d.n_parts; z += 32) M = fmaxf(M, __ldcg(&parts[((size_t)z * G + g) * (HD + 2) + HD]));
+        M = warp_max(M);
+        float L = 0.f, A[DPL];
+#pragma unroll
+        for (int u = 0; u < DPL; ++u) A[u] = 0.f;
+        for (int z0 = 0; z0 < d.n_parts; z0 += 32) {
+          const int z = z0 + lane;
+          float wz = 0.f, lw = 0.f;
+          if (z < d.n_parts) {
+            const float* pz = parts + ((size_t)z * G + g) * (HD + 2);
+            const float mz = __ldcg(&pz[HD]);
+            wz = (mz == -INFINITY) ? 0.f : expf(mz - M);
+            lw = __ldcg(&pz[HD + 1]) * wz;
+          }
+          const int nz = min(32, d.n_parts - z0);
+          for (int j0 = 0; j0 < nz; j0 += 4) {
+            float v[4][DPL];
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              const float* pj = parts + ((size_t)(z0 + min(j0 + jj, nz - 1)) * G + g) * (HD + 2);
+#pragma unroll
+              for (int u = 0; u < DPL; ++u) v[jj][u] = (lane + 32 * u < HD) ? __ldcg(&pj[lane + 32 * u]) : 0.f;
+            }
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              const int j = min(j0 + jj, nz - 1);
+              const float w = (j0 + jj < nz) ? __shfl_sync(0xffffffffu, wz, j) : 0.f;
+              L += (j0 + jj < nz) ? __shfl_sync(0xffffffffu, lw, j) : 0.f;
+#pragma unroll
+              for (int u = 0; u < DPL; ++u) A[u] = fmaf(w, v[jj][u], A[u]);
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < DPL; ++u)
+          if (lane + 32 * u < HD)
+            p.out[(size_t)d.tok * p.ldo + (size_t)(d.kvh * G + g) * HD + lane + 32 * u] = __float2bfloat16_rn(A[u] / L);
+      }
+      __syncwarp();
+      if (lane == 0) p.tickets[d.seq * p.n_kv_heads + d.kvh] = 0;
+    }
+    return;
+  }
+
+  // ---- consumers: lane = (row group r, 16-byte chunk c) of a key row ----
   const int c = lane % C::LPR, r = lane / C::LPR;
   const int ctid = threadIdx.x;   // 0..127
+  int it = 0, n_split_items = 0;
   bool ok = true;
-  for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
-    int seq, kvh, split, lo, pos, pg0, n_pages, first_split, n_parts;
-    if (!item_range(item, seq, kvh, split, lo, pos, pg0, n_pages, first_split, n_parts)) continue;
-    const int tok = p.seq_q_start[seq];
+  DecItem d, dn;
+  int item = next_item(blockIdx.x, d);
+  uint4 q_raw[G], q_next[G];
+  if (item < n_items) {
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+      q_raw[g] = *reinterpret_cast<const uint4*>(p.q + (size_t)d.tok * p.ldq + (size_t)(d.kvh * G + g) * HD + c * 8);
+  }
+  while (item < n_items && ok) {
+    const int item_next = next_item(item + gridDim.x, dn);
+    if (item_next < n_items) {     // the next item's q is fetched while this item's pages are worked on
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+        q_next[g] = *reinterpret_cast<const uint4*>(p.q + (size_t)dn.tok * p.ldq + (size_t)(dn.kvh * G + g) * HD + c * 8);
+    }
     float q[G][8];
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(p.q + (size_t)tok * p.ldq + (size_t)(kvh * G + g) * HD + c * 8);
-      bf16x8_to_f32(raw, q[g]);
-    }
+    for (int g = 0; g < G; ++g) bf16x8_to_f32(q_raw[g], q[g]);
     float m[G], l[G], acc[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -162,12 +261,12 @@ attention_decode_kernel(DecodeParams p, int n_items) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
     }
-    for (int i = 0; i < n_pages; ++i, ++it) {
+    for (int i = 0; i < d.n_pages; ++i, ++it) {
       const int s = it % C::STAGES;
       ok = mbar_wait(full_bar(s), (it / C::STAGES) & 1, p.error_flag, 12);
       if (!ok) break;
       const uint32_t k_tile = base + s * C::STAGE_BYTES, v_tile = k_tile + C::TILE_BYTES;
-      const int page_pos0 = (pg0 + i) * DEC_PAGE;
+      const int page_pos0 = (d.pg0 + i) * DEC_PAGE;
       float sc[C::NI][G];
       float pmax[G];
 #pragma unroll
@@ -182,15 +281,15 @@ attention_decode_kernel(DecodeParams p, int n_items) {
         float kf[8];
         bf16x8_to_f32(raw, kf);
         const int kpos = page_pos0 + row;
-        const bool valid = kpos >= lo && kpos <= pos;
+        const bool valid = kpos >= d.lo && kpos <= d.pos;
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-          float d = 0.f;
+          float dot = 0.f;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) d = fmaf(q[g][e], kf[e], d);
+          for (int e = 0; e < 8; ++e) dot = fmaf(q[g][e], kf[e], dot);
 #pragma unroll
-          for (int o = 1; o < C::LPR; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-          sc[j][g] = valid ? d * p.scale : -INFINITY;
+          for (int o = 1; o < C::LPR; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+          sc[j][g] = valid ? dot * p.scale : -INFINITY;
           pmax[g] = fmaxf(pmax[g], sc[j][g]);
         }
       }
@@ -215,7 +314,7 @@ attention_decode_kernel(DecodeParams p, int n_items) {
         float vf[8];
         bf16x8_to_f32(raw, vf);
         const int kpos = page_pos0 + row;
-        if (kpos < lo || kpos > pos) {   // whatever lies outside the sequence's positions counts as zero
+        if (kpos < d.lo || kpos > d.pos) {   // whatever lies outside the sequence's positions counts as zero
 #pragma unroll
           for (int e = 0; e < 8; ++e) vf[e] = 0.f;
         }
@@ -251,10 +350,15 @@ attention_decode_kernel(DecodeParams p, int n_items) {
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");   // the four consumer warps
 
-    // merge the four consumer warps (fixed order), then either finish or leave a partial
-    float* part = p.partials + ((((size_t)seq * p.n_kv_heads + kvh) * p.max_splits + (split - first_split)) * G) * (HD + 2);
+    // merge the four consumer warps (fixed order); a whole sequence-head is written at once, a split
+    // goes to the epilogue warp
+    const int b = n_split_items & 1;
+    if (d.n_parts > 1) {
+      if (n_split_items >= 2) ok = mbar_wait(rempty_bar(b), ((n_split_items >> 1) - 1) & 1, p.error_flag, 14);
+      if (!ok) break;
+    }
     for (int idx = ctid; idx < G * HD; idx += DEC_CONSUMERS * 32) {
-      const int g = idx / HD, d = idx - g * HD;
+      const int g = idx / HD, dd = idx - g * HD;
       float M = -INFINITY;
 #pragma unroll
       for (int w = 0; w < DEC_CONSUMERS; ++w) M = fmaxf(M, s_m[w][g]);
@@ -263,45 +367,46 @@ attention_decode_kernel(DecodeParams p, int n_items) {
       for (int w = 0; w < DEC_CONSUMERS; ++w) {
         const float f = (s_m[w][g] == -INFINITY) ? 0.f : expf(s_m[w][g] - M);
         L += s_l[w][g] * f;
-        A += s_acc[w][g][d] * f;
+        A += s_acc[w][g][dd] * f;
       }
-      if (n_parts == 1) {
-        p.out[(size_t)tok * p.ldo + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(A / L);
+      if (d.n_parts == 1) {
+        p.out[(size_t)d.tok * p.ldo + (size_t)(d.kvh * G + g) * HD + dd] = __float2bfloat16_rn(A / L);
       } else {
-        part[g * (HD + 2) + d] = A;
-        if (d == 0) {
-          part[g * (HD + 2) + HD] = M;
-          part[g * (HD + 2) + HD + 1] = L;
+        r_buf[b][g][dd] = A;
+        if (dd == 0) {
+          r_buf[b][g][HD] = M;
+          r_buf[b][g][HD + 1] = L;
         }
       }
     }
-    if (n_parts > 1) {
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (ctid == 0) s_last = (atomicAdd(&p.tickets[seq * p.n_kv_heads + kvh], 1) == n_parts - 1);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (s_last) {
-        __threadfence();
-        const float* parts = p.partials + (((size_t)seq * p.n_kv_heads + kvh) * p.max_splits) * G * (HD + 2);
-        for (int idx = ctid; idx < G * HD; idx += DEC_CONSUMERS * 32) {
-          const int g = idx / HD, d = idx - g * HD;
-          float M = -INFINITY;
-          for (int z = 0; z < n_parts; ++z) M = fmaxf(M, __ldcg(&parts[((size_t)z * G + g) * (HD + 2) + HD]));
-          float L = 0.f, A = 0.f;
-          for (int z = 0; z < n_parts; ++z) {
-            const float* pz = parts + ((size_t)z * G + g) * (HD + 2);
-            const float mz = __ldcg(&pz[HD]);
-            const float f = (mz == -INFINITY) ? 0.f : expf(mz - M);
-            L += __ldcg(&pz[HD + 1]) * f;
-            A += __ldcg(&pz[d]) * f;
-          }
-          p.out[(size_t)tok * p.ldo + (size_t)(kvh * G + g) * HD + d] = __float2bfloat16_rn(A / L);
-        }
-        if (ctid == 0) p.tickets[seq * p.n_kv_heads + kvh] = 0;
-      }
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // r_buf is complete; s_m / s_acc are free again
+    if (d.n_parts > 1) {
+      if (ctid == 0) mbar_arrive(rfull_bar(b));
+      ++n_split_items;
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");   // s_m / s_acc / s_last are free for the next item
+    item = item_next;
+    d = dn;
+#pragma unroll
+    for (int g = 0; g < G; ++g) q_raw[g] = q_next[g];
   }
+}
+
+// Blocks of this kernel that fit on the device at once.
+template <int HD, int G>
+int decode_resident() {
+  using C = DecCfg<HD>;
+  static int resident = 0;
+  if (!resident) {
+    cudaFuncSetAttribute(attention_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    int per_sm = 0, sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<HD, G>, DEC_THREADS,
+                                                      C::SMEM_BYTES) != cudaSuccess || per_sm < 1)
+      per_sm = 1;
+    resident = per_sm * (sms > 0 ? sms : 148);
+  }
+  return resident;
 }
 
 template <int HD, int G>
@@ -316,19 +421,9 @@ int launch_decode(const DecodeParams& p, int n_seqs, cudaStream_t stream) {
   }
   const long n_items = (long)n_seqs * p.n_kv_heads * p.max_splits;
   if (n_items > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
-  static int resident = 0;   // blocks of this kernel that fit on the device at once
-  if (!resident) {
-    int per_sm = 0, sms = 0, dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<HD, G>, DEC_THREADS,
-                                                      C::SMEM_BYTES) != cudaSuccess || per_sm < 1)
-      per_sm = 1;
-    resident = per_sm * (sms > 0 ? sms : 148);
-  }
+  const int resident = decode_resident<HD, G>();
   const int grid = (int)(n_items < resident ? n_items : resident);
-  attention_decode_kernel<HD, G><<<grid, DEC_THREADS, C::SMEM_BYTES, stream>>>(p, (int)n_items);
-  return launch_status();
+  return launch_pdl(PDL_ATTENTION, attention_decode_kernel<HD, G>, grid, DEC_THREADS, C::SMEM_BYTES, stream, p, (int)n_items);
 }
 
 }  // namespace llmi
@@ -341,6 +436,9 @@ LLMI_EXPORT int llmi_attention_decode_supported(int head_dim, int group) {
   if (head_dim == 32) return group == 1 || group == 2 || group == 4;
   return 0;
 }
+
+// Blocks of the (head size, group) kernel that are resident on the device at once (0: no such kernel).
+LLMI_EXPORT int llmi_attention_decode_resident(int head_dim, int group);
 
 // Floats of workspace for n_seqs sequences of at most max_pages pages each.
 LLMI_EXPORT long llmi_attention_decode_workspace(int n_seqs, int n_heads, int head_dim, int max_pages,
@@ -374,4 +472,14 @@ LLMI_EXPORT int llmi_attention_decode(const void* q, long ldq, void* out, long l
   LLMI_DEC(32, 1); LLMI_DEC(32, 2); LLMI_DEC(32, 4);
 #undef LLMI_DEC
   return LLMI_ERR_UNSUPPORTED;
+}
+
+LLMI_EXPORT int llmi_attention_decode_resident(int head_dim, int group) {
+#define LLMI_DEC(HD, G) \
+  if (head_dim == HD && group == G) return decode_resident<HD, G>()
+  LLMI_DEC(64, 1); LLMI_DEC(64, 2); LLMI_DEC(64, 3); LLMI_DEC(64, 4); LLMI_DEC(64, 8);
+  LLMI_DEC(128, 1); LLMI_DEC(128, 2); LLMI_DEC(128, 3); LLMI_DEC(128, 4); LLMI_DEC(128, 8);
+  LLMI_DEC(32, 1); LLMI_DEC(32, 2); LLMI_DEC(32, 4);
+#undef LLMI_DEC
+  return 0;
 }

@@ -170,16 +170,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   uint32_t tmem_d;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_d) : "r"(tmem_slot));
 
+  pdl_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % C::STAGES;
-        if (i >= C::STAGES && !mbar_wait(empty_bar(s), ((i / C::STAGES) - 1) & 1, p.error_flag, 1)) break;
-        mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+      // The weights do not depend on the kernel before this one: their first tiles are requested at once.
+      // The activations do: they wait for it.
+      const int pre = nkb < C::STAGES ? nkb : C::STAGES;
+      auto load_w = [&](int i, int s) {
         const uint32_t a_dst = base + s * C::STAGE_BYTES;
         if (p.w_tiled) tma_load_2d(a_dst, &map_w, 0, (blockIdx.x * kblocks + kb0 + i) * TC_BM, full_bar(s));
         else tma_load_2d(a_dst, &map_w, (kb0 + i) * TC_BK, m0, full_bar(s));
-        tma_load_2d(a_dst + C::A_BYTES, &map_x, (kb0 + i) * TC_BK, n0, full_bar(s));
+      };
+      auto load_x = [&](int i, int s) {
+        tma_load_2d(base + s * C::STAGE_BYTES + C::A_BYTES, &map_x, (kb0 + i) * TC_BK, n0, full_bar(s));
+      };
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(full_bar(i), C::STAGE_BYTES);
+        load_w(i, i);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i) load_x(i, i);
+      for (int i = pre; i < nkb; ++i) {
+        const int s = i % C::STAGES;
+        if (!mbar_wait(empty_bar(s), ((i / C::STAGES) - 1) & 1, p.error_flag, 1)) break;
+        mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+        load_w(i, s);
+        load_x(i, s);
       }
     }
   } else if (warp == 1) {
@@ -208,6 +224,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int quad = warp & 3;
     const int m = m0 + quad * 32 + lane;
     const uint32_t t_base = tmem_d + ((uint32_t)(quad * 32) << 16);
+    pdl_wait();   // the output (read-modify-write), the workspace and the tickets belong to earlier kernels until now
     const bool ok = nkb > 0 ? mbar_wait(accum_bar, 0, p.error_flag, 3) : true;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int tile = blockIdx.y * gridDim.x + blockIdx.x;
@@ -322,8 +339,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, d
       return LLMI_ERR_LAUNCH;
     configured = true;
   }
-  gemm_tc_kernel<BN><<<grid, TC_THREADS, C::SMEM_BYTES, stream>>>(mw, mx, p);
-  return launch_status();
+  return launch_pdl(PDL_GEMM, gemm_tc_kernel<BN>, grid, TC_THREADS, C::SMEM_BYTES, stream, mw, mx, p);
 }
 
 }  // namespace llmi

@@ -25,6 +25,8 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32)
 rope_store_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ inv_freq, int rotary_dim,
                   const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos, PagedKV kv,
                   T* __restrict__ k_cache, T* __restrict__ v_cache, int n_heads, int write_kv, long n_items) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long item = (long)blockIdx.x * ROPE_WARPS + (threadIdx.x >> 5);
   if (item >= n_items) return;
   const int lane = threadIdx.x & 31;
@@ -77,13 +79,12 @@ LLMI_EXPORT int llmi_rope_store(int dtype, void* qkv, long ld, const float* inv_
   const long blocks = (n_items + ROPE_WARPS - 1) / ROPE_WARPS;
   if (blocks > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
   if (dtype == LLMI_DTYPE_F32)
-    rope_store_kernel<float><<<(unsigned)blocks, ROPE_WARPS * 32, 0, stream>>>(
-        (float*)qkv, ld, inv_freq, rotary_dim, tok_seq, tok_pos, kv, (float*)k_cache, (float*)v_cache, n_heads, write_kv,
-        n_items);
+    return launch_pdl(PDL_ROPE, rope_store_kernel<float>, (unsigned)blocks, ROPE_WARPS * 32, 0, stream, (float*)qkv, ld, inv_freq,
+                      rotary_dim, tok_seq, tok_pos, kv, (float*)k_cache, (float*)v_cache, n_heads, write_kv, n_items);
   else if (dtype == LLMI_DTYPE_BF16)
-    rope_store_kernel<__nv_bfloat16><<<(unsigned)blocks, ROPE_WARPS * 32, 0, stream>>>(
-        (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, tok_seq, tok_pos, kv, (__nv_bfloat16*)k_cache,
-        (__nv_bfloat16*)v_cache, n_heads, write_kv, n_items);
+    return launch_pdl(PDL_ROPE, rope_store_kernel<__nv_bfloat16>, (unsigned)blocks, ROPE_WARPS * 32, 0, stream,
+                      (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, tok_seq, tok_pos, kv, (__nv_bfloat16*)k_cache,
+                      (__nv_bfloat16*)v_cache, n_heads, write_kv, n_items);
   else
     return LLMI_ERR_BAD_DTYPE;
   return launch_status();

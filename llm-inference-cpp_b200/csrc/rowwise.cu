@@ -12,6 +12,7 @@ namespace llmi {
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids, float* __restrict__ out,
                              int width) {
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * width;
@@ -29,6 +30,8 @@ template <typename T>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ weight, T* __restrict__ out,
                                const int32_t* __restrict__ rows, int width, float eps) {
   __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   T* o = out + (size_t)r * width;
@@ -53,6 +56,8 @@ template <typename T, int VPT>
 __global__ void rmsnorm_reg_kernel(const float* __restrict__ x, const float* __restrict__ weight, T* __restrict__ out,
                                    const int32_t* __restrict__ rows, int width, float eps) {
   __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   T* o = out + (size_t)r * width;
@@ -91,6 +96,8 @@ __global__ void rmsnorm_reg_kernel(const float* __restrict__ x, const float* __r
 // gate_up is [rows, 2*inner]: gate in the first half of a row, up in the second.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inner, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t r = i / inner, c = i - r * inner;
     const float g = to_f32(gate_up[r * 2 * inner + c]);
@@ -125,13 +132,13 @@ LLMI_EXPORT int llmi_rmsnorm(int out_dtype, const float* x, const float* weight,
   const bool aligned = (width % 4 == 0) && !((uintptr_t)x & 15) && !((uintptr_t)weight & 15);
   if (aligned && width <= 4 * 2 * threads) {
     if (out_dtype == LLMI_DTYPE_F32)
-      rmsnorm_reg_kernel<float, 2><<<n_rows, threads, 0, stream>>>(x, weight, (float*)out, rows, width, eps);
+      return launch_pdl(PDL_SMALL, rmsnorm_reg_kernel<float, 2>, n_rows, threads, 0, stream, x, weight, (float*)out, rows, width, eps);
     else
-      rmsnorm_reg_kernel<__nv_bfloat16, 2><<<n_rows, threads, 0, stream>>>(x, weight, (__nv_bfloat16*)out, rows, width, eps);
+      return launch_pdl(PDL_SMALL, rmsnorm_reg_kernel<__nv_bfloat16, 2>, n_rows, threads, 0, stream, x, weight, (__nv_bfloat16*)out, rows, width, eps);
   } else if (out_dtype == LLMI_DTYPE_F32)
-    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, weight, (float*)out, rows, width, eps);
+    return launch_pdl(PDL_SMALL, rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, weight, (float*)out, rows, width, eps);
   else
-    rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, weight, (__nv_bfloat16*)out, rows, width, eps);
+    return launch_pdl(PDL_SMALL, rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, weight, (__nv_bfloat16*)out, rows, width, eps);
   return launch_status();
 }
 
@@ -141,10 +148,10 @@ LLMI_EXPORT int llmi_swiglu(int dtype, const void* gate_up, void* out, int n_row
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == LLMI_DTYPE_F32)
-    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inner, total);
+    return launch_pdl(PDL_SMALL, swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, inner, total);
   else if (dtype == LLMI_DTYPE_BF16)
-    swiglu_kernel<__nv_bfloat16>
-        <<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inner, total);
+    return launch_pdl(PDL_SMALL, swiglu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up,
+                      (__nv_bfloat16*)out, inner, total);
   else
     return LLMI_ERR_BAD_DTYPE;
   return launch_status();

@@ -27,6 +27,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, long ld, int vocab, int32_t* __restrict__ out) {
   __shared__ float best_v[32];
   __shared__ int best_i[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const float* row = logits + (size_t)blockIdx.x * ld;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
@@ -243,8 +245,7 @@ using namespace llmi;
 
 LLMI_EXPORT int llmi_argmax(const float* logits, long ld, int n_rows, int vocab, int32_t* out, cudaStream_t stream) {
   if (n_rows <= 0 || vocab <= 0) return LLMI_ERR_BAD_SIZE;
-  argmax_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, out);
-  return launch_status();
+  return launch_pdl(PDL_SMALL, argmax_kernel, n_rows, SAMPLE_THREADS, 0, stream, logits, ld, vocab, out);
 }
 
 // temperature must be > 0 (the caller maps temperature <= 0 to llmi_argmax, as the reference does).

@@ -82,7 +82,7 @@ def lib():
     if not _configured:
         for name in ("llmi_embed", "llmi_rmsnorm", "llmi_swiglu", "llmi_linear_simt", "llmi_rope_store",
                      "llmi_attention_generic", "llmi_argmax", "llmi_sample", "llmi_gemm_tc", "llmi_gemm_tc_splits",
-                     "llmi_attention_decode", "llmi_attention_decode_supported"):
+                     "llmi_attention_decode", "llmi_attention_decode_supported", "llmi_attention_decode_resident"):
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
         l.llmi_attention_decode_workspace.restype = c_long
@@ -289,7 +289,35 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, u
                                        _ptr(probs_scratch), _ptr(out), _stream()))
 
 
-DECODE_PAGES_PER_SPLIT = 8     # a split of the decode kernel covers 512 positions, whatever the batch
+DECODE_PAGES_PER_SPLIT = 8     # default split of the decode kernel: 512 positions
+
+
+_resident_cache: dict = {}
+
+
+def decode_pages_per_split(n_seqs: int, n_kv_heads: int, max_pages: int, head_dim: int = 64, group: int = 1) -> int:
+    """How many pages one work item of the decode kernel covers.
+
+    The kernel is persistent: ``resident`` blocks share the items round-robin.  The split is chosen so
+    that the last round of items is nearly full (little idle tail) while an item stays long enough
+    (at least 8 pages unless the batch is tiny) that its fixed cost — first load, merge, ticket —
+    is small beside its streaming time.  Large batches get no split at all.
+    """
+    key = (head_dim, group)
+    if key not in _resident_cache:
+        _resident_cache[key] = max(1, int(lib().llmi_attention_decode_resident(c_int(head_dim), c_int(group))))
+    resident = _resident_cache[key]
+    pairs = max(1, n_seqs * n_kv_heads)
+    best, best_score = max_pages, -1.0
+    for splits in range(1, max(1, max_pages // 4) + 1):
+        pps = -(-max_pages // splits)
+        items = pairs * -(-max_pages // pps)
+        rounds = -(-items // resident)
+        fill = items / (rounds * resident)                 # how full the rounds are
+        score = fill * pps / (pps + 2.0)                   # an item costs about two pages of streaming on top
+        if score > best_score + 1e-9:
+            best, best_score = pps, score
+    return best
 
 
 def attention_decode_supported(head_dim: int, group: int) -> bool:
@@ -335,9 +363,10 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
             and seq_pages.shape[0] * n_kv_heads <= _TcScratch.N_ATTN_TICKETS
             and attention_decode_supported(head_dim, n_heads // n_kv_heads)):
         S, P = seq_pages.shape
-        partials = rt.scratch("attn_partials", (attention_decode_workspace(S, n_heads, head_dim, P),), torch.float32)
+        pps = decode_pages_per_split(S, n_kv_heads, P, head_dim, n_heads // n_kv_heads)
+        partials = rt.scratch("attn_partials", (attention_decode_workspace(S, n_heads, head_dim, P, pps),), torch.float32)
         attention_decode(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_kv_len, ctx.seq_q_start, n_heads, n_kv_heads,
-                         head_dim, scale, window, partials)
+                         head_dim, scale, window, partials, pps)
         return
     attention_generic(qkv, out, k_cache, v_cache, ctx.tok_seq, ctx.tok_pos, seq_pages, page_size, n_heads,
                       n_kv_heads, head_dim, scale, window)

@@ -311,3 +311,48 @@ def test_gemm_tc_tiled_weights(n_tok, m_out, k):
     assert torch.equal(a, b)
     assert rel(b, x.double() @ w.double().T) < 2e-5
     kk.check_device_errors("cuda:0")
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(32, 32, 64), (15, 5, 64), (8, 2, 128), (8, 8, 32), (16, 2, 64)])
+@pytest.mark.parametrize("pps,window", [(1, 0), (4, 0), (64, 0), (2, 200)])
+def test_attention_decode_ragged(nh, nkv, hd, pps, window):
+    """The split decode kernel against the plain formula: sequences of very different lengths, a
+    padding sequence, scrambled pages, poisoned cache outside the sequences, several split sizes."""
+    kk = K()
+    rng = np.random.default_rng(1)
+    lens = [1, 64, 65, 700, 0, 129, 1000]
+    P = 16
+    n_pages = 48
+    kc, vc = paged(n_pages, nkv, hd, "bfloat16")
+    perm = rng.permutation(n_pages).tolist()
+    pages = torch.full((len(lens), P), -1, dtype=torch.int32)
+    store = []
+    for s_, n in enumerate(lens):
+        keys = torch.randn(max(n, 1), nkv, hd).to(torch.bfloat16)
+        vals = torch.randn(max(n, 1), nkv, hd).to(torch.bfloat16)
+        store.append((keys, vals))
+        for pg_i in range((n + 63) // 64):
+            pg = perm.pop()
+            pages[s_, pg_i] = pg
+            m_ = min(64, n - 64 * pg_i)
+            kc[pg, :, :m_] = keys[64 * pg_i:64 * pg_i + m_].transpose(0, 1).cuda()
+            vc[pg, :, :m_] = vals[64 * pg_i:64 * pg_i + m_].transpose(0, 1).cuda()
+    S = len(lens)
+    q = torch.randn(S, (nh + 2 * nkv) * hd).to(torch.bfloat16).cuda()
+    out = torch.full((S, nh * hd), 7.0, device="cuda", dtype=torch.bfloat16)
+    kvlen = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    qstart = torch.arange(S, dtype=torch.int32, device="cuda")
+    part = torch.empty(kk.attention_decode_workspace(S, nh, hd, P, pps), device="cuda")
+    scale = 1 / math.sqrt(hd)
+    for _ in range(2):          # twice: the tickets must come back to zero
+        kk.attention_decode(q, out, kc, vc, pages.cuda(), kvlen, qstart, nh, nkv, hd, scale, window, part, pps)
+    kk.check_device_errors("cuda:0")
+    assert int(kk.tc_scratch("cuda:0").attn_tickets.abs().sum()) == 0
+    for s_, n in enumerate(lens):
+        if n == 0:
+            assert (out[s_] == 7.0).all()          # a padding sequence is not touched
+            continue
+        keys, vals = store[s_]
+        ref = plain_attention_rows(q[s_, :nh * hd].double().cpu().numpy().reshape(nh, hd), keys[:n].double().numpy(),
+                                   vals[:n].double().numpy(), nh // nkv, scale, window)
+        assert rel(out[s_].reshape(nh, hd), torch.from_numpy(ref)) < 1e-2, (s_, n)
