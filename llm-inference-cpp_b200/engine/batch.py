@@ -192,6 +192,7 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
     ctx.max_q_len = max(len(s.tokens) for s in seqs)
     ctx.max_kv_len = max_kv
     ctx.decode = decode
+    ctx.n_q_blocks = sum((len(s.tokens) + 127) // 128 for s in seqs)     # 128-query blocks of the prompt kernel
     ctx.h2d_bytes = cur * 4
 
     def view(name):

@@ -82,7 +82,8 @@ def lib():
     if not _configured:
         for name in ("llmi_embed", "llmi_rmsnorm", "llmi_swiglu", "llmi_linear_simt", "llmi_rope_store",
                      "llmi_attention_generic", "llmi_argmax", "llmi_sample", "llmi_gemm_tc", "llmi_gemm_tc_splits",
-                     "llmi_attention_decode", "llmi_attention_decode_supported", "llmi_attention_decode_resident"):
+                     "llmi_attention_decode", "llmi_attention_decode_supported", "llmi_attention_decode_resident",
+                     "llmi_attention_prefill", "llmi_attention_prefill_supported"):
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
         l.llmi_attention_decode_workspace.restype = c_long
@@ -349,6 +350,29 @@ def attention_decode_workspace(n_seqs: int, n_heads: int, head_dim: int, max_pag
                                                      c_int(pages_per_split)))
 
 
+def attention_prefill_supported(head_dim: int) -> bool:
+    return bool(lib().llmi_attention_prefill_supported(c_int(head_dim)))
+
+
+def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_q_start, seq_kv_len,
+                      n_blocks: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+    """Causal attention of the prompts of a step over their cache pages (bf16, head size 64 or 128, page 64).
+
+    ``seq_q_start`` [n_seqs + 1] are the sequences' offsets into the step's tokens, ``seq_kv_len`` their
+    lengths after the step, ``n_blocks`` the sum over sequences of ceil(tokens / 128).
+    """
+    _need_cuda(q, out, k_cache, v_cache, seq_pages, seq_q_start, seq_kv_len)
+    S = seq_pages.shape[0]
+    assert q.dtype == out.dtype == k_cache.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    assert k_cache.shape[-2] == 64 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    sc = tc_scratch(q.device)
+    _check("attention_prefill", lib().llmi_attention_prefill(
+        _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
+        c_long(k_cache.shape[0]), _ptr(seq_pages), c_int(seq_pages.stride(0)), _ptr(seq_q_start), _ptr(seq_kv_len),
+        c_int(S), c_int(n_blocks), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window),
+        _ptr(sc.error), _stream()))
+
+
 _FORCE_GENERIC_ATTENTION = __import__("os").environ.get("LLMI_ATTENTION", "") == "generic"
 
 
@@ -356,8 +380,8 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
               n_kv_heads: int, head_dim: int, scale: float, window: int = 0, rt=None) -> None:
     """Attention of a step's tokens over the cache; q is the first n_heads*head_dim columns of ``qkv``.
 
-    A decode step in bf16 with a head size the split kernel has goes to it; everything else (the
-    32-bit path, prefill for now, other head sizes) goes to the generic kernel.
+    In bf16, a decode step goes to the split kernel and a prompt step to the flash kernel when they
+    have the head size; everything else (the 32-bit path, other head sizes) goes to the generic kernel.
     """
     if (ctx.decode and qkv.dtype == torch.bfloat16 and page_size == 64 and rt is not None and not _FORCE_GENERIC_ATTENTION
             and seq_pages.shape[0] * n_kv_heads <= _TcScratch.N_ATTN_TICKETS
@@ -367,6 +391,11 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
         partials = rt.scratch("attn_partials", (attention_decode_workspace(S, n_heads, head_dim, P, pps),), torch.float32)
         attention_decode(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_kv_len, ctx.seq_q_start, n_heads, n_kv_heads,
                          head_dim, scale, window, partials, pps)
+        return
+    if (not ctx.decode and qkv.dtype == torch.bfloat16 and page_size == 64 and not _FORCE_GENERIC_ATTENTION
+            and attention_prefill_supported(head_dim)):
+        attention_prefill(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_q_start, ctx.seq_kv_len, ctx.n_q_blocks,
+                          n_heads, n_kv_heads, head_dim, scale, window)
         return
     attention_generic(qkv, out, k_cache, v_cache, ctx.tok_seq, ctx.tok_pos, seq_pages, page_size, n_heads,
                       n_kv_heads, head_dim, scale, window)

@@ -356,3 +356,53 @@ def test_attention_decode_ragged(nh, nkv, hd, pps, window):
         ref = plain_attention_rows(q[s_, :nh * hd].double().cpu().numpy().reshape(nh, hd), keys[:n].double().numpy(),
                                    vals[:n].double().numpy(), nh // nkv, scale, window)
         assert rel(out[s_].reshape(nh, hd), torch.from_numpy(ref)) < 1e-2, (s_, n)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 4, 64, 0), (6, 2, 64, 0), (4, 1, 128, 0), (3, 3, 64, 100), (2, 2, 128, 70)])
+def test_attention_prefill_ragged(nh, nkv, hd, window):
+    """The flash prompt kernel against the plain formula: prompts of 1..600 tokens in one launch, one of
+    them continuing a sequence that already holds 300 positions, scrambled pages, a poisoned cache."""
+    kk = K()
+    rng = np.random.default_rng(2)
+    q_lens = [1, 127, 128, 129, 600, 200]
+    bases = [0, 0, 0, 0, 0, 300]
+    P = 16
+    n_pages = 64
+    kc, vc = paged(n_pages, nkv, hd, "bfloat16")
+    perm = rng.permutation(n_pages).tolist()
+    S = len(q_lens)
+    pages = torch.full((S, P), -1, dtype=torch.int32)
+    store, qs, starts = [], [], [0]
+    for s_, (n, b) in enumerate(zip(q_lens, bases)):
+        tot = n + b
+        keys = torch.randn(tot, nkv, hd).to(torch.bfloat16)
+        vals = torch.randn(tot, nkv, hd).to(torch.bfloat16)
+        store.append((keys, vals))
+        for pg_i in range((tot + 63) // 64):
+            pg = perm.pop()
+            pages[s_, pg_i] = pg
+            m_ = min(64, tot - 64 * pg_i)
+            kc[pg, :, :m_] = keys[64 * pg_i:64 * pg_i + m_].transpose(0, 1).cuda()
+            vc[pg, :, :m_] = vals[64 * pg_i:64 * pg_i + m_].transpose(0, 1).cuda()
+        qs.append(torch.randn(n, nh * hd).to(torch.bfloat16))
+        starts.append(starts[-1] + n)
+    T = starts[-1]
+    q = torch.zeros(T, (nh + 2 * nkv) * hd, dtype=torch.bfloat16)
+    q[:, :nh * hd] = torch.cat(qs)
+    q = q.cuda()
+    out = torch.full((T, nh * hd), 7.0, device="cuda", dtype=torch.bfloat16)
+    qstart = torch.tensor(starts, dtype=torch.int32, device="cuda")
+    kvlen = torch.tensor([n + b for n, b in zip(q_lens, bases)], dtype=torch.int32, device="cuda")
+    n_blocks = sum((n + 127) // 128 for n in q_lens)
+    scale = 1 / math.sqrt(hd)
+    kk.attention_prefill(q, out, kc, vc, pages.cuda(), qstart, kvlen, n_blocks, nh, nkv, hd, scale, window)
+    kk.check_device_errors("cuda:0")
+    assert torch.isfinite(out.float()).all()
+    for s_, (n, b) in enumerate(zip(q_lens, bases)):
+        keys, vals = store[s_]
+        for row in sorted(set([0, n // 2, n - 1, min(n - 1, 63), min(n - 1, 64)])):
+            pos = b + row
+            ref = plain_attention_rows(qs[s_][row].double().numpy().reshape(nh, hd), keys[:pos + 1].double().numpy(),
+                                       vals[:pos + 1].double().numpy(), nh // nkv, scale, window)
+            got = out[starts[s_] + row].reshape(nh, hd)
+            assert rel(got, torch.from_numpy(ref)) < 1.5e-2, (s_, row)
