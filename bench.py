@@ -180,6 +180,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run one part only and print its numbers (for profiling one kernel class; not a bench line)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -200,6 +202,16 @@ def main():
     t0 = time.time()
     model = L.random_model(cfg, seed=0, dtype="bfloat16", on_device=True)
     weight_bytes = model.weight_bytes()
+
+    if args.only == "prefill":
+        pre_ms = prefill_run(model, PREFILL_TOKENS, iters=3)
+        print(json.dumps({"only": "prefill", "ms": round(pre_ms, 3), "tokens": PREFILL_TOKENS, "layers": args.layers}))
+        return 0
+    if args.only == "decode":
+        ms, launches, *_ = decode_run(model, args.batch, args.context, steps, warmup)
+        print(json.dumps({"only": "decode", "ms_per_step": round(ms, 4), "batch": args.batch, "layers": args.layers,
+                          "gpu_launches": launches}))
+        return 0
 
     clocks = ClockSampler()
     ms, launches, _, _, cache_bytes = decode_run(model, args.batch, args.context, steps, warmup, clocks=clocks)

@@ -32,7 +32,7 @@ constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int TC_THREADS = 192;
 
-constexpr int OUT_STORE = 0, OUT_STORE_F32 = 1, OUT_ADD_F32 = 2;
+constexpr int OUT_STORE = 0, OUT_STORE_F32 = 1, OUT_ADD_F32 = 2, OUT_SWIGLU = 3;
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile(
@@ -86,8 +86,9 @@ struct TcConfig {
   // hide each CTA's start-up behind its neighbours; large tiles are compute-bound and take the whole SM
   static constexpr int STAGES = BN <= 64 ? 4 : (BN == 128 ? 6 : 4);
   static constexpr int CTAS_PER_SM = BN <= 32 ? 3 : (BN == 64 ? 2 : 1);
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 8 * (2 * STAGES + 4) + 16 /*barriers, TMEM slot*/;
+  static constexpr int ACC_COLS = BN;                       // one accumulator: 128 lanes x BN columns of fp32
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;   // two of them, so that epilogue and MMAs overlap
 };
 
 struct TcParams {
@@ -100,12 +101,28 @@ struct TcParams {
   float* workspace;         // [splits][tiles][BN][128] fp32 when splits > 1
   int* tickets;             // [tiles], zero before and after the launch
   int* error_flag;
-  int w_tiled;              // weights stored as contiguous [m tile][k block][128][64] tiles
 };
 
+// The epilogue of one thread: v holds 16 consecutive tokens (n_base..) of out feature m.  Called by all
+// 32 lanes of a warp together (the gated mode exchanges values between neighbouring lanes).
 template <int BN>
 __device__ __forceinline__ void tc_epilogue_store(const TcParams& p, float* v, int m, int n_base, int n_valid) {
-  // v: 16 consecutive tokens (n_base..) of out feature m
+  if (p.mode == OUT_SWIGLU) {
+    // Rows come in pairs (2f: gate of feature f, 2f+1: up of feature f), so neighbouring lanes hold the
+    // two halves of silu(gate) * up (src/model/transformer.cpp:290; src/model/kernels.cpp:148).  The even
+    // lane finishes tokens 0..7 of the pair, the odd lane tokens 8..15.
+    const bool is_gate = (m & 1) == 0;
+    __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)n_base * p.ldo + (m >> 1);
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      const float other = __shfl_xor_sync(0xffffffffu, v[c], 1);
+      if ((c < 8) == is_gate && c < n_valid && m < p.m_out) {
+        const float g = is_gate ? v[c] : other, u = is_gate ? other : v[c];
+        o[(size_t)c * p.ldo] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+      }
+    }
+    return;
+  }
   if (m >= p.m_out) return;
   const float b = p.bias ? p.bias[m] : 0.f;
   if (p.mode == OUT_ADD_F32) {
@@ -129,26 +146,33 @@ __device__ __forceinline__ void tc_epilogue_store(const TcParams& p, float* v, i
   }
 }
 
+// Work is cut into units (m tile, n tile, k split); `n_units` of them, m fastest.  The grid is
+// persistent: block b takes units b, b + gridDim.x, ...  The ring of stages runs on across units,
+// and the accumulator is double-buffered in TMEM, so the epilogue of one unit (TMEM -> registers ->
+// global) overlaps the loads and MMAs of the next.
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p,
+               int m_tiles, int n_tiles) {
   using C = TcConfig<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bars = base + C::STAGES * C::STAGE_BYTES;          // full[STAGES], empty[STAGES], accum, tmem slot
+  const uint32_t bars = base + C::STAGES * C::STAGE_BYTES;   // full[S], empty[S], acc_full[2], acc_empty[2], tmem slot
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
-  const uint32_t accum_bar = bars + 8u * (2 * C::STAGES);
-  const uint32_t tmem_slot = accum_bar + 8u;
+  auto acc_full = [&](int b) { return bars + 8u * (2 * C::STAGES + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (2 * C::STAGES + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (2 * C::STAGES + 4);
   __shared__ int s_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * BN;
   const int kblocks = (p.k + TC_BK - 1) / TC_BK;
   const int per = (kblocks + p.splits - 1) / p.splits;
-  const int kb0 = blockIdx.z * per;
-  const int kb1 = min(kblocks, kb0 + per);
-  const int nkb = max(0, kb1 - kb0);
+  const int n_out_tiles = m_tiles * n_tiles;
+  const int n_units = n_out_tiles * p.splits;
+  // A block with a single unit needs one accumulator; with several it takes two and alternates.
+  const int acc_bufs = n_units > (int)gridDim.x ? 2 : 1;
+  const uint32_t tmem_cols = (uint32_t)(acc_bufs * BN < 32 ? 32 : acc_bufs * BN);
 
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
@@ -157,11 +181,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 4);   // the four epilogue warps
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(C::TMEM_COLS));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(tmem_cols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -170,77 +197,149 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   uint32_t tmem_d;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_d) : "r"(tmem_slot));
 
+  // unit -> (m tile, n tile, first k block, number of k blocks)
+  auto unit_of = [&](int u, int& mt, int& nt, int& z, int& kb0, int& nkb) {
+    const int tile = u % n_out_tiles;
+    z = u / n_out_tiles;
+    mt = tile % m_tiles;
+    nt = tile / m_tiles;
+    kb0 = z * per;
+    nkb = max(0, min(kblocks, kb0 + per) - kb0);
+  };
+
   pdl_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
-      // The weights do not depend on the kernel before this one: their first tiles are requested at once.
-      // The activations do: they wait for it.
-      const int pre = nkb < C::STAGES ? nkb : C::STAGES;
-      auto load_w = [&](int i, int s) {
-        const uint32_t a_dst = base + s * C::STAGE_BYTES;
-        if (p.w_tiled) tma_load_2d(a_dst, &map_w, 0, (blockIdx.x * kblocks + kb0 + i) * TC_BM, full_bar(s));
-        else tma_load_2d(a_dst, &map_w, (kb0 + i) * TC_BK, m0, full_bar(s));
-      };
-      auto load_x = [&](int i, int s) {
-        tma_load_2d(base + s * C::STAGE_BYTES + C::A_BYTES, &map_x, (kb0 + i) * TC_BK, n0, full_bar(s));
-      };
-      for (int i = 0; i < pre; ++i) {
-        mbar_expect_tx(full_bar(i), C::STAGE_BYTES);
-        load_w(i, i);
+      // ---- TMA producer ----
+      // The weights do not depend on the kernel before this one: the weight tiles of the first stages are
+      // requested at once.  The activations do: their tiles follow after pdl_wait().
+      int total = 0;
+      for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+        int mt, nt, z, kb0, nkb;
+        unit_of(u, mt, nt, z, kb0, nkb);
+        total += nkb;
       }
-      pdl_wait();
-      for (int i = 0; i < pre; ++i) load_x(i, i);
-      for (int i = pre; i < nkb; ++i) {
-        const int s = i % C::STAGES;
-        if (!mbar_wait(empty_bar(s), ((i / C::STAGES) - 1) & 1, p.error_flag, 1)) break;
-        mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
-        load_w(i, s);
-        load_x(i, s);
+      const int ahead = total < C::STAGES ? total : C::STAGES;   // k blocks requested before the wait
+      int xk[C::STAGES], xn[C::STAGES];
+      int it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+        int mt, nt, z, kb0, nkb;
+        unit_of(u, mt, nt, z, kb0, nkb);
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % C::STAGES;
+          if (it >= C::STAGES && !mbar_wait(empty_bar(s), ((it / C::STAGES) - 1) & 1, p.error_flag, 1)) { ok = false; break; }
+          mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+          const uint32_t a_dst = base + s * C::STAGE_BYTES;
+          tma_load_2d(a_dst, &map_w, (kb0 + i) * TC_BK, mt * TC_BM, full_bar(s));
+          if (it < ahead) {
+            xk[s] = (kb0 + i) * TC_BK;
+            xn[s] = nt * BN;
+            if (it == ahead - 1) {
+              pdl_wait();
+              for (int j = 0; j < ahead; ++j)
+                tma_load_2d(base + j * C::STAGE_BYTES + C::A_BYTES, &map_x, xk[j], xn[j], full_bar(j));
+            }
+          } else {
+            tma_load_2d(a_dst + C::A_BYTES, &map_x, (kb0 + i) * TC_BK, nt * BN, full_bar(s));
+          }
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      // ---- MMA issuer ----
       // instruction descriptor: D fp32, A and B bf16, both K-major, N = BN, M = 128
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+      int it = 0, j = 0;
       bool ok = true;
-      for (int i = 0; i < nkb && ok; ++i) {
-        const int s = i % C::STAGES;
-        ok = mbar_wait(full_bar(s), (i / C::STAGES) & 1, p.error_flag, 2);
-        if (!ok) break;
+      for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++j) {
+        int mt, nt, z, kb0, nkb;
+        unit_of(u, mt, nt, z, kb0, nkb);
+        const int b = j & (acc_bufs - 1);
+        if (j >= acc_bufs && !mbar_wait(acc_empty(b), ((j / acc_bufs) - 1) & 1, p.error_flag, 4)) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = base + s * C::STAGE_BYTES;
-        const uint64_t a_desc = umma_desc(a_addr), b_desc = umma_desc(a_addr + C::A_BYTES);
+        const uint32_t d_addr = tmem_d + (uint32_t)(b * C::ACC_COLS);
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % C::STAGES;
+          ok = mbar_wait(full_bar(s), (it / C::STAGES) & 1, p.error_flag, 2);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = base + s * C::STAGE_BYTES;
+          const uint64_t a_desc = umma_desc(a_addr), b_desc = umma_desc(a_addr + C::A_BYTES);
 #pragma unroll
-        for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
-          // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
-          umma_bf16(tmem_d, a_desc + 2 * k4, b_desc + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+          for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
+            // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
+            umma_bf16(d_addr, a_desc + 2 * k4, b_desc + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));
         }
-        umma_commit(empty_bar(s));
+        if (ok) umma_commit(acc_full(b));
       }
-      umma_commit(accum_bar);
     }
   } else {
-    // epilogue warps: TMEM lane quadrant = warp % 4
+    // ---- epilogue warps: TMEM lane quadrant = warp % 4 ----
     const int quad = warp & 3;
-    const int m = m0 + quad * 32 + lane;
-    const uint32_t t_base = tmem_d + ((uint32_t)(quad * 32) << 16);
     pdl_wait();   // the output (read-modify-write), the workspace and the tickets belong to earlier kernels until now
-    const bool ok = nkb > 0 ? mbar_wait(accum_bar, 0, p.error_flag, 3) : true;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-    const int n_tiles = gridDim.x * gridDim.y;
-    if (p.splits == 1) {
-      if (ok) {
+    int j = 0;
+    for (int u = blockIdx.x; u < n_units; u += gridDim.x, ++j) {
+      int mt, nt, z, kb0, nkb;
+      unit_of(u, mt, nt, z, kb0, nkb);
+      const int b = j & (acc_bufs - 1);
+      const uint32_t acc_parity = (uint32_t)(j / acc_bufs) & 1u;
+      const int m = mt * TC_BM + quad * 32 + lane;
+      const int n0 = nt * BN;
+      const uint32_t t_base = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * C::ACC_COLS);
+      const int tile = nt * m_tiles + mt;
+      if (p.splits == 1 && p.mode == OUT_ADD_F32) {
+        // Residual add: the old values are fetched one 16-token chunk ahead of the accumulator reads, so
+        // that their round trip to L2 overlaps the chunk before (and, for the first chunk, the MMAs).
+        const int nch = (min(BN, p.n_tok - n0) + 15) / 16;
+        const bool row_ok = m < p.m_out;
+        const float bias = (p.bias && row_ok) ? p.bias[m] : 0.f;
+        float* o = (float*)p.out + (size_t)n0 * p.ldo + m;
+        float nxt[16];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) nxt[c] = (row_ok && n0 + c < p.n_tok) ? o[(size_t)c * p.ldo] : 0.f;
+        if (!mbar_wait(acc_full(b), acc_parity, p.error_flag, 3)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int ci = 0; ci < nch; ++ci) {
+          float cur[16], v[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) cur[c] = nxt[c];
+          if (ci + 1 < nch) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              nxt[c] = (row_ok && n0 + (ci + 1) * 16 + c < p.n_tok) ? o[(size_t)((ci + 1) * 16 + c) * p.ldo] : 0.f;
+          }
+          tmem_ld16(t_base + ci * 16, v);
+          if (ci == nch - 1) {   // the last read of this accumulator: hand it back
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(b));
+          }
+#pragma unroll
+          for (int c = 0; c < 16; ++c)
+            if (row_ok && n0 + ci * 16 + c < p.n_tok) o[(size_t)(ci * 16 + c) * p.ldo] = cur[c] + (v[c] + bias);
+        }
+        continue;
+      }
+      if (!mbar_wait(acc_full(b), acc_parity, p.error_flag, 3)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (p.splits == 1) {
         for (int c0 = 0; c0 < BN; c0 += 16) {
           if (n0 + c0 >= p.n_tok) break;
           float v[16];
           tmem_ld16(t_base + c0, v);
+          if (c0 + 16 >= BN || n0 + c0 + 16 >= p.n_tok) {   // the last read of this accumulator: hand it back
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(b));
+          }
           tc_epilogue_store<BN>(p, v, m, n0 + c0, p.n_tok - (n0 + c0));
         }
-      }
-    } else {
-      float* ws = p.workspace + ((size_t)blockIdx.z * n_tiles + tile) * (BN * TC_BM);
-      if (ok) {
+      } else {
+        float* ws = p.workspace + ((size_t)z * n_out_tiles + tile) * (BN * TC_BM);
         for (int c0 = 0; c0 < BN; c0 += 16) {
           if (n0 + c0 >= p.n_tok) break;
           float v[16];
@@ -252,47 +351,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
           for (int c = 0; c < 16; ++c) ws[(c0 + c) * TC_BM + quad * 32 + lane] = v[c];
         }
-      }
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
-      if (threadIdx.x == 64) s_last = (atomicAdd(&p.tickets[tile], 1) == p.splits - 1);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (s_last) {
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty(b));
         __threadfence();
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-          if (n0 + c0 >= p.n_tok) break;
-          float v[16];
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+        if (threadIdx.x == 64) s_last = (atomicAdd(&p.tickets[tile], 1) == p.splits - 1);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool last = s_last != 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // s_last may be rewritten by the next unit
+        if (last) {
+          __threadfence();
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            if (n0 + c0 >= p.n_tok) break;
+            float v[16];
 #pragma unroll
-          for (int c = 0; c < 16; ++c) v[c] = 0.f;
-          // partials in split order, four splits' loads in flight at a time
-          const size_t zs = (size_t)n_tiles * (BN * TC_BM);
-          const float* src0 = p.workspace + (size_t)tile * (BN * TC_BM) + c0 * TC_BM + quad * 32 + lane;
-          int z = 0;
-          for (; z + 4 <= p.splits; z += 4) {
-            float t[4][16];
+            for (int c = 0; c < 16; ++c) v[c] = 0.f;
+            // partials in split order, four splits' loads in flight at a time
+            const size_t zs = (size_t)n_out_tiles * (BN * TC_BM);
+            const float* src0 = p.workspace + (size_t)tile * (BN * TC_BM) + c0 * TC_BM + quad * 32 + lane;
+            int zz = 0;
+            for (; zz + 4 <= p.splits; zz += 4) {
+              float t[4][16];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+              for (int q = 0; q < 4; ++q)
 #pragma unroll
-              for (int c = 0; c < 16; ++c) t[u][c] = __ldcg(src0 + (z + u) * zs + c * TC_BM);
+                for (int c = 0; c < 16; ++c) t[q][c] = __ldcg(src0 + (zz + q) * zs + c * TC_BM);
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
+              for (int q = 0; q < 4; ++q)
 #pragma unroll
-              for (int c = 0; c < 16; ++c) v[c] += t[u][c];
+                for (int c = 0; c < 16; ++c) v[c] += t[q][c];
+            }
+            for (; zz < p.splits; ++zz) {
+#pragma unroll
+              for (int c = 0; c < 16; ++c) v[c] += __ldcg(src0 + zz * zs + c * TC_BM);
+            }
+            tc_epilogue_store<BN>(p, v, m, n0 + c0, p.n_tok - (n0 + c0));
           }
-          for (; z < p.splits; ++z) {
-#pragma unroll
-            for (int c = 0; c < 16; ++c) v[c] += __ldcg(src0 + z * zs + c * TC_BM);
-          }
-          tc_epilogue_store<BN>(p, v, m, n0 + c0, p.n_tok - (n0 + c0));
+          if (threadIdx.x == 64) p.tickets[tile] = 0;
         }
-        if (threadIdx.x == 64) p.tickets[tile] = 0;
       }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(C::TMEM_COLS));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(tmem_cols));
   }
 }
 
@@ -331,7 +435,8 @@ static int make_map(CUtensorMap* map, const void* ptr, long rows, long k, long l
 }
 
 template <int BN>
-static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, dim3 grid, cudaStream_t stream) {
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int m_tiles, int n_tiles,
+                     cudaStream_t stream) {
   using C = TcConfig<BN>;
   static bool configured = false;
   if (!configured) {
@@ -339,7 +444,10 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, d
       return LLMI_ERR_LAUNCH;
     configured = true;
   }
-  return launch_pdl(PDL_GEMM, gemm_tc_kernel<BN>, grid, TC_THREADS, C::SMEM_BYTES, stream, mw, mx, p);
+  const long n_units = (long)m_tiles * n_tiles * p.splits;
+  const long resident = 148L * C::CTAS_PER_SM;
+  const int grid = (int)(n_units < resident ? n_units : resident);
+  return launch_pdl(PDL_GEMM, gemm_tc_kernel<BN>, grid, TC_THREADS, C::SMEM_BYTES, stream, mw, mx, p, m_tiles, n_tiles);
 }
 
 }  // namespace llmi
@@ -373,36 +481,34 @@ LLMI_EXPORT long llmi_gemm_tc_workspace(int n_tok, int m_out, int k, int* n_tick
 }
 
 // y[n_tok, m_out] (mode) = x[n_tok, k] · w[m_out, k]ᵀ + bias; bf16 inputs; pitches in elements.
+// mode 3 (gated): w's rows alternate gate and up rows of a feed-forward, y is [n_tok, m_out / 2] bf16 and
+// receives silu(gate) * up.
 // Requirements (else LLMI_ERR_ALIGN): x, w 16-byte aligned; ldx, ldw multiples of 8 elements.
-// w_tiled != 0: w is not [m_out, k] row-major but the same matrix cut into contiguous tiles,
-// [ceil(m_out/128)][ceil(k/64)][128][64] with zero padding (ldw is ignored): one weight tile is then one
-// contiguous 16 KB read, which is what a decode step's weight stream wants from HBM.
-LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, int w_tiled, const float* bias, void* y,
-                             long ldy, int n_tok, int m_out, int k, int mode, float* workspace, long workspace_bytes,
+LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, const float* bias, void* y, long ldy,
+                             int n_tok, int m_out, int k, int mode, float* workspace, long workspace_bytes,
                              int* tickets, int n_tickets, int* error_flag, cudaStream_t stream) {
   if (n_tok <= 0 || m_out <= 0 || k <= 0) return LLMI_ERR_BAD_SIZE;
-  if (mode < 0 || mode > 2) return LLMI_ERR_UNSUPPORTED;
-  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (!w_tiled && (ldw & 7))) return LLMI_ERR_ALIGN;
+  if (mode < 0 || mode > 3) return LLMI_ERR_UNSUPPORTED;
+  if (mode == OUT_SWIGLU && ((m_out & 1) || bias)) return LLMI_ERR_UNSUPPORTED;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (ldw & 7)) return LLMI_ERR_ALIGN;
   const int bn = tc_bn(n_tok);
   int need_tickets = 0;
   const long need_ws = llmi_gemm_tc_workspace(n_tok, m_out, k, &need_tickets);
   int splits = llmi_gemm_tc_splits(n_tok, m_out, k);
   if (splits > 1 && (need_ws > workspace_bytes || need_tickets > n_tickets || !workspace || !tickets)) splits = 1;
   CUtensorMap mw, mx;
-  const long m_tiles = (m_out + TC_BM - 1) / TC_BM, k_blocks = (k + TC_BK - 1) / TC_BK;
-  int rc = w_tiled ? make_map(&mw, w, m_tiles * k_blocks * TC_BM, TC_BK, TC_BK, TC_BM)
-                   : make_map(&mw, w, m_out, k, ldw, TC_BM);
+  int rc = make_map(&mw, w, m_out, k, ldw, TC_BM);
   if (rc != LLMI_OK) return rc;
   rc = make_map(&mx, x, n_tok, k, ldx, bn);
   if (rc != LLMI_OK) return rc;
-  TcParams p{m_out, n_tok, k, y, ldy, bias, mode, splits, workspace, tickets, error_flag, w_tiled};
-  dim3 grid((m_out + TC_BM - 1) / TC_BM, (n_tok + bn - 1) / bn, splits);
-  if (grid.y > 65535) return LLMI_ERR_BAD_SIZE;
+  TcParams p{m_out, n_tok, k, y, ldy, bias, mode, splits, workspace, tickets, error_flag};
+  const int m_tiles = (m_out + TC_BM - 1) / TC_BM, n_tiles = (n_tok + bn - 1) / bn;
+  if ((long)m_tiles * n_tiles * splits > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
   switch (bn) {
-    case 16: return launch_tc<16>(mw, mx, p, grid, stream);
-    case 32: return launch_tc<32>(mw, mx, p, grid, stream);
-    case 64: return launch_tc<64>(mw, mx, p, grid, stream);
-    case 128: return launch_tc<128>(mw, mx, p, grid, stream);
-    default: return launch_tc<256>(mw, mx, p, grid, stream);
+    case 16: return launch_tc<16>(mw, mx, p, m_tiles, n_tiles, stream);
+    case 32: return launch_tc<32>(mw, mx, p, m_tiles, n_tiles, stream);
+    case 64: return launch_tc<64>(mw, mx, p, m_tiles, n_tiles, stream);
+    case 128: return launch_tc<128>(mw, mx, p, m_tiles, n_tiles, stream);
+    default: return launch_tc<256>(mw, mx, p, m_tiles, n_tiles, stream);
   }
 }

@@ -18,6 +18,7 @@ from . import library
 OUT_STORE = 0        # y (compute type) = x·Wᵀ
 OUT_STORE_F32 = 1    # y (fp32) = x·Wᵀ
 OUT_ADD_F32 = 2      # y (fp32) += x·Wᵀ
+OUT_SWIGLU = 3       # y (compute type) = silu(gate)·up, W's rows alternating gate and up rows (tensor-core kernel only)
 
 _ERRORS = {
     -1: "unsupported element type",
@@ -178,53 +179,22 @@ def gemm_tc_eligible(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
 
 
-class TiledMatrix:
-    """A bf16 weight matrix [out, in] stored as contiguous 128x64 tiles, [out tiles][in blocks][128][64],
-    zero-padded: the layout the tensor-core product streams best (one tile = one 16 KB read)."""
-
-    def __init__(self, w: torch.Tensor):
-        assert w.dtype == torch.bfloat16 and w.dim() == 2
-        self.shape = tuple(w.shape)
-        m, k = w.shape
-        mt, kb = (m + 127) // 128, (k + 63) // 64
-        if mt * 128 != m or kb * 64 != k:
-            padded = torch.zeros(mt * 128, kb * 64, dtype=w.dtype, device=w.device)
-            padded[:m, :k] = w
-            w = padded
-        self.tiles = w.view(mt, 128, kb, 64).permute(0, 2, 1, 3).contiguous()
-        self.dtype = torch.bfloat16
-        self.device = self.tiles.device
-
-    def numel(self):
-        return self.tiles.numel()
-
-    def element_size(self):
-        return 2
-
-    def dense(self) -> torch.Tensor:
-        mt, kb = self.tiles.shape[:2]
-        return self.tiles.permute(0, 2, 1, 3).reshape(mt * 128, kb * 64)[:self.shape[0], :self.shape[1]]
-
-
-def gemm_tc(x: torch.Tensor, w, out: torch.Tensor, bias: torch.Tensor | None = None,
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
             mode: int = OUT_STORE) -> None:
-    """out (mode) x·wᵀ + bias on the tcgen05 tensor cores; bf16 inputs, fp32 accumulation.
-    ``w`` is a plain [out, in] tensor or a :class:`TiledMatrix`."""
-    tiled = isinstance(w, TiledMatrix)
-    wt = w.tiles if tiled else w
-    _need_cuda(x, wt, out, bias)
+    """out (mode) x·wᵀ + bias on the tcgen05 tensor cores; bf16 inputs, fp32 accumulation."""
+    _need_cuda(x, w, out, bias)
     M, K = x.shape
     N = w.shape[0]
-    assert w.shape[1] == K and out.shape == (M, N) and x.stride(1) == 1 and out.stride(1) == 1
-    assert tiled or w.stride(1) == 1
-    assert out.dtype == (torch.bfloat16 if mode == OUT_STORE else torch.float32)
+    assert w.shape[1] == K and out.shape == (M, N // 2 if mode == OUT_SWIGLU else N)
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    assert out.dtype == (torch.bfloat16 if mode in (OUT_STORE, OUT_SWIGLU) else torch.float32)
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == N
     sc = tc_scratch(x.device)
     _check("gemm_tc", lib().llmi_gemm_tc(
-        _ptr(x), c_long(x.stride(0)), _ptr(wt), c_long(0 if tiled else w.stride(0)), c_int(1 if tiled else 0), _ptr(bias),
-        _ptr(out), c_long(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(mode), _ptr(sc.workspace),
-        c_long(sc.WORKSPACE_BYTES), _ptr(sc.tickets), c_int(sc.N_TICKETS), _ptr(sc.error), _stream()))
+        _ptr(x), c_long(x.stride(0)), _ptr(w), c_long(w.stride(0)), _ptr(bias), _ptr(out), c_long(out.stride(0)),
+        c_int(M), c_int(N), c_int(K), c_int(mode), _ptr(sc.workspace), c_long(sc.WORKSPACE_BYTES), _ptr(sc.tickets),
+        c_int(sc.N_TICKETS), _ptr(sc.error), _stream()))
 
 
 _FORCE_SIMT = __import__("os").environ.get("LLMI_LINEAR", "") == "simt"
@@ -233,9 +203,7 @@ _FORCE_SIMT = __import__("os").environ.get("LLMI_LINEAR", "") == "simt"
 def linear(x, w, out, bias=None, mode: int = OUT_STORE) -> None:
     """The matrix product of the step: the tensor-core kernel for bf16 operands it can take (16-byte
     aligned rows), the fp32 FMA kernel for the 32-bit path and for everything else."""
-    if isinstance(w, TiledMatrix):
-        gemm_tc(x, w, out, bias, mode)
-    elif not _FORCE_SIMT and gemm_tc_eligible(x, w):
+    if not _FORCE_SIMT and gemm_tc_eligible(x, w):
         gemm_tc(x, w, out, bias, mode)
     else:
         linear_simt(x, w, out, bias, mode)

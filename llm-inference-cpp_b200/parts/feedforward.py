@@ -22,7 +22,14 @@ class SwiGLU:
     def __init__(self, spec, tensors, rt, **_):
         self.rt = rt
         self.width, self.inner = int(spec.params["width"]), int(spec.params["inner"])
-        self.w_gate_up = rt.to_compute(torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0))
+        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        # The tensor-core product can finish silu(gate)·up itself when gate and up rows alternate;
+        # otherwise the rows are [gate; up] and a gating kernel follows the product.
+        self.fused_gate = rt.dtype == torch.bfloat16 and self.width % 8 == 0 and not kernels._FORCE_SIMT
+        if self.fused_gate:
+            self.w_gate_up = rt.to_compute(torch.stack([gate, up], dim=1).reshape(2 * self.inner, self.width))
+        else:
+            self.w_gate_up = rt.to_compute(torch.cat([gate, up], dim=0))
         self.w_down = rt.to_compute(tensors["down_proj.weight"])
 
     def weight_bytes(self) -> int:
@@ -30,8 +37,13 @@ class SwiGLU:
 
     def forward(self, h, x, ctx) -> None:
         T = h.shape[0]
-        gate_up = self.rt.scratch("ffn_gate_up", (T, 2 * self.inner))
-        kernels.linear(h, self.w_gate_up, gate_up)
         act = self.rt.scratch("ffn_act", (T, self.inner))
-        kernels.swiglu(gate_up, act)
+        if self.fused_gate and kernels.gemm_tc_eligible(h, self.w_gate_up):
+            kernels.gemm_tc(h, self.w_gate_up, act, None, kernels.OUT_SWIGLU)
+        else:
+            if self.fused_gate:
+                raise kernels.KernelError("swiglu: activations are not aligned for the tensor-core product")
+            gate_up = self.rt.scratch("ffn_gate_up", (T, 2 * self.inner))
+            kernels.linear(h, self.w_gate_up, gate_up)
+            kernels.swiglu(gate_up, act)
         kernels.linear(act, self.w_down, x, None, kernels.OUT_ADD_F32)

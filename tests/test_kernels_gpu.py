@@ -296,23 +296,6 @@ def test_gemm_tc_strided_input_and_refusals():
                    torch.empty(4, 8, device="cuda"), None, kk.OUT_STORE_F32)
 
 
-@pytest.mark.parametrize("n_tok,m_out,k", [(3, 200, 72), (64, 2048, 8192), (300, 520, 136), (8, 384, 2048)])
-def test_gemm_tc_tiled_weights(n_tok, m_out, k):
-    """The same product with the weight matrix stored as contiguous 128x64 tiles."""
-    kk = K()
-    x = torch.randn(n_tok, k, device="cuda").to(torch.bfloat16)
-    w = (torch.randn(m_out, k, device="cuda") * 0.05).to(torch.bfloat16)
-    tiled = kk.TiledMatrix(w)
-    assert torch.equal(tiled.dense(), w)
-    a = torch.empty(n_tok, m_out, device="cuda")
-    b = torch.empty(n_tok, m_out, device="cuda")
-    kk.gemm_tc(x, w, a, None, kk.OUT_STORE_F32)
-    kk.gemm_tc(x, tiled, b, None, kk.OUT_STORE_F32)
-    assert torch.equal(a, b)
-    assert rel(b, x.double() @ w.double().T) < 2e-5
-    kk.check_device_errors("cuda:0")
-
-
 @pytest.mark.parametrize("nh,nkv,hd", [(32, 32, 64), (15, 5, 64), (8, 2, 128), (8, 8, 32), (16, 2, 64)])
 @pytest.mark.parametrize("pps,window", [(1, 0), (4, 0), (64, 0), (2, 200)])
 def test_attention_decode_ragged(nh, nkv, hd, pps, window):
@@ -406,3 +389,19 @@ def test_attention_prefill_ragged(nh, nkv, hd, window):
                                        vals[:pos + 1].double().numpy(), nh // nkv, scale, window)
             got = out[starts[s_] + row].reshape(nh, hd)
             assert rel(got, torch.from_numpy(ref)) < 1.5e-2, (s_, row)
+
+
+@pytest.mark.parametrize("n_tok,inner,k", [(1, 100, 72), (8, 8192, 2048), (70, 176, 64), (300, 320, 120), (2048, 512, 256)])
+def test_gemm_tc_gated_epilogue(n_tok, inner, k):
+    """silu(gate)·up finished inside the product, rows alternating gate and up; with and without split-K."""
+    kk = K()
+    x = torch.randn(n_tok, k, device="cuda").to(torch.bfloat16)
+    gate = (torch.randn(inner, k, device="cuda") * 0.1).to(torch.bfloat16)
+    up = (torch.randn(inner, k, device="cuda") * 0.1).to(torch.bfloat16)
+    w = torch.stack([gate, up], dim=1).reshape(2 * inner, k).contiguous()
+    out = torch.full((n_tok, inner), float("nan"), device="cuda", dtype=torch.bfloat16)
+    kk.gemm_tc(x, w, out, None, kk.OUT_SWIGLU)
+    g = x.double() @ gate.double().T
+    u = x.double() @ up.double().T
+    assert rel(out, g / (1 + torch.exp(-g)) * u) < 8e-3
+    kk.check_device_errors("cuda:0")
