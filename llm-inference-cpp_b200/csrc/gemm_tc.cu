@@ -114,12 +114,13 @@ __device__ __forceinline__ void tc_epilogue_store(const TcParams& p, float* v, i
     const bool is_gate = (m & 1) == 0;
     __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)n_base * p.ldo + (m >> 1);
 #pragma unroll
-    for (int c = 0; c < 16; ++c) {
-      const float other = __shfl_xor_sync(0xffffffffu, v[c], 1);
-      if ((c < 8) == is_gate && c < n_valid && m < p.m_out) {
-        const float g = is_gate ? v[c] : other, u = is_gate ? other : v[c];
-        o[(size_t)c * p.ldo] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
-      }
+    for (int c = 0; c < 8; ++c) {
+      // the even lane sends its gate of token c+8 and gets the up of token c; the odd lane the reverse
+      const float recv = __shfl_xor_sync(0xffffffffu, is_gate ? v[c + 8] : v[c], 1);
+      const float g = is_gate ? v[c] : recv, u = is_gate ? recv : v[c + 8];
+      const int tok = is_gate ? c : c + 8;
+      if (tok < n_valid && m < p.m_out)
+        o[(size_t)tok * p.ldo] = __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * u);   // bf16 result: fast exp and divide suffice
     }
     return;
   }

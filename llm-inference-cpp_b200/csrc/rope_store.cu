@@ -64,6 +64,63 @@ rope_store_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ inv_fr
   for (int d = lane; d < hd; d += 32) v_cache[dst + d] = vsrc[d];
 }
 
+// The same for whole-head rotation with head_dim % 4 == 0: one thread per two neighbouring pairs, so that
+// every access is a pair of elements (4 bytes in bf16) and a prompt of thousands of tokens moves at
+// memory speed.
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+  static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ void store(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+};
+template <> struct Pair<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float2 v) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y);
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_store_vec_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ inv_freq, const int32_t* __restrict__ tok_seq,
+                      const int32_t* __restrict__ tok_pos, PagedKV kv, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                      int n_heads, int write_kv, long n_items) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long item = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= n_items) return;
+  const int hd = kv.head_dim, half = hd / 2, per_head = half / 2;
+  const int per_tok = (n_heads + kv.n_kv_heads) * per_head;
+  const int t = (int)(item / per_tok);
+  const int rest = (int)(item - (long)t * per_tok);
+  const int j = rest / per_head, i = (rest - j * per_head) * 2;    // head j, pairs i and i+1
+  const int seq = tok_seq[t];
+  if (seq < 0) return;
+  const int pos = tok_pos[t];
+  float s0, c0, s1, c1;
+  sincosf((float)pos * inv_freq[i], &s0, &c0);
+  sincosf((float)pos * inv_freq[i + 1], &s1, &c1);
+  T* row = qkv + (size_t)t * ld;
+  if (j < n_heads) {
+    T* p = row + (size_t)j * hd;
+    const float2 a = Pair<T>::load(p + i), b = Pair<T>::load(p + i + half);
+    Pair<T>::store(p + i, make_float2(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1));
+    Pair<T>::store(p + i + half, make_float2(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1));
+    return;
+  }
+  if (!write_kv) return;
+  const int h = j - n_heads;
+  const T* ksrc = row + (size_t)(n_heads + h) * hd;
+  const T* vsrc = row + (size_t)(n_heads + kv.n_kv_heads + h) * hd;
+  const size_t dst = kv_row_offset(kv, seq, pos, h);
+  const float2 a = Pair<T>::load(ksrc + i), b = Pair<T>::load(ksrc + i + half);
+  Pair<T>::store(k_cache + dst + i, make_float2(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1));
+  Pair<T>::store(k_cache + dst + i + half, make_float2(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1));
+  Pair<T>::store(v_cache + dst + i, Pair<T>::load(vsrc + i));
+  Pair<T>::store(v_cache + dst + i + half, Pair<T>::load(vsrc + i + half));
+}
+
 }  // namespace llmi
 
 using namespace llmi;
@@ -75,6 +132,19 @@ LLMI_EXPORT int llmi_rope_store(int dtype, void* qkv, long ld, const float* inv_
   if (n_tokens <= 0 || n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || page_size <= 0) return LLMI_ERR_BAD_SIZE;
   if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1) || rotary_dim / 2 > MAX_HALF) return LLMI_ERR_BAD_SIZE;
   PagedKV kv{seq_pages, pages_stride, page_size, n_kv_heads, head_dim};
+  const size_t esz = dtype == LLMI_DTYPE_F32 ? 4 : 2;
+  const bool pair_aligned = !(((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache) & (2 * esz - 1)) && !(ld & 1);
+  if (rotary_dim == head_dim && head_dim % 4 == 0 && pair_aligned && (dtype == LLMI_DTYPE_F32 || dtype == LLMI_DTYPE_BF16)) {
+    const long n_vec = (long)n_tokens * (n_heads + n_kv_heads) * (head_dim / 4);
+    const long vblocks = (n_vec + 255) / 256;
+    if (vblocks > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
+    if (dtype == LLMI_DTYPE_F32)
+      return launch_pdl(PDL_ROPE, rope_store_vec_kernel<float>, (unsigned)vblocks, 256, 0, stream, (float*)qkv, ld, inv_freq,
+                        tok_seq, tok_pos, kv, (float*)k_cache, (float*)v_cache, n_heads, write_kv, n_vec);
+    return launch_pdl(PDL_ROPE, rope_store_vec_kernel<__nv_bfloat16>, (unsigned)vblocks, 256, 0, stream, (__nv_bfloat16*)qkv,
+                      ld, inv_freq, tok_seq, tok_pos, kv, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads,
+                      write_kv, n_vec);
+  }
   const long n_items = (long)n_tokens * (n_heads + n_kv_heads);
   const long blocks = (n_items + ROPE_WARPS - 1) / ROPE_WARPS;
   if (blocks > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;

@@ -116,6 +116,10 @@ def build(verbose: bool = True) -> str:
     if r.returncode != 0:
         raise KernelLibraryError(f"link failed:\n{r.stdout}\n{r.stderr}")
     os.replace(tmp, path)
+    for name in os.listdir(os.path.dirname(out_dir)):      # builds of older sources are of no use any more
+        stale = os.path.join(os.path.dirname(out_dir), name)
+        if stale != out_dir and os.path.isdir(stale) and len(name) == 16:
+            shutil.rmtree(stale, ignore_errors=True)
     if verbose:
         _say(f"built {LIB_NAME} in {time.time() - t0:.0f} s")
     return path
