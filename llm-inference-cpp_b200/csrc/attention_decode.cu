@@ -483,3 +483,75 @@ LLMI_EXPORT int llmi_attention_decode_resident(int head_dim, int group) {
 #undef LLMI_DEC
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// The same decode attention for callers that cannot allocate device memory (see llmi_no_alloc.h).
+// Its scratch — the per-split partial results, the tickets and an error word — lives in the array
+// below, which every GPU that loads this library holds until the process exits.
+
+namespace {
+
+constexpr long STATIC_PARTIALS_FLOATS = 1L << 20;   // 4 MiB of partial results
+constexpr int STATIC_TICKETS = 1 << 14;             // 64 KiB of tickets
+constexpr int STATIC_MAX_DEVICES = 64;
+
+struct DecodeStaticScratch {
+  float partials[STATIC_PARTIALS_FLOATS];
+  int tickets[STATIC_TICKETS];
+  int error;
+};
+
+static __device__ __align__(256) DecodeStaticScratch g_decode_static_scratch;
+
+// The device address of the array, per device.  In host code the name g_decode_static_scratch is only a
+// stand-in for the symbol, not an address a kernel could use: the address comes from cudaGetSymbolAddress,
+// asked once per device with that device current.
+DecodeStaticScratch* g_decode_static_ptr[STATIC_MAX_DEVICES] = {};
+
+}  // namespace
+
+LLMI_EXPORT int llmi_attention_decode_static(const void* q, long ldq, void* out, long ldo, const void* k_cache,
+                                             const void* v_cache, const int32_t* seq_pages, int pages_stride,
+                                             const int32_t* seq_kv_len, const int32_t* seq_q_start, int n_seqs,
+                                             int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                                             int max_pages, int pages_per_split, int* error_out, cudaStream_t stream) {
+  if (n_seqs <= 0 || n_heads <= 0 || n_kv_heads <= 0 || max_pages <= 0 || pages_per_split <= 0) return LLMI_ERR_BAD_SIZE;
+  if (n_heads % n_kv_heads) return LLMI_ERR_BAD_SIZE;
+  const int group = n_heads / n_kv_heads;
+  if (!llmi_attention_decode_supported(head_dim, group)) return LLMI_ERR_UNSUPPORTED;
+  if (((uintptr_t)q & 15) || (ldq & 7) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15)) return LLMI_ERR_ALIGN;
+  // the built-in scratch has a fixed size: a problem that needs more is refused, never truncated
+  if (llmi_attention_decode_workspace(n_seqs, n_heads, head_dim, max_pages, pages_per_split) > STATIC_PARTIALS_FLOATS ||
+      (long)n_seqs * n_kv_heads > STATIC_TICKETS)
+    return LLMI_ERR_STATIC_SCRATCH;
+
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= STATIC_MAX_DEVICES) return LLMI_ERR_DRIVER;
+  if (!g_decode_static_ptr[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_decode_static_scratch) != cudaSuccess || !ptr) return LLMI_ERR_DRIVER;
+    g_decode_static_ptr[dev] = (DecodeStaticScratch*)ptr;
+  }
+  DecodeStaticScratch* sc = g_decode_static_ptr[dev];
+  // The array keeps what the last call left.  The tickets of this call's sequences and the error word must
+  // start at zero (a call that was cut short may have left them otherwise); the partials are written before
+  // they are read and need no clearing.
+  if (cudaMemsetAsync(sc->tickets, 0, sizeof(int) * (size_t)n_seqs * n_kv_heads, stream) != cudaSuccess ||
+      cudaMemsetAsync(&sc->error, 0, sizeof(int), stream) != cudaSuccess)
+    return LLMI_ERR_LAUNCH;
+  const int splits = (max_pages + pages_per_split - 1) / pages_per_split;
+  DecodeParams p{(const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)k_cache,
+                 (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads, scale,
+                 window, pages_per_split, splits, sc->partials, sc->tickets, &sc->error};
+  int rc = LLMI_ERR_UNSUPPORTED;
+#define LLMI_DEC(HD, G) \
+  if (head_dim == HD && group == G) rc = launch_decode<HD, G>(p, n_seqs, stream)
+  LLMI_DEC(64, 1); LLMI_DEC(64, 2); LLMI_DEC(64, 3); LLMI_DEC(64, 4); LLMI_DEC(64, 8);
+  LLMI_DEC(128, 1); LLMI_DEC(128, 2); LLMI_DEC(128, 3); LLMI_DEC(128, 4); LLMI_DEC(128, 8);
+  LLMI_DEC(32, 1); LLMI_DEC(32, 2); LLMI_DEC(32, 4);
+#undef LLMI_DEC
+  if (rc != LLMI_OK) return rc;
+  if (error_out && cudaMemcpyAsync(error_out, &sc->error, sizeof(int), cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
+    return LLMI_ERR_LAUNCH;
+  return LLMI_OK;
+}

@@ -23,6 +23,7 @@
 #define LLMI_ERR_ALIGN (-4)
 #define LLMI_ERR_UNSUPPORTED (-5)
 #define LLMI_ERR_DRIVER (-6)
+#define LLMI_ERR_STATIC_SCRATCH (-7)  // the problem needs more scratch than a built-in array holds
 
 #define LLMI_EXPORT extern "C" __attribute__((visibility("default")))
 
