@@ -1,0 +1,283 @@
+// y = x · Wᵀ for a handful of tokens (decode at small batch): a weight-streaming product.
+//
+// Same operation as the reference's matmul (src/model/kernels.cpp:97-113; W is [out, in]) and as gemm_tc.cu,
+// for the case where it is nothing but a read of W from HBM: 1..32 tokens.  The big kernel's 128-row weight
+// tiles leave too few blocks for such products unless k is split across blocks, and the cross-block reduce,
+// the TMEM allocation and the ticket cost more than the product itself (a 8 MB weight matrix is 1.2 us of
+// HBM time).  Here a block owns 16 output rows over the WHOLE k range, so nothing crosses blocks:
+//
+//   * a producer warp streams W[16 rows, 256 k] and x[tokens, 256 k] by TMA (128-byte swizzle) into a ring
+//     of shared-memory stages — 72 KB in flight per block, three blocks per SM;
+//   * four consumer warps each take one 64-wide k slice of every stage: ldmatrix + mma.sync m16n8k16
+//     (bf16 in, fp32 accumulators in registers: 16 rows x 8 tokens per tile);
+//   * at the end of a row tile the four partial sums are added in warp order through shared memory and
+//     the epilogue (bias, store / fp32 store / residual add / silu(gate)·up on interleaved rows) writes
+//     token-major output.
+// Blocks are persistent over row tiles and the ring runs on across tiles.  The k order of the additions is
+// fixed (it does not depend on the number of tokens), and programmatic dependent launch lets the first
+// weight tiles be requested before the kernel that produces x has finished.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace llmi {
+
+constexpr int SK_ROWS = 16;          // output rows per tile
+constexpr int SK_BK = 256;           // k per stage: four 64-wide slices, one per consumer warp
+constexpr int SK_STAGES = 6;
+constexpr int SK_CONSUMERS = 4;
+constexpr int SK_THREADS = (SK_CONSUMERS + 1) * 32;
+
+constexpr int SK_STORE = 0, SK_STORE_F32 = 1, SK_ADD_F32 = 2, SK_SWIGLU = 3;
+
+struct SkinnyParams {
+  int m_out, n_tok, k;
+  void* out;
+  long ldo;
+  const float* bias;
+  int mode;
+  int* error_flag;
+};
+
+// One copy fetches [4 k slices][rows][64 k]: the matrix is seen as a 3-D tensor (k within a slice, row, slice).
+__device__ __forceinline__ void sk_tma(uint32_t dst, const CUtensorMap* map, int row, int slice, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(row), "r"(slice)
+      : "memory");
+}
+__device__ __forceinline__ void sk_mma(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// NT = token tiles of 8 (tokens <= 8 * NT)
+template <int NT>
+__global__ void __launch_bounds__(SK_THREADS)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, SkinnyParams p,
+                   int m_tiles) {
+  constexpr int NPAD = NT * 8;
+  constexpr int W_SLICE = SK_ROWS * 128;          // 16 rows x 64 k of bf16
+  constexpr int X_SLICE = NPAD * 128;
+  constexpr int W_BYTES = 4 * W_SLICE, X_BYTES = 4 * X_SLICE;
+  constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ float s_part[SK_CONSUMERS][32][NT * 4];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + SK_STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (SK_STAGES + s); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kstages = (p.k + SK_BK - 1) / SK_BK;
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    for (int s = 0; s < SK_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), SK_CONSUMERS);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+
+  if (warp == SK_CONSUMERS) {
+    // ---- producer ----
+    if (lane == 0) {
+      int my_tiles = 0;
+      for (int t = blockIdx.x; t < m_tiles; t += gridDim.x) ++my_tiles;
+      const int total = my_tiles * kstages;
+      const int ahead = total < SK_STAGES ? total : SK_STAGES;   // stages whose weights are requested before the wait
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < m_tiles && ok; t += gridDim.x) {
+        for (int ks = 0; ks < kstages; ++ks, ++it) {
+          const int s = it % SK_STAGES;
+          if (it >= SK_STAGES && !mbar_wait(empty_bar(s), ((it / SK_STAGES) - 1) & 1, p.error_flag, 31)) { ok = false; break; }
+          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          const uint32_t dst = base + s * STAGE_BYTES;
+          sk_tma(dst, &map_w, t * SK_ROWS, ks * 4, full_bar(s));
+          if (it < ahead) {
+            if (it == ahead - 1) {
+              pdl_wait();   // x comes from the kernel before; the weights requested so far did not have to wait for it
+              for (int j = 0; j < ahead; ++j) {
+                const int ksj = j % kstages;      // the first stages belong to this block's first tile(s)
+                sk_tma(base + j * STAGE_BYTES + W_BYTES, &map_x, 0, ksj * 4, full_bar(j));
+              }
+            }
+          } else {
+            sk_tma(dst + W_BYTES, &map_x, 0, ks * 4, full_bar(s));
+          }
+        }
+      }
+    }
+    return;
+  }
+
+  // ---- consumers ----
+  pdl_wait();   // the output (residual add) and the bias of a previous layer's step are safe to touch from here
+  int it = 0;
+  bool ok = true;
+  const int g = lane >> 2, tq = lane & 3;
+  for (int t = blockIdx.x; t < m_tiles && ok; t += gridDim.x) {
+    float acc[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
+    for (int ks = 0; ks < kstages; ++ks, ++it) {
+      const int s = it % SK_STAGES;
+      ok = mbar_wait(full_bar(s), (it / SK_STAGES) & 1, p.error_flag, 32);
+      if (!ok) break;
+      const uint32_t w_slice = base + s * STAGE_BYTES + warp * W_SLICE;
+      const uint32_t x_slice = base + s * STAGE_BYTES + W_BYTES + warp * X_SLICE;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {       // four k16 chunks of this warp's 64-wide slice
+        uint32_t a[4];
+        {
+          const int mtx = lane >> 3, r = lane & 7;
+          const int row = (mtx & 1) * 8 + r, kch = c * 2 + (mtx >> 1);
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+                       : "r"(w_slice + (uint32_t)(row * 128 + ((kch ^ (row & 7)) << 4))));
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          uint32_t b0, b1;
+          {
+            const int mtx = (lane >> 3) & 1, r = lane & 7;       // lanes 16..31 repeat the addresses of 0..15 (x2)
+            const int row = n * 8 + r, kch = c * 2 + mtx;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];"
+                         : "=r"(b0), "=r"(b1)
+                         : "r"(x_slice + (uint32_t)(row * 128 + ((kch ^ (row & 7)) << 4))));
+          }
+          sk_mma(acc[n], a, b0, b1);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar(s));
+    }
+    if (!ok) break;
+    // add the four warps' partial sums in warp order, then the epilogue, token-major
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s_part[warp][lane][n * 4 + e] = acc[n][e];
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const int m0 = t * SK_ROWS;
+    if (p.mode == SK_SWIGLU) {
+      // rows alternate gate and up: 8 features per tile
+      for (int idx = threadIdx.x; idx < NPAD * 8; idx += SK_CONSUMERS * 32) {
+        const int tok = idx >> 3, f = idx & 7;
+        if (tok >= p.n_tok || m0 + 2 * f + 1 >= p.m_out) continue;
+        float gu[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int row = 2 * f + h;                       // accumulator element (row, tok) lives in lane (row%8)*4 + (tok%8)/2
+          const int ln = (row & 7) * 4 + ((tok & 7) >> 1), e = (row >> 3) * 2 + (tok & 1), n = tok >> 3;
+          float v = 0.f;
+#pragma unroll
+          for (int w = 0; w < SK_CONSUMERS; ++w) v += s_part[w][ln][n * 4 + e];
+          gu[h] = v;
+        }
+        ((__nv_bfloat16*)p.out)[(size_t)tok * p.ldo + (m0 >> 1) + f] =
+            __float2bfloat16_rn(__fdividef(gu[0], 1.0f + __expf(-gu[0])) * gu[1]);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < NPAD * SK_ROWS; idx += SK_CONSUMERS * 32) {
+        const int tok = idx >> 4, row = idx & 15;
+        const int m = m0 + row;
+        if (tok >= p.n_tok || m >= p.m_out) continue;
+        const int ln = (row & 7) * 4 + ((tok & 7) >> 1), e = (row >> 3) * 2 + (tok & 1), n = tok >> 3;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < SK_CONSUMERS; ++w) v += s_part[w][ln][n * 4 + e];
+        if (p.bias) v += p.bias[m];
+        const size_t o = (size_t)tok * p.ldo + m;
+        if (p.mode == SK_STORE) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
+        else if (p.mode == SK_STORE_F32) ((float*)p.out)[o] = v;
+        else ((float*)p.out)[o] += v;
+      }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // s_part is free for the next tile
+  }
+}
+
+typedef CUresult (*SkEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int sk_make_map(CUtensorMap* map, const void* ptr, long rows, long k, long ld, int box_rows) {
+  static SkEncodeFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return LLMI_ERR_DRIVER;
+    fn = (SkEncodeFn)sym;
+  }
+  // (k within a 64-wide slice, row, slice): k must be a multiple of 64, so that no slice runs over a row's end
+  const cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(k / 64)};
+  const cuuint64_t strides[2] = {(cuuint64_t)ld * 2, 128};
+  const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 4};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
+             ? LLMI_OK
+             : LLMI_ERR_DRIVER;
+}
+
+template <int NT>
+static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& mx, const SkinnyParams& p, int m_tiles,
+                         cudaStream_t stream) {
+  constexpr int SMEM = SK_STAGES * (4 * SK_ROWS * 128 + 4 * NT * 8 * 128) + 1024 + 8 * 2 * SK_STAGES + 16;
+  static int resident = 0;
+  if (!resident) {
+    if (cudaFuncSetAttribute(gemm_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+      return LLMI_ERR_LAUNCH;
+    int per_sm = 0, sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_skinny_kernel<NT>, SK_THREADS, SMEM) != cudaSuccess ||
+        per_sm < 1)
+      per_sm = 1;
+    resident = per_sm * (sms > 0 ? sms : 148);
+  }
+  const int grid = m_tiles < resident ? m_tiles : resident;
+  return launch_pdl(PDL_GEMM, gemm_skinny_kernel<NT>, grid, SK_THREADS, SMEM, stream, mw, mx, p, m_tiles);
+}
+
+}  // namespace llmi
+
+using namespace llmi;
+
+// Most tokens the weight-streaming product takes.
+LLMI_EXPORT int llmi_gemm_skinny_max_tokens() { return 32; }
+
+// y[n_tok, m_out] (mode) = x[n_tok, k] · w[m_out, k]ᵀ + bias for n_tok <= 32 and k % 64 == 0; bf16 inputs; pitches in elements;
+// modes as llmi_gemm_tc (0 store, 1 fp32 store, 2 fp32 add, 3 gated with alternating gate/up rows).
+LLMI_EXPORT int llmi_gemm_skinny(const void* x, long ldx, const void* w, long ldw, const float* bias, void* y, long ldy,
+                                 int n_tok, int m_out, int k, int mode, int* error_flag, cudaStream_t stream) {
+  if (n_tok <= 0 || n_tok > 32 || m_out <= 0 || k <= 0) return LLMI_ERR_BAD_SIZE;
+  if (mode < 0 || mode > 3) return LLMI_ERR_UNSUPPORTED;
+  if (mode == SK_SWIGLU && ((m_out & 1) || bias)) return LLMI_ERR_UNSUPPORTED;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (ldw & 7)) return LLMI_ERR_ALIGN;
+  if (k % 64) return LLMI_ERR_UNSUPPORTED;   // the 3-D view of the matrices needs whole 64-wide k slices
+  const int nt = n_tok <= 8 ? 1 : (n_tok <= 16 ? 2 : 4);
+  CUtensorMap mw, mx;
+  int rc = sk_make_map(&mw, w, m_out, k, ldw, SK_ROWS);
+  if (rc != LLMI_OK) return rc;
+  rc = sk_make_map(&mx, x, n_tok, k, ldx, nt * 8);
+  if (rc != LLMI_OK) return rc;
+  SkinnyParams p{m_out, n_tok, k, y, ldy, bias, mode, error_flag};
+  const int m_tiles = (m_out + SK_ROWS - 1) / SK_ROWS;
+  if (nt == 1) return launch_skinny<1>(mw, mx, p, m_tiles, stream);
+  if (nt == 2) return launch_skinny<2>(mw, mx, p, m_tiles, stream);
+  return launch_skinny<4>(mw, mx, p, m_tiles, stream);
+}

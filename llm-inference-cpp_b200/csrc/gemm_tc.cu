@@ -28,6 +28,13 @@
 
 namespace llmi {
 
+#ifndef LLMI_TC_SMALL_STAGES
+#define LLMI_TC_SMALL_STAGES 4
+#endif
+#ifndef LLMI_TC_SMALL_CTAS
+#define LLMI_TC_SMALL_CTAS 3
+#endif
+
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int TC_THREADS = 192;
@@ -84,8 +91,8 @@ struct TcConfig {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   // few-token tiles stream weights: 4 stages per CTA and 2-3 CTAs per SM keep more bytes in flight and
   // hide each CTA's start-up behind its neighbours; large tiles are compute-bound and take the whole SM
-  static constexpr int STAGES = BN <= 64 ? 4 : (BN == 128 ? 6 : 4);
-  static constexpr int CTAS_PER_SM = BN <= 32 ? 3 : (BN == 64 ? 2 : 1);
+  static constexpr int STAGES = BN <= 32 ? LLMI_TC_SMALL_STAGES : (BN == 64 ? 4 : (BN == 128 ? 6 : 4));
+  static constexpr int CTAS_PER_SM = BN <= 32 ? LLMI_TC_SMALL_CTAS : (BN == 64 ? 2 : 1);
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 8 * (2 * STAGES + 4) + 16 /*barriers, TMEM slot*/;
   static constexpr int ACC_COLS = BN;                       // one accumulator: 128 lanes x BN columns of fp32
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;   // two of them, so that epilogue and MMAs overlap
@@ -456,7 +463,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, i
 using namespace llmi;
 
 static int tc_bn(int n_tok) { return n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : n_tok <= 128 ? 128 : 256; }
-static int tc_ctas_per_sm(int bn) { return bn <= 32 ? 3 : (bn == 64 ? 2 : 1); }
+static int tc_ctas_per_sm(int bn) { return bn <= 32 ? LLMI_TC_SMALL_CTAS : (bn == 64 ? 2 : 1); }
 
 // How many k-splits a product of this shape gets (a function of the shape only): enough blocks to
 // fill every SM's resident slots once, each with at least four k-blocks to stream.

@@ -84,7 +84,8 @@ def lib():
         for name in ("llmi_embed", "llmi_rmsnorm", "llmi_swiglu", "llmi_linear_simt", "llmi_rope_store",
                      "llmi_attention_generic", "llmi_argmax", "llmi_sample", "llmi_gemm_tc", "llmi_gemm_tc_splits",
                      "llmi_attention_decode", "llmi_attention_decode_supported", "llmi_attention_decode_resident",
-                     "llmi_attention_prefill", "llmi_attention_prefill_supported"):
+                     "llmi_attention_prefill", "llmi_attention_prefill_supported", "llmi_gemm_skinny",
+                     "llmi_gemm_skinny_max_tokens"):
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
         l.llmi_attention_decode_workspace.restype = c_long
@@ -197,14 +198,42 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Ten
         c_int(sc.N_TICKETS), _ptr(sc.error), _stream()))
 
 
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
+                mode: int = OUT_STORE) -> None:
+    """The same product for at most 32 tokens: the weight-streaming kernel (``csrc/gemm_skinny.cu``)."""
+    _need_cuda(x, w, out, bias)
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N // 2 if mode == OUT_SWIGLU else N)
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    assert out.dtype == (torch.bfloat16 if mode in (OUT_STORE, OUT_SWIGLU) else torch.float32)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == N
+    sc = tc_scratch(x.device)
+    _check("gemm_skinny", lib().llmi_gemm_skinny(
+        _ptr(x), c_long(x.stride(0)), _ptr(w), c_long(w.stride(0)), _ptr(bias), _ptr(out), c_long(out.stride(0)),
+        c_int(M), c_int(N), c_int(K), c_int(mode), _ptr(sc.error), _stream()))
+
+
+SKINNY_MAX_TOKENS = 16
 _FORCE_SIMT = __import__("os").environ.get("LLMI_LINEAR", "") == "simt"
+_NO_SKINNY = __import__("os").environ.get("LLMI_LINEAR", "") == "tc"
+
+
+def gemm_bf16(x, w, out, bias=None, mode: int = OUT_STORE) -> None:
+    """The bf16 tensor-core product: the weight-streaming kernel for a handful of tokens, the tcgen05
+    kernel for more."""
+    if x.shape[0] <= SKINNY_MAX_TOKENS and x.shape[1] % 64 == 0 and not _NO_SKINNY:
+        gemm_skinny(x, w, out, bias, mode)
+    else:
+        gemm_tc(x, w, out, bias, mode)
 
 
 def linear(x, w, out, bias=None, mode: int = OUT_STORE) -> None:
     """The matrix product of the step: the tensor-core kernel for bf16 operands it can take (16-byte
     aligned rows), the fp32 FMA kernel for the 32-bit path and for everything else."""
     if not _FORCE_SIMT and gemm_tc_eligible(x, w):
-        gemm_tc(x, w, out, bias, mode)
+        gemm_bf16(x, w, out, bias, mode)
     else:
         linear_simt(x, w, out, bias, mode)
 

@@ -39,7 +39,7 @@ class SwiGLU:
         T = h.shape[0]
         act = self.rt.scratch("ffn_act", (T, self.inner))
         if self.fused_gate and kernels.gemm_tc_eligible(h, self.w_gate_up):
-            kernels.gemm_tc(h, self.w_gate_up, act, None, kernels.OUT_SWIGLU)
+            kernels.gemm_bf16(h, self.w_gate_up, act, None, kernels.OUT_SWIGLU)
         else:
             if self.fused_gate:
                 raise kernels.KernelError("swiglu: activations are not aligned for the tensor-core product")

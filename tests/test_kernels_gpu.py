@@ -405,3 +405,35 @@ def test_gemm_tc_gated_epilogue(n_tok, inner, k):
     u = x.double() @ up.double().T
     assert rel(out, g / (1 + torch.exp(-g)) * u) < 8e-3
     kk.check_device_errors("cuda:0")
+
+
+@pytest.mark.parametrize("n_tok,m_out,k", [(1, 200, 64), (5, 64, 64), (8, 2048, 2048), (8, 130, 8192), (16, 384, 192),
+                                           (17, 6144, 2048), (32, 520, 960), (3, 16, 320)])
+def test_gemm_skinny_all_modes(n_tok, m_out, k):
+    """The weight-streaming product (at most 32 tokens) against fp64, ragged shapes, every epilogue."""
+    kk = K()
+    torch.manual_seed(n_tok * 7 + m_out + k)
+    x = torch.randn(n_tok, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(m_out, k, device="cuda") * 0.05).to(torch.bfloat16)
+    b = torch.randn(m_out, device="cuda")
+    ref = x.double() @ w.double().T
+    y32 = torch.full((n_tok, m_out), float("nan"), device="cuda")
+    kk.gemm_skinny(x, w, y32, None, kk.OUT_STORE_F32)
+    assert rel(y32, ref) < 2e-5
+    y = torch.empty(n_tok, m_out, device="cuda", dtype=torch.bfloat16)
+    kk.gemm_skinny(x, w, y, b, kk.OUT_STORE)
+    assert rel(y, ref + b.double()) < 6e-3
+    acc = torch.randn(n_tok, m_out, device="cuda")
+    before = acc.clone()
+    kk.gemm_skinny(x, w, acc, None, kk.OUT_ADD_F32)
+    assert rel(acc, before.double() + ref) < 2e-5
+    if m_out % 2 == 0:
+        gated = torch.full((n_tok, m_out // 2), float("nan"), device="cuda", dtype=torch.bfloat16)
+        kk.gemm_skinny(x, w, gated, None, kk.OUT_SWIGLU)
+        g, u = ref[:, 0::2], ref[:, 1::2]
+        assert rel(gated, g / (1 + torch.exp(-g)) * u) < 8e-3
+    # a row's value does not depend on how many tokens are in the call
+    y1 = torch.empty(1, m_out, device="cuda")
+    kk.gemm_skinny(x[n_tok - 1:], w, y1, None, kk.OUT_STORE_F32)
+    assert torch.equal(y1, y32[n_tok - 1:])
+    kk.check_device_errors("cuda:0")
