@@ -175,13 +175,17 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
 #pragma unroll
     for (int kc = 0; kc < HD / 16; ++kc) {
       const uint32_t sub = k_tile + (kc / 4) * SUB_BYTES;
-      const int col = (kc % 4) * 16 + 2 * t;
 #pragma unroll
-      for (int nc = 0; nc < 8; ++nc) {
-        uint32_t b0, b1;
-        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b0) : "r"(sub + swz(nc * 8 + g, col)));
-        asm volatile("ld.shared.b32 %0, [%1];" : "=r"(b1) : "r"(sub + swz(nc * 8 + g, col + 8)));
+      for (int nc = 0; nc < 8; nc += 2) {
+        // one ldmatrix.x4 = the B fragments (k 0-7 and k 8-15 of this chunk) of two blocks of 8 keys
+        const int mtx = lane >> 3, r = lane & 7;
+        const int row = (nc + (mtx >> 1)) * 8 + r, kch = (kc % 4) * 2 + (mtx & 1);
+        uint32_t b0, b1, b2, b3;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                     : "r"(sub + (uint32_t)(row * 128 + ((kch ^ (row & 7)) << 4))));
         mma_bf16(sc[nc], qa[kc], b0, b1);
+        mma_bf16(sc[nc + 1], qa[kc], b2, b3);
       }
     }
     // mask, running maximum, probabilities

@@ -201,3 +201,77 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     s3, _ = H.trace_whole({"a": [9] + reqs["a"][1:]})
     other = H.collect(s3, H.replay(model, s3, 256, poison=False), 90)
     assert H.rel_to_max(other["a"][1:2], whole["a"][1:2].astype(np.float64)) > 1e-4
+
+
+# -- layers with different cache needs -----------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_windowed_and_global_layers_keep_separate_cache_groups(tmp_path, dtype):
+    """A toy architecture whose first layer sees all keys and whose second sees a window of 40: the two
+    get cache groups (page pools) of their own, the windowed one gives pages back while decoding, and
+    prefill, decode and batches agree with the plain formulas."""
+    import llmi_b200 as L
+    from llmi_b200.config.registry import Architecture
+    from llmi_b200.parts import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+
+    W, NH, NKV, HD, F, V, WIN = 128, 4, 2, 64, 192, 300, 40
+
+    def toy_spec(c):
+        def layer(i, window):
+            p = f"blk{i}."
+            pos = PartSpec("rotary_half", {"head_dim": HD, "theta": 10000.0})
+            return LayerSpec("prenorm", PartSpec("rms", {"width": W, "eps": 1e-5}, p + "n1."),
+                             PartSpec("gqa", {"width": W, "n_heads": NH, "n_kv_heads": NKV, "head_dim": HD, "bias": False,
+                                              "window": window, "position": pos}, p + "attn."),
+                             PartSpec("rms", {"width": W, "eps": 1e-5}, p + "n2."),
+                             PartSpec("swiglu", {"width": W, "inner": F}, p + "ffn."))
+        return ModelSpec("ToyWindowLM", V, W, 2048, PartSpec("token_table", {"vocab": V, "width": W}, "emb."),
+                         (layer(0, 0), layer(1, WIN)), (ScheduleEntry(0), ScheduleEntry(1)),
+                         PartSpec("rms", {"width": W, "eps": 1e-5}, "final."),
+                         PartSpec("linear_head", {"vocab": V, "width": W, "tied": True}, "head."))
+
+    L.register_architecture(Architecture("ToyWindowLM", lambda root: dict(root), toy_spec), replace=True)
+    storage = torch.float32 if dtype == "float32" else torch.bfloat16
+    L.write_random_model(str(tmp_path), {"architectures": ["ToyWindowLM"]}, 3, storage)
+    model = L.load(str(tmp_path), dtype)
+    cache = model.new_cache(64 * 12)
+    assert len(cache.kv_groups) == 2 and sorted(g.request.window for g in cache.kv_groups) == [0, WIN]
+
+    w = P.read_safetensors(str(tmp_path / "model.safetensors"))
+
+    def plain(tokens):
+        T = len(tokens)
+        x = P.embedding(w["emb.weight"], tokens)
+        inv = P.rope_inv_freq(HD, 10000.0)
+        for i, window in ((0, 0), (1, WIN)):
+            p = f"blk{i}."
+            h = P.rmsnorm(x, w[p + "n1.weight"], 1e-5)
+            q = P.linear(h, w[p + "attn.q_proj.weight"]).reshape(T, NH, HD)
+            k = P.linear(h, w[p + "attn.k_proj.weight"]).reshape(T, NKV, HD)
+            v = P.linear(h, w[p + "attn.v_proj.weight"]).reshape(T, NKV, HD)
+            pos = np.arange(T)
+            a = P.attention(P.rope(q, pos, inv), P.rope(k, pos, inv), v, window).reshape(T, NH * HD)
+            x = x + P.linear(a, w[p + "attn.o_proj.weight"])
+            h = P.rmsnorm(x, w[p + "n2.weight"], 1e-5)
+            x = x + P.swiglu_ffn(h, w[p + "ffn.gate_proj.weight"], w[p + "ffn.up_proj.weight"], w[p + "ffn.down_proj.weight"])
+        return P.linear(P.rmsnorm(x, w["final.weight"], 1e-5), w["emb.weight"])
+
+    rng = np.random.default_rng(4)
+    reqs = {"a": rng.integers(0, V, 150).tolist(), "b": rng.integers(0, V, 47).tolist(), "c": rng.integers(0, V, 260).tolist()}
+    refs = {r: plain(t) for r, t in reqs.items()}
+    tol = H.TOL[dtype]
+    for steps, most in (H.trace_whole(reqs), H.trace_last_decoded(reqs, 100), H.trace_batches(reqs, 3, {"a": 30, "b": 47, "c": 129})):
+        got = H.collect(steps, H.replay(model, steps, max(most, 64 * 12)), V)
+        for r in reqs:
+            assert np.isfinite(got[r]).all()
+            assert H.rel_to_max(got[r], refs[r]) < tol, r
+    # long decoding keeps the windowed group's pages bounded: after 260 positions it holds at most 2 pages
+    s = cache.alloc_slot()
+    model.step(cache, [L.SequenceStep(s, reqs["c"][:200], [])])
+    for t in reqs["c"][200:]:
+        model.step(cache, [L.SequenceStep(s, [t], [])])
+    win_group = [g for g in cache.kv_groups if g.request.window][0]
+    all_group = [g for g in cache.kv_groups if not g.request.window][0]
+    assert sum(p >= 0 for p in win_group.pool.table(s)) <= 2 and sum(p >= 0 for p in all_group.pool.table(s)) == 5
+    cache.free_slot(s)
+    cache.check()

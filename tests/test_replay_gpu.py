@@ -164,3 +164,27 @@ def test_causality(loaded):
         cache.free_slot(s)
     assert (outs[0][:9] == outs[1][:9]).all()
     assert not (outs[0][9:] == outs[1][9:]).all()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_smollm2_135m_layer_sizes(tmp_path, dtype):
+    """Two layers at SmolLM2-135M sizes (9 heads over 3 kv heads of 64, width 576, vocabulary 49,152): the
+    kernels' fast paths for real head shapes (group of 3, vocabulary that is no power of two) against the
+    plain implementation, prompt whole and then decoded."""
+    import torch
+    import llmi_b200 as L
+    cfg = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 576, "num_attention_heads": 9,
+           "num_key_value_heads": 3, "intermediate_size": 1536, "vocab_size": 49152, "rope_theta": 100000.0,
+           "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 8192, "hidden_act": "silu",
+           "eos_token_id": 0}
+    L.write_random_model(str(tmp_path), cfg, 8, torch.float32 if dtype == "float32" else torch.bfloat16)
+    pcfg, w = P.read_model(str(tmp_path))
+    model = L.load(str(tmp_path), dtype)
+    rng = np.random.default_rng(9)
+    reqs = {"x": rng.integers(0, 49152, 150).tolist(), "y": rng.integers(0, 49152, 70).tolist()}
+    refs = {r: P.forward(pcfg, w, t) for r, t in reqs.items()}
+    steps, most = H.trace_batches(reqs, 2, {"x": 130, "y": 40})
+    got = H.collect(steps, H.replay(model, steps, most), 49152)
+    check(got, refs, dtype)
+    for r in reqs:
+        assert (got[r].argmax(1) == refs[r].argmax(1)).mean() > (0.999 if dtype == "float32" else 0.9)
