@@ -20,6 +20,14 @@
 
 namespace llmi {
 
+// 2^x on the special-function unit, one instruction (ex2.approx: relative error about 2^-22; the results
+// here end up in bf16).  exp2f() costs several such instructions.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 constexpr int PF_BM = 128;      // queries per block
 constexpr int PF_PAGE = 64;     // keys per step = the cache's page size
 constexpr int PF_THREADS = 256;
@@ -207,8 +215,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     const float mn0 = fmaxf(mrow[0], mx0), mn1 = fmaxf(mrow[1], mx1);
-    const float c0 = (mn0 == -INFINITY) ? 1.f : exp2f(mrow[0] - mn0);
-    const float c1 = (mn1 == -INFINITY) ? 1.f : exp2f(mrow[1] - mn1);
+    const float c0 = (mn0 == -INFINITY) ? 1.f : fast_exp2(mrow[0] - mn0);
+    const float c1 = (mn1 == -INFINITY) ? 1.f : fast_exp2(mrow[1] - mn1);
     mrow[0] = mn0;
     mrow[1] = mn1;
     lrow[0] *= c0;
@@ -223,10 +231,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     uint32_t pa[4][4];
 #pragma unroll
     for (int nc = 0; nc < 8; ++nc) {
-      const float p0 = (mn0 == -INFINITY) ? 0.f : exp2f(sc[nc][0] - mn0);
-      const float p1 = (mn0 == -INFINITY) ? 0.f : exp2f(sc[nc][1] - mn0);
-      const float p2 = (mn1 == -INFINITY) ? 0.f : exp2f(sc[nc][2] - mn1);
-      const float p3 = (mn1 == -INFINITY) ? 0.f : exp2f(sc[nc][3] - mn1);
+      const float p0 = (mn0 == -INFINITY) ? 0.f : fast_exp2(sc[nc][0] - mn0);
+      const float p1 = (mn0 == -INFINITY) ? 0.f : fast_exp2(sc[nc][1] - mn0);
+      const float p2 = (mn1 == -INFINITY) ? 0.f : fast_exp2(sc[nc][2] - mn1);
+      const float p3 = (mn1 == -INFINITY) ? 0.f : fast_exp2(sc[nc][3] - mn1);
       lrow[0] += p0 + p1;
       lrow[1] += p2 + p3;
       pa[nc >> 1][(nc & 1) * 2 + 0] = pack_bf16(p0, p1);

@@ -85,7 +85,7 @@ def lib():
                      "llmi_attention_generic", "llmi_argmax", "llmi_sample", "llmi_gemm_tc", "llmi_gemm_tc_splits",
                      "llmi_attention_decode", "llmi_attention_decode_supported", "llmi_attention_decode_resident",
                      "llmi_attention_prefill", "llmi_attention_prefill_supported", "llmi_gemm_skinny",
-                     "llmi_gemm_skinny_max_tokens"):
+                     "llmi_gemm_skinny_max_tokens", "llmi_attention_prefill_tc", "llmi_attention_prefill_tc_supported"):
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
         l.llmi_attention_decode_workspace.restype = c_long
@@ -370,6 +370,24 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_
         _ptr(sc.error), _stream()))
 
 
+def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_q_start, seq_kv_len,
+                         n_blocks: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
+    """The same prompt attention on the tcgen05 tensor cores (head size 64); arguments as ``attention_prefill``."""
+    _need_cuda(q, out, k_cache, v_cache, seq_pages, seq_q_start, seq_kv_len)
+    S = seq_pages.shape[0]
+    assert q.dtype == out.dtype == k_cache.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    assert k_cache.shape[-2] == 64 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    sc = tc_scratch(q.device)
+    _check("attention_prefill_tc", lib().llmi_attention_prefill_tc(
+        _ptr(q), c_long(q.stride(0)), c_long(q.shape[0]), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
+        c_long(k_cache.shape[0]), _ptr(seq_pages), c_int(seq_pages.stride(0)), _ptr(seq_q_start), _ptr(seq_kv_len),
+        c_int(S), c_int(n_blocks), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window),
+        _ptr(sc.error), _stream()))
+
+
+# Which prompt-attention kernel runs for head size 64: "mma" (mma.sync, the faster of the two as measured:
+# 114 against 142 us for a 2,048-token prompt of 32 heads) or "tc" (tcgen05, kept selectable and tested).
+_PREFILL_ATTENTION = __import__("os").environ.get("LLMI_PREFILL_ATTENTION", "mma")
 _FORCE_GENERIC_ATTENTION = __import__("os").environ.get("LLMI_ATTENTION", "") == "generic"
 
 
@@ -391,6 +409,10 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
         return
     if (not ctx.decode and qkv.dtype == torch.bfloat16 and page_size == 64 and not _FORCE_GENERIC_ATTENTION
             and attention_prefill_supported(head_dim)):
+        if head_dim == 64 and _PREFILL_ATTENTION == "tc" and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
+            attention_prefill_tc(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_q_start, ctx.seq_kv_len, ctx.n_q_blocks,
+                                 n_heads, n_kv_heads, head_dim, scale, window)
+            return
         attention_prefill(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_q_start, ctx.seq_kv_len, ctx.n_q_blocks,
                           n_heads, n_kv_heads, head_dim, scale, window)
         return

@@ -341,11 +341,15 @@ def test_attention_decode_ragged(nh, nkv, hd, pps, window):
         assert rel(out[s_].reshape(nh, hd), torch.from_numpy(ref)) < 1e-2, (s_, n)
 
 
+@pytest.mark.parametrize("kernel", ["mma", "tc"])
 @pytest.mark.parametrize("nh,nkv,hd,window", [(4, 4, 64, 0), (6, 2, 64, 0), (4, 1, 128, 0), (3, 3, 64, 100), (2, 2, 128, 70)])
-def test_attention_prefill_ragged(nh, nkv, hd, window):
+def test_attention_prefill_ragged(nh, nkv, hd, window, kernel):
     """The flash prompt kernel against the plain formula: prompts of 1..600 tokens in one launch, one of
     them continuing a sequence that already holds 300 positions, scrambled pages, a poisoned cache."""
     kk = K()
+    if kernel == "tc" and hd != 64:
+        pytest.skip("the tcgen05 prompt kernel has head size 64 only")
+    run = kk.attention_prefill_tc if kernel == "tc" else kk.attention_prefill
     rng = np.random.default_rng(2)
     q_lens = [1, 127, 128, 129, 600, 200]
     bases = [0, 0, 0, 0, 0, 300]
@@ -378,7 +382,7 @@ def test_attention_prefill_ragged(nh, nkv, hd, window):
     kvlen = torch.tensor([n + b for n, b in zip(q_lens, bases)], dtype=torch.int32, device="cuda")
     n_blocks = sum((n + 127) // 128 for n in q_lens)
     scale = 1 / math.sqrt(hd)
-    kk.attention_prefill(q, out, kc, vc, pages.cuda(), qstart, kvlen, n_blocks, nh, nkv, hd, scale, window)
+    run(q, out, kc, vc, pages.cuda(), qstart, kvlen, n_blocks, nh, nkv, hd, scale, window)
     kk.check_device_errors("cuda:0")
     assert torch.isfinite(out.float()).all()
     for s_, (n, b) in enumerate(zip(q_lens, bases)):
