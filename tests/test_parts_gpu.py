@@ -275,3 +275,49 @@ def test_windowed_and_global_layers_keep_separate_cache_groups(tmp_path, dtype):
     assert sum(p >= 0 for p in win_group.pool.table(s)) <= 2 and sum(p >= 0 for p in all_group.pool.table(s)) == 5
     cache.free_slot(s)
     cache.check()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,bias", [(4, 2, 64, False), (5, 1, 24, True), (6, 6, 32, False)])
+def test_attention_mixer_part_alone(dtype, nh, nkv, hd, bias):
+    """The grouped-query attention part by itself, on a cache of its own: a prompt in one step, then a few
+    single tokens, against the plain attention block (projections, rotation, attention, output projection)."""
+    from llmi_b200.cache import SequenceCache
+    from llmi_b200.cache.storage import CacheBinding
+    from llmi_b200.engine.batch import SequenceStep, StepBuffers, plan_step
+    from llmi_b200.parts import get_part
+    W = 136
+    r = rt(dtype)
+    names = {"q_proj.weight": (nh * hd, W), "k_proj.weight": (nkv * hd, W), "v_proj.weight": (nkv * hd, W),
+             "o_proj.weight": (W, nh * hd)}
+    if bias:
+        names.update({"q_proj.bias": (nh * hd,), "k_proj.bias": (nkv * hd,), "v_proj.bias": (nkv * hd,)})
+    t = {n: (torch.randn(*s) * 0.08).to(dtype) for n, s in names.items()}
+    pos = spec("rotary_half", {"head_dim": hd, "theta": 5000.0})
+    part = get_part("mixer", "gqa")(spec("gqa", {"width": W, "n_heads": nh, "n_kv_heads": nkv, "head_dim": hd, "bias": bias,
+                                                 "window": 0, "position": pos}), t, r)
+    req = part.cache_request()
+    cache = SequenceCache([(req, 1)], [], 256, 4096, dtype, "cuda:0")
+    binding = CacheBinding(cache.kv_groups[0], 0)
+    buffers = StepBuffers(torch.device("cuda:0"))
+    T, extra = 70, 5
+    h_all = (torch.randn(T + extra, W) * 0.5).to(dtype)
+    slot = cache.alloc_slot()
+    outs = []
+    for lo, hi in [(0, T)] + [(T + i, T + i + 1) for i in range(extra)]:
+        ctx = plan_step(cache, [SequenceStep(slot, [0] * (hi - lo), [])], 10, buffers)
+        x = torch.zeros(hi - lo, W, device="cuda")
+        part.forward(h_all[lo:hi].cuda().contiguous(), x, ctx, binding)
+        outs.append(x.cpu())
+    got = torch.cat(outs).double().numpy()
+    # the plain block without its norm: q/k/v projections (+bias), rotation, attention, output projection
+    w64 = {k: v.double().numpy() for k, v in t.items()}
+    hh = h_all.double().numpy()
+    n = T + extra
+    q = P.linear(hh, w64["q_proj.weight"], w64.get("q_proj.bias")).reshape(n, nh, hd)
+    k = P.linear(hh, w64["k_proj.weight"], w64.get("k_proj.bias")).reshape(n, nkv, hd)
+    v = P.linear(hh, w64["v_proj.weight"], w64.get("v_proj.bias")).reshape(n, nkv, hd)
+    inv = P.rope_inv_freq(hd, 5000.0)
+    a = P.attention(P.rope(q, np.arange(n), inv), P.rope(k, np.arange(n), inv), v).reshape(n, nh * hd)
+    ref = P.linear(a, w64["o_proj.weight"])
+    assert H.rel_to_max(got, ref) < (2e-5 if dtype == torch.float32 else 1.5e-2)
