@@ -66,7 +66,8 @@ class PagePool:
     become -1.
     """
 
-    def __init__(self, n_pages: int, page_size: int = PAGE_SIZE, window: int = 0):
+    def __init__(self, n_pages: int, page_size: int = PAGE_SIZE, window: int = 0, n_slots: int = 0,
+                 max_pages_per_slot: int = 0):
         if n_pages <= 0:
             raise CacheError("cache: needs at least one page")
         self.n_pages = n_pages
@@ -75,6 +76,12 @@ class PagePool:
         self._free = list(range(n_pages - 1, -1, -1))
         self._pages: dict[int, list[int]] = {}     # slot -> page ids by position (-1: released)
         self._length: dict[int, int] = {}
+        # the same tables as one int32 matrix [slot, page], kept in step with the lists, so that a step can
+        # gather the page tables of its sequences with one indexing operation
+        self.matrix = None
+        if n_slots > 0 and max_pages_per_slot > 0:
+            import numpy as np
+            self.matrix = np.full((n_slots, max_pages_per_slot), -1, dtype=np.int32)
 
     # -- slots -----------------------------------------------------------------------------
     def open(self, slot: int) -> None:
@@ -82,6 +89,8 @@ class PagePool:
             raise CacheError(f"cache: slot {slot} is already open in this group")
         self._pages[slot] = []
         self._length[slot] = 0
+        if self.matrix is not None and slot < self.matrix.shape[0]:
+            self.matrix[slot, :] = -1
 
     def close(self, slot: int) -> None:
         if slot not in self._pages:
@@ -90,6 +99,8 @@ class PagePool:
             if p >= 0:
                 self._free.append(p)
         del self._length[slot]
+        if self.matrix is not None and slot < self.matrix.shape[0]:
+            self.matrix[slot, :] = -1
 
     # -- growth ----------------------------------------------------------------------------
     def pages_needed(self, slot: int, n_new: int) -> int:
@@ -107,7 +118,10 @@ class PagePool:
         if need > len(self._free):
             raise CacheError("cache is full")
         for _ in range(need):
-            self._pages[slot].append(self._free.pop())
+            page = self._free.pop()
+            if self.matrix is not None and slot < self.matrix.shape[0] and len(self._pages[slot]) < self.matrix.shape[1]:
+                self.matrix[slot, len(self._pages[slot])] = page
+            self._pages[slot].append(page)
         self._length[slot] = base + n_new
         return base
 
@@ -117,6 +131,8 @@ class PagePool:
             if table[i] >= 0:
                 self._free.append(table[i])
                 table[i] = -1
+                if self.matrix is not None and slot < self.matrix.shape[0] and i < self.matrix.shape[1]:
+                    self.matrix[slot, i] = -1
 
     # -- views -----------------------------------------------------------------------------
     def length(self, slot: int) -> int:

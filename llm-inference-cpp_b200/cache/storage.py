@@ -44,11 +44,12 @@ class CacheBinding:
 
 
 class KVGroup:
-    def __init__(self, request: KVRequest, n_calls: int, n_pages: int, page_size: int, dtype, device):
+    def __init__(self, request: KVRequest, n_calls: int, n_pages: int, page_size: int, dtype, device, n_slots: int = 0,
+                 max_pages_per_slot: int = 0):
         self.request = request
         self.n_calls = n_calls
         self.page_size = page_size
-        self.pool = PagePool(n_pages, page_size, request.window)
+        self.pool = PagePool(n_pages, page_size, request.window, n_slots, max_pages_per_slot)
         shape = (n_calls, n_pages, request.n_kv_heads, page_size, request.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
         self.v = torch.zeros(shape, dtype=dtype, device=device)
@@ -81,9 +82,10 @@ class SequenceCache:
         n_pages = max_tokens // page_size
         self.n_slots = n_slots if n_slots is not None else n_pages
         self.slots = SlotTable(self.n_slots)
-        self.kv_groups = [KVGroup(r, n, n_pages, page_size, dtype, device) for r, n in kv_requests]
-        self.state_groups = [StateGroup(r, n, self.n_slots, device) for r, n in state_requests]
         self.max_pages_per_seq = min(pages_for(max_positions, page_size), n_pages)
+        self.kv_groups = [KVGroup(r, n, n_pages, page_size, dtype, device, self.n_slots, self.max_pages_per_seq)
+                          for r, n in kv_requests]
+        self.state_groups = [StateGroup(r, n, self.n_slots, device) for r, n in state_requests]
         self._length: dict[int, int] = {}
         self.device = device
         self.dtype = dtype

@@ -98,34 +98,39 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
     """
     if not seqs:
         raise StepError("step: no sequences")
-    seen = set()
-    for s in seqs:
-        if len(s.tokens) == 0:
-            raise StepError("step: a sequence brings no tokens")
-        if s.slot in seen:
-            raise StepError(f"step: slot {s.slot} is named twice")
-        seen.add(s.slot)
-        for tok in s.tokens:
-            if not (0 <= int(tok) < vocab_size):
-                raise StepError(f"step: token id {tok} out of range")
-        for w in s.want:
-            if not (0 <= int(w) < len(s.tokens)):
-                raise StepError(f"step: wanted place {w} is not among the {len(s.tokens)} tokens given")
-    bases = [cache.length(s.slot) for s in seqs]          # raises CacheError for a slot that is not live
-    firsts = [b == 0 for b in bases]
-    decode = all(len(s.tokens) == 1 for s in seqs)
-    if not decode and not all(firsts):
-        raise StepError("step: sequences must all start at their first token or all continue by one token")
-    cache.can_extend({s.slot: len(s.tokens) for s in seqs})
-    for s in seqs:
-        cache.extend(s.slot, len(s.tokens))
-
     n_real = len(seqs)
+    lens = [len(s.tokens) for s in seqs]
+    if min(lens) == 0:
+        raise StepError("step: a sequence brings no tokens")
+    slots = [s.slot for s in seqs]
+    if len(set(slots)) != n_real:
+        dup = next(x for x in slots if slots.count(x) > 1)
+        raise StepError(f"step: slot {dup} is named twice")
+    decode = max(lens) == 1
+    if decode:
+        all_tokens = np.fromiter((s.tokens[0] for s in seqs), dtype=np.int64, count=n_real)
+    else:
+        all_tokens = np.concatenate([np.asarray(s.tokens, dtype=np.int64) for s in seqs])
+    if all_tokens.min() < 0 or all_tokens.max() >= vocab_size:
+        bad = int(all_tokens[(all_tokens < 0) | (all_tokens >= vocab_size)][0])
+        raise StepError(f"step: token id {bad} out of range")
+    for s, n in zip(seqs, lens):
+        for w in s.want:
+            if not (0 <= int(w) < n):
+                raise StepError(f"step: wanted place {w} is not among the {n} tokens given")
+    bases = [cache.length(slot) for slot in slots]          # raises CacheError for a slot that is not live
+    if not decode and any(bases):
+        raise StepError("step: sequences must all start at their first token or all continue by one token")
+    cache.can_extend(dict(zip(slots, lens)))
+    for slot, n in zip(slots, lens):
+        cache.extend(slot, n)
+
     n_seqs = max(n_real, pad_seqs_to) if decode else n_real
-    n_tokens = sum(len(s.tokens) for s in seqs) + (n_seqs - n_real)
+    n_pad = n_seqs - n_real
+    n_tokens = sum(lens) + n_pad
     n_want_real = sum(len(s.want) for s in seqs)
-    n_want = n_want_real + (n_seqs - n_real if pad_seqs_to else 0)   # a padded step also wants its padding rows
-    kv_lens = [b + len(s.tokens) for b, s in zip(bases, seqs)]
+    n_want = n_want_real + (n_pad if pad_seqs_to else 0)   # a padded step also wants its padding rows
+    kv_lens = [b + n for b, n in zip(bases, lens)]
     max_kv = max(kv_lens)
 
     # layout of the block
@@ -143,56 +148,64 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
     host, dev = buffers.stage(cur)
     h = host.numpy()
 
-    tok = h[off["token_ids"][0]:off["token_ids"][0] + n_tokens]
-    tseq = h[off["tok_seq"][0]:off["tok_seq"][0] + n_tokens]
-    tpos = h[off["tok_pos"][0]:off["tok_pos"][0] + n_tokens]
-    want = h[off["want_rows"][0]:off["want_rows"][0] + max(n_want, 1)]
-    qstart = h[off["seq_q_start"][0]:off["seq_q_start"][0] + n_seqs + 1]
-    kvlen = h[off["seq_kv_len"][0]:off["seq_kv_len"][0] + n_seqs]
-    sslot = h[off["seq_slot"][0]:off["seq_slot"][0] + n_seqs]
-    t = 0
-    w = 0
+    def region(name):
+        a, n = off[name]
+        return h[a:a + n]
+    tok, tseq, tpos = region("token_ids"), region("tok_seq"), region("tok_pos")
+    want, qstart, kvlen, sslot = region("want_rows"), region("seq_q_start"), region("seq_kv_len"), region("seq_slot")
+    n_tok_real = n_tokens - n_pad
+    tok[:n_tok_real] = all_tokens
+    if decode:
+        tseq[:n_real] = np.arange(n_real, dtype=np.int32)
+        tpos[:n_real] = bases
+        qstart[:n_real] = np.arange(n_real, dtype=np.int32)
+    else:
+        starts = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+        tseq[:n_tok_real] = np.repeat(np.arange(n_real, dtype=np.int32), lens)
+        tpos[:n_tok_real] = np.arange(n_tok_real, dtype=np.int32) - np.repeat(starts[:-1], lens) + np.repeat(
+            np.asarray(bases, dtype=np.int32), lens)
+        qstart[:n_real] = starts[:-1]
+    kvlen[:n_real] = kv_lens
+    sslot[:n_real] = slots
     want[:] = 0
-    for i, (s, base) in enumerate(zip(seqs, bases)):
-        n = len(s.tokens)
-        tok[t:t + n] = np.asarray(s.tokens, dtype=np.int32)
-        tseq[t:t + n] = i
-        tpos[t:t + n] = np.arange(base, base + n, dtype=np.int32)
-        qstart[i] = t
-        kvlen[i] = base + n
-        sslot[i] = s.slot
+    w = 0
+    for i, s in enumerate(seqs):
         for place in s.want:
-            want[w] = t + int(place)
+            want[w] = qstart[i] + int(place)
             w += 1
-        t += n
-    for i in range(n_real, n_seqs):        # padding sequences: one token that no kernel touches
-        tok[t] = -1
-        tseq[t] = -1
-        tpos[t] = 0
-        qstart[i] = t
-        kvlen[i] = 0
-        sslot[i] = -1
+    if n_pad:                               # padding sequences: one token each that no kernel touches
+        t0 = n_tok_real
+        tok[t0:] = -1
+        tseq[t0:] = -1
+        tpos[t0:] = 0
+        qstart[n_real:n_seqs] = np.arange(t0, t0 + n_pad, dtype=np.int32)
+        kvlen[n_real:] = 0
+        sslot[n_real:] = -1
         if pad_seqs_to:
-            want[w] = t
-            w += 1
-        t += 1
-    qstart[n_seqs] = t
+            want[w:w + n_pad] = np.arange(t0, t0 + n_pad, dtype=np.int32)
+    qstart[n_seqs] = n_tokens
+    slot_index = np.asarray(slots, dtype=np.int64)
     for g, start, P in page_layout:
         table = h[start:start + n_seqs * P].reshape(n_seqs, P)
-        table[:] = -1
-        for i, s in enumerate(seqs):
-            pages = g.pool.table(s.slot)
-            table[i, :len(pages)] = pages
+        m = g.pool.matrix
+        if m is not None and P <= m.shape[1] and slot_index.max() < m.shape[0]:
+            table[:n_real] = m[slot_index, :P]
+            table[n_real:] = -1
+        else:
+            table[:] = -1
+            for i, slot in enumerate(slots):
+                pages = g.pool.table(slot)
+                table[i, :len(pages)] = pages
     buffers.upload(cur)
 
     ctx = StepContext()
     ctx.n_tokens, ctx.n_seqs, ctx.n_want = n_tokens, n_seqs, n_want
     ctx.n_want_real = n_want_real
     ctx.n_real_seqs = n_real
-    ctx.max_q_len = max(len(s.tokens) for s in seqs)
+    ctx.max_q_len = max(lens)
     ctx.max_kv_len = max_kv
     ctx.decode = decode
-    ctx.n_q_blocks = sum((len(s.tokens) + 127) // 128 for s in seqs)     # 128-query blocks of the prompt kernel
+    ctx.n_q_blocks = sum((n + 127) // 128 for n in lens)     # 128-query blocks of the prompt kernel
     ctx.h2d_bytes = cur * 4
 
     def view(name):
