@@ -408,6 +408,238 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// The same product on PAIRS of SMs (cta_group::2) for long prompts.
+//
+// A 128x256 tile per SM needs 48 KB from L2 per 64-deep k block, and with 227 KB of shared memory only
+// four such stages fit: not enough work in flight to cover the latency of the loads, which is what holds
+// the single-SM kernel at ~58 % tensor-pipe activity.  Two SMs of a cluster share one 256-token tile: each
+// loads its own 128 weight rows and HALF of the token tile, one thread of the leader issues
+// tcgen05.mma.cta_group::2 (M = 256 over both SMs' TMEM, N = 256), so a stage is 32 KB per SM for the same
+// MMA work and six stages fit.  No multicast load is used: each SM fetches what it needs itself, and its
+// copies report to the leader's mbarrier (the .cta_group::2 form of cp.async.bulk.tensor).
+//
+//   full[s]      in the leader; 64 KB expected per stage (both SMs' A and B halves)
+//   empty[s]     in each SM; signalled by the leader's tcgen05.commit, multicast to the pair
+//   acc_full[b]  in each SM (multicast commit);  acc_empty[b] in the leader, 8 arrivals (4 warps x 2 SMs)
+constexpr int TP_BN = 256;
+constexpr int TP_STAGES = 6;
+constexpr int TP_STAGE_BYTES = 2 * TC_BM * TC_BK * 2;   // A half-tile + B half-tile, 16 KB each
+constexpr int TP_SMEM = TP_STAGES * TP_STAGE_BYTES + 1024 + 8 * (2 * TP_STAGES + 4) + 16;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// the address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {   // arrives on `bar` in both CTAs of the pair
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((uint16_t)3)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p,
+                    int m_tiles, int n_tiles) {   // tiles of 256 weight rows x 256 tokens
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + TP_STAGES * TP_STAGE_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (TP_STAGES + s); };
+  auto acc_full = [&](int b) { return bars + 8u * (2 * TP_STAGES + b); };
+  auto acc_empty = [&](int b) { return bars + 8u * (2 * TP_STAGES + 2 + b); };
+  const uint32_t tmem_slot = bars + 8u * (2 * TP_STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();          // 0: leader, 1: peer
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int kblocks = (p.k + TC_BK - 1) / TC_BK;
+  const int n_units = m_tiles * n_tiles;
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    for (int s = 0; s < TP_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full(b), 1);
+      mbar_init(acc_empty(b), 8);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  // both CTAs' barriers exist before anything signals across the pair
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  uint32_t tmem_d;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_d) : "r"(tmem_slot));
+
+  pdl_launch_dependents();
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- TMA producer (both CTAs): own 128 weight rows and own half of the token tile ----
+      pdl_wait();
+      int it = 0;
+      bool ok = true;
+      for (int u = pair; u < n_units && ok; u += n_pairs) {
+        const int mt = u % m_tiles, nt = u / m_tiles;
+        for (int i = 0; i < kblocks; ++i, ++it) {
+          const int s = it % TP_STAGES;
+          if (it >= TP_STAGES && !mbar_wait(empty_bar(s), ((it / TP_STAGES) - 1) & 1, p.error_flag, 5)) { ok = false; break; }
+          const uint32_t leader_full = map_to_rank(full_bar(s), 0);
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * TP_STAGE_BYTES);
+          const uint32_t dst = base + s * TP_STAGE_BYTES;
+          tma_load_2d_pair(dst, &map_w, i * TC_BK, mt * 256 + (int)rank * TC_BM, leader_full);
+          tma_load_2d_pair(dst + TC_BM * TC_BK * 2, &map_x, i * TC_BK, nt * TP_BN + (int)rank * 128, leader_full);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // ---- MMA issuer (leader only): D fp32, A and B bf16 K-major, M = 256 over the pair, N = 256 ----
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TP_BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+      int it = 0, j = 0;
+      bool ok = true;
+      for (int u = pair; u < n_units && ok; u += n_pairs, ++j) {
+        const int b = j & 1;
+        if (j >= 2 && !mbar_wait(acc_empty(b), ((j >> 1) - 1) & 1, p.error_flag, 6)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t d_addr = tmem_d + (uint32_t)(b * TP_BN);
+        for (int i = 0; i < kblocks; ++i, ++it) {
+          const int s = it % TP_STAGES;
+          ok = mbar_wait(full_bar(s), (it / TP_STAGES) & 1, p.error_flag, 7);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = base + s * TP_STAGE_BYTES;
+          const uint64_t a_desc = umma_desc(a_addr), b_desc = umma_desc(a_addr + TC_BM * TC_BK * 2);
+#pragma unroll
+          for (int k4 = 0; k4 < TC_BK / 16; ++k4)
+            umma_bf16_pair(d_addr, a_desc + 2 * k4, b_desc + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+          umma_commit_pair(empty_bar(s));
+        }
+        if (ok) umma_commit_pair(acc_full(b));
+      }
+    }
+  } else {
+    // ---- epilogue warps (both CTAs): this CTA's 128 rows x 256 tokens ----
+    const int quad = warp & 3;
+    pdl_wait();
+    int j = 0;
+    for (int u = pair; u < n_units; u += n_pairs, ++j) {
+      const int mt = u % m_tiles, nt = u / m_tiles;
+      const int b = j & 1;
+      const int m = mt * 256 + (int)rank * TC_BM + quad * 32 + lane;
+      const int n0 = nt * TP_BN;
+      const uint32_t t_base = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * TP_BN);
+      const uint32_t leader_empty = map_to_rank(acc_empty(b), 0);
+      if (!mbar_wait(acc_full(b), (j >> 1) & 1, p.error_flag, 8)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int nch = (min(TP_BN, p.n_tok - n0) + 15) / 16;
+      if (p.mode == OUT_ADD_F32) {
+        const bool row_ok = m < p.m_out;
+        const float bias = (p.bias && row_ok) ? p.bias[m] : 0.f;
+        float* o = (float*)p.out + (size_t)n0 * p.ldo + m;
+        float nxt[16];
+#pragma unroll
+        for (int c = 0; c < 16; ++c) nxt[c] = (row_ok && n0 + c < p.n_tok) ? o[(size_t)c * p.ldo] : 0.f;
+        for (int ci = 0; ci < nch; ++ci) {
+          float cur[16], v[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) cur[c] = nxt[c];
+          if (ci + 1 < nch) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              nxt[c] = (row_ok && n0 + (ci + 1) * 16 + c < p.n_tok) ? o[(size_t)((ci + 1) * 16 + c) * p.ldo] : 0.f;
+          }
+          tmem_ld16(t_base + ci * 16, v);
+          if (ci == nch - 1) {
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(leader_empty);
+          }
+#pragma unroll
+          for (int c = 0; c < 16; ++c)
+            if (row_ok && n0 + ci * 16 + c < p.n_tok) o[(size_t)(ci * 16 + c) * p.ldo] = cur[c] + (v[c] + bias);
+        }
+      } else {
+        for (int ci = 0; ci < nch; ++ci) {
+          float v[16];
+          tmem_ld16(t_base + ci * 16, v);
+          if (ci == nch - 1) {
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(leader_empty);
+          }
+          tc_epilogue_store<TP_BN>(p, v, m, n0 + ci * 16, p.n_tok - (n0 + ci * 16));
+        }
+      }
+    }
+  }
+  // nobody leaves while its partner may still signal it or read its shared memory
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(512));
+  }
+}
+
+static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int m_tiles, int n_tiles,
+                          cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM) != cudaSuccess)
+      return LLMI_ERR_LAUNCH;
+    configured = true;
+  }
+  const long n_units = (long)m_tiles * n_tiles;
+  const long pairs = n_units < 74 ? n_units : 74;     // 148 SMs
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = TP_SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled(PDL_GEMM) ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mw, mx, p, m_tiles, n_tiles) == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH;
+}
+
 // ------------------------------------------------------------------------------------------- host
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -507,6 +739,18 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
   CUtensorMap mw, mx;
   int rc = make_map(&mw, w, m_out, k, ldw, TC_BM);
   if (rc != LLMI_OK) return rc;
+  // long prompts: pairs of SMs share a 256-token tile (each loads 128 of its rows)
+  static int pair_ok = -1;
+  if (pair_ok < 0) {
+    const char* e = getenv("LLMI_TC_PAIR");
+    pair_ok = (e && e[0] == '0') ? 0 : 1;
+  }
+  if (pair_ok && n_tok >= 512 && splits == 1) {
+    rc = make_map(&mx, x, n_tok, k, ldx, 128);
+    if (rc != LLMI_OK) return rc;
+    TcParams pp{m_out, n_tok, k, y, ldy, bias, mode, 1, workspace, tickets, error_flag};
+    return launch_tc_pair(mw, mx, pp, (m_out + 255) / 256, (n_tok + 255) / 256, stream);
+  }
   rc = make_map(&mx, x, n_tok, k, ldx, bn);
   if (rc != LLMI_OK) return rc;
   TcParams p{m_out, n_tok, k, y, ldy, bias, mode, splits, workspace, tickets, error_flag};
