@@ -197,44 +197,53 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       }
     }
     // mask, running maximum, probabilities
+    // Running maximum on the raw scores (the scale is positive), masked only where a page can hold keys a
+    // query may not see; the scale enters with the subtraction of the maximum: p = 2^(s*scale - m*scale).
     const bool need_mask = (key0 + PF_PAGE - 1 > first_q) || (p.window > 0);
     float mx0 = -INFINITY, mx1 = -INFINITY;
+    if (need_mask) {
 #pragma unroll
-    for (int nc = 0; nc < 8; ++nc)
+      for (int nc = 0; nc < 8; ++nc)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = key0 + nc * 8 + 2 * t + (e & 1);
-        const int qp = (e < 2) ? qpos0 : qpos1;
-        float v = sc[nc][e] * p.scale_log2;
-        if (need_mask && (key > qp || (p.window > 0 && key < qp - p.window + 1))) v = -INFINITY;
-        sc[nc][e] = v;
-        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
-      }
+        for (int e = 0; e < 4; ++e) {
+          const int key = key0 + nc * 8 + 2 * t + (e & 1);
+          const int qp = (e < 2) ? qpos0 : qpos1;
+          if (key > qp || (p.window > 0 && key < qp - p.window + 1)) sc[nc][e] = -INFINITY;
+        }
+    }
+#pragma unroll
+    for (int nc = 0; nc < 8; ++nc) {
+      mx0 = fmaxf(mx0, fmaxf(sc[nc][0], sc[nc][1]));
+      mx1 = fmaxf(mx1, fmaxf(sc[nc][2], sc[nc][3]));
+    }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float mn0 = fmaxf(mrow[0], mx0), mn1 = fmaxf(mrow[1], mx1);
+    const float mn0 = fmaxf(mrow[0], mx0 * p.scale_log2), mn1 = fmaxf(mrow[1], mx1 * p.scale_log2);   // scaled maxima
     const float c0 = (mn0 == -INFINITY) ? 1.f : fast_exp2(mrow[0] - mn0);
     const float c1 = (mn1 == -INFINITY) ? 1.f : fast_exp2(mrow[1] - mn1);
     mrow[0] = mn0;
     mrow[1] = mn1;
-    lrow[0] *= c0;
-    lrow[1] *= c1;
+    if (__any_sync(0xffffffffu, c0 != 1.f || c1 != 1.f)) {   // the maximum settles after a few pages: then nothing to rescale
+      lrow[0] *= c0;
+      lrow[1] *= c1;
 #pragma unroll
-    for (int dc = 0; dc < HD / 8; ++dc) {
-      o[dc][0] *= c0;
-      o[dc][1] *= c0;
-      o[dc][2] *= c1;
-      o[dc][3] *= c1;
+      for (int dc = 0; dc < HD / 8; ++dc) {
+        o[dc][0] *= c0;
+        o[dc][1] *= c0;
+        o[dc][2] *= c1;
+        o[dc][3] *= c1;
+      }
     }
+    const float nm0 = (mn0 == -INFINITY) ? 0.f : -mn0, nm1 = (mn1 == -INFINITY) ? 0.f : -mn1;
     uint32_t pa[4][4];
 #pragma unroll
     for (int nc = 0; nc < 8; ++nc) {
-      const float p0 = (mn0 == -INFINITY) ? 0.f : fast_exp2(sc[nc][0] - mn0);
-      const float p1 = (mn0 == -INFINITY) ? 0.f : fast_exp2(sc[nc][1] - mn0);
-      const float p2 = (mn1 == -INFINITY) ? 0.f : fast_exp2(sc[nc][2] - mn1);
-      const float p3 = (mn1 == -INFINITY) ? 0.f : fast_exp2(sc[nc][3] - mn1);
+      const float p0 = fast_exp2(fmaf(sc[nc][0], p.scale_log2, nm0));   // 2^(-inf) = 0 for masked keys
+      const float p1 = fast_exp2(fmaf(sc[nc][1], p.scale_log2, nm0));
+      const float p2 = fast_exp2(fmaf(sc[nc][2], p.scale_log2, nm1));
+      const float p3 = fast_exp2(fmaf(sc[nc][3], p.scale_log2, nm1));
       lrow[0] += p0 + p1;
       lrow[1] += p2 + p3;
       pa[nc >> 1][(nc & 1) * 2 + 0] = pack_bf16(p0, p1);
