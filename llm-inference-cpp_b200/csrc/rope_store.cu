@@ -16,7 +16,14 @@
 namespace llmi {
 
 constexpr int MAX_HALF = 256;
+
+// The rotation of one pair, with its roundings spelled out so that every kernel of this file gives the
+// same bits whatever the compiler would contract: the result must not depend on which kernel a step's
+// size selects.
+__device__ __forceinline__ float rot_lo(float a, float b, float c, float s) { return __fmaf_rn(a, c, -__fmul_rn(b, s)); }
+__device__ __forceinline__ float rot_hi(float a, float b, float c, float s) { return __fmaf_rn(b, c, __fmul_rn(a, s)); }
 constexpr int ROPE_WARPS = 4;
+constexpr int ROWS_MIN_TOKENS = 256;   // from here on the kernel that shares sines and cosines among the heads pays
 
 // One warp per (token, head): heads 0..n_heads-1 are query heads (rotated in place), heads
 // n_heads..n_heads+n_kv-1 are key heads (rotated into the cache) together with their value heads.
@@ -43,8 +50,8 @@ rope_store_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ inv_fr
       float s, c;
       sincosf((float)pos * inv_freq[i], &s, &c);
       const float a = to_f32(p[i]), b = to_f32(p[i + half]);
-      p[i] = from_f32<T>(a * c - b * s);
-      p[i + half] = from_f32<T>(b * c + a * s);
+      p[i] = from_f32<T>(rot_lo(a, b, c, s));
+      p[i + half] = from_f32<T>(rot_hi(a, b, c, s));
     }
     return;
   }
@@ -57,8 +64,8 @@ rope_store_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ inv_fr
     float s, c;
     sincosf((float)pos * inv_freq[i], &s, &c);
     const float a = to_f32(ksrc[i]), b = to_f32(ksrc[i + half]);
-    k_cache[dst + i] = from_f32<T>(a * c - b * s);
-    k_cache[dst + i + half] = from_f32<T>(b * c + a * s);
+    k_cache[dst + i] = from_f32<T>(rot_lo(a, b, c, s));
+    k_cache[dst + i + half] = from_f32<T>(rot_hi(a, b, c, s));
   }
   for (int d = rotary_dim + lane; d < hd; d += 32) k_cache[dst + d] = ksrc[d];
   for (int d = lane; d < hd; d += 32) v_cache[dst + d] = vsrc[d];
@@ -105,8 +112,8 @@ rope_store_vec_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ in
   if (j < n_heads) {
     T* p = row + (size_t)j * hd;
     const float2 a = Pair<T>::load(p + i), b = Pair<T>::load(p + i + half);
-    Pair<T>::store(p + i, make_float2(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1));
-    Pair<T>::store(p + i + half, make_float2(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1));
+    Pair<T>::store(p + i, make_float2(rot_lo(a.x, b.x, c0, s0), rot_lo(a.y, b.y, c1, s1)));
+    Pair<T>::store(p + i + half, make_float2(rot_hi(a.x, b.x, c0, s0), rot_hi(a.y, b.y, c1, s1)));
     return;
   }
   if (!write_kv) return;
@@ -115,10 +122,109 @@ rope_store_vec_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ in
   const T* vsrc = row + (size_t)(n_heads + kv.n_kv_heads + h) * hd;
   const size_t dst = kv_row_offset(kv, seq, pos, h);
   const float2 a = Pair<T>::load(ksrc + i), b = Pair<T>::load(ksrc + i + half);
-  Pair<T>::store(k_cache + dst + i, make_float2(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1));
-  Pair<T>::store(k_cache + dst + i + half, make_float2(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1));
+  Pair<T>::store(k_cache + dst + i, make_float2(rot_lo(a.x, b.x, c0, s0), rot_lo(a.y, b.y, c1, s1)));
+  Pair<T>::store(k_cache + dst + i + half, make_float2(rot_hi(a.x, b.x, c0, s0), rot_hi(a.y, b.y, c1, s1)));
   Pair<T>::store(v_cache + dst + i, Pair<T>::load(vsrc + i));
   Pair<T>::store(v_cache + dst + i + half, Pair<T>::load(vsrc + i + half));
+}
+
+// The same for a long prompt: the angle of (position, pair) is the same for every head of a token, and
+// sine and cosine are the costly part.  A thread takes one 16-byte chunk of the first half of a head and
+// its partner chunk in the second half, computes the chunk's sines and cosines once, and walks over every
+// ROWS_HEAD_LANES-th head of the token with 16-byte loads and stores.  The arithmetic of an element is
+// that of the kernels above, so the results are the same bits.
+constexpr int ROWS_HEAD_LANES = 8;
+
+template <typename T> struct Chunk;
+template <> struct Chunk<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x, f[1] = v.y, f[2] = v.z, f[3] = v.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* f) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+  static __device__ __forceinline__ void copy(float* dst, const float* src) {
+    *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+  }
+};
+template <> struct Chunk<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 v = __bfloat1622float2(h[e]);
+      f[2 * e] = v.x, f[2 * e + 1] = v.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* f) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+  }
+  static __device__ __forceinline__ void copy(__nv_bfloat16* dst, const __nv_bfloat16* src) {
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+rope_store_rows_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ inv_freq, const int32_t* __restrict__ tok_seq,
+                       const int32_t* __restrict__ tok_pos, PagedKV kv, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                       int n_heads, int write_kv, long n_items) {
+  constexpr int N = Chunk<T>::N;
+  pdl_launch_dependents();
+  pdl_wait();
+  const long item = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= n_items) return;
+  const int hd = kv.head_dim, half = hd / 2, n_chunks = half / N;
+  const int per_tok = n_chunks * ROWS_HEAD_LANES;
+  const int t = (int)(item / per_tok);
+  const int rest = (int)(item - (long)t * per_tok);
+  const int hl = rest / n_chunks, i0 = (rest - hl * n_chunks) * N;
+  const int seq = tok_seq[t];
+  if (seq < 0) return;
+  const int pos = tok_pos[t];
+  float sn[N], cs[N];
+#pragma unroll
+  for (int e = 0; e < N; ++e) sincosf((float)pos * inv_freq[i0 + e], &sn[e], &cs[e]);
+  T* row = qkv + (size_t)t * ld;
+  for (int j = hl; j < n_heads; j += ROWS_HEAD_LANES) {
+    T* p = row + (size_t)j * hd + i0;
+    float a[N], b[N], lo[N], hi[N];
+    Chunk<T>::load(p, a);
+    Chunk<T>::load(p + half, b);
+#pragma unroll
+    for (int e = 0; e < N; ++e) {
+      lo[e] = rot_lo(a[e], b[e], cs[e], sn[e]);
+      hi[e] = rot_hi(a[e], b[e], cs[e], sn[e]);
+    }
+    Chunk<T>::store(p, lo);
+    Chunk<T>::store(p + half, hi);
+  }
+  if (!write_kv) return;
+  for (int h = hl; h < kv.n_kv_heads; h += ROWS_HEAD_LANES) {
+    const T* ksrc = row + (size_t)(n_heads + h) * hd + i0;
+    const T* vsrc = row + (size_t)(n_heads + kv.n_kv_heads + h) * hd + i0;
+    const size_t dst = kv_row_offset(kv, seq, pos, h) + i0;
+    float a[N], b[N], lo[N], hi[N];
+    Chunk<T>::load(ksrc, a);
+    Chunk<T>::load(ksrc + half, b);
+#pragma unroll
+    for (int e = 0; e < N; ++e) {
+      lo[e] = rot_lo(a[e], b[e], cs[e], sn[e]);
+      hi[e] = rot_hi(a[e], b[e], cs[e], sn[e]);
+    }
+    Chunk<T>::store(k_cache + dst, lo);
+    Chunk<T>::store(k_cache + dst + half, hi);
+    Chunk<T>::copy(v_cache + dst, vsrc);
+    Chunk<T>::copy(v_cache + dst + half, vsrc + half);
+  }
 }
 
 }  // namespace llmi
@@ -134,6 +240,21 @@ LLMI_EXPORT int llmi_rope_store(int dtype, void* qkv, long ld, const float* inv_
   PagedKV kv{seq_pages, pages_stride, page_size, n_kv_heads, head_dim};
   const size_t esz = dtype == LLMI_DTYPE_F32 ? 4 : 2;
   const bool pair_aligned = !(((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache) & (2 * esz - 1)) && !(ld & 1);
+  const int chunk = 16 / (int)esz;
+  const bool chunk_aligned = !(((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) && !((ld * esz) & 15) &&
+                             (head_dim / 2) % chunk == 0;
+  if (rotary_dim == head_dim && chunk_aligned && n_tokens >= ROWS_MIN_TOKENS &&
+      (dtype == LLMI_DTYPE_F32 || dtype == LLMI_DTYPE_BF16)) {
+    const long n_thr = (long)n_tokens * (head_dim / 2 / chunk) * ROWS_HEAD_LANES;
+    const long rblocks = (n_thr + 127) / 128;
+    if (rblocks > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
+    if (dtype == LLMI_DTYPE_F32)
+      return launch_pdl(PDL_ROPE, rope_store_rows_kernel<float>, (unsigned)rblocks, 128, 0, stream, (float*)qkv, ld, inv_freq,
+                        tok_seq, tok_pos, kv, (float*)k_cache, (float*)v_cache, n_heads, write_kv, n_thr);
+    return launch_pdl(PDL_ROPE, rope_store_rows_kernel<__nv_bfloat16>, (unsigned)rblocks, 128, 0, stream, (__nv_bfloat16*)qkv,
+                      ld, inv_freq, tok_seq, tok_pos, kv, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads,
+                      write_kv, n_thr);
+  }
   if (rotary_dim == head_dim && head_dim % 4 == 0 && pair_aligned && (dtype == LLMI_DTYPE_F32 || dtype == LLMI_DTYPE_BF16)) {
     const long n_vec = (long)n_tokens * (n_heads + n_kv_heads) * (head_dim / 4);
     const long vblocks = (n_vec + 255) / 256;

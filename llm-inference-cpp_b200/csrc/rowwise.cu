@@ -50,8 +50,20 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<T>(weight[i] * (xr[i] * scale));
 }
 
-// The same, with the row held in registers between the sum of squares and the scaling: one read of x.
-// Needs width % 4 == 0 and width <= 4 * VPT * blockDim.x.
+// The same, with the row held in registers between the sum of squares and the scaling: one read of x,
+// 16-byte loads (VPT of them in flight per thread, which is what keeps a many-row launch at memory speed)
+// and one store per four outputs.  Needs width % 4 == 0 and width <= 4 * VPT * blockDim.x.
+__device__ __forceinline__ void store4(float* o, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(o) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* o, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t*>(&lo);
+  u.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(o) = u;
+}
+
 template <typename T, int VPT>
 __global__ void rmsnorm_reg_kernel(const float* __restrict__ x, const float* __restrict__ weight, T* __restrict__ out,
                                    const int32_t* __restrict__ rows, int width, float eps) {
@@ -85,10 +97,7 @@ __global__ void rmsnorm_reg_kernel(const float* __restrict__ x, const float* __r
     const int i = threadIdx.x + j * blockDim.x;
     if (i < nvec) {
       const float4 w = wv[i];
-      o[4 * i + 0] = from_f32<T>(w.x * (v[j].x * scale));
-      o[4 * i + 1] = from_f32<T>(w.y * (v[j].y * scale));
-      o[4 * i + 2] = from_f32<T>(w.z * (v[j].z * scale));
-      o[4 * i + 3] = from_f32<T>(w.w * (v[j].w * scale));
+      store4(o + 4 * i, w.x * (v[j].x * scale), w.y * (v[j].y * scale), w.z * (v[j].z * scale), w.w * (v[j].w * scale));
     }
   }
 }
@@ -129,12 +138,14 @@ LLMI_EXPORT int llmi_rmsnorm(int out_dtype, const float* x, const float* weight,
   if (n_rows <= 0 || width <= 0) return LLMI_ERR_BAD_SIZE;
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
   if (out_dtype != LLMI_DTYPE_F32 && out_dtype != LLMI_DTYPE_BF16) return LLMI_ERR_BAD_DTYPE;
-  const bool aligned = (width % 4 == 0) && !((uintptr_t)x & 15) && !((uintptr_t)weight & 15);
-  if (aligned && width <= 4 * 2 * threads) {
+  const bool aligned = (width % 4 == 0) && !((uintptr_t)x & 15) && !((uintptr_t)weight & 15) && !((uintptr_t)out & 15);
+  constexpr int VPT = 4;
+  const int reg_threads = ((width / 4 + VPT - 1) / VPT + 31) / 32 * 32;    // four 16-byte loads per thread
+  if (aligned && reg_threads <= 1024) {
     if (out_dtype == LLMI_DTYPE_F32)
-      return launch_pdl(PDL_SMALL, rmsnorm_reg_kernel<float, 2>, n_rows, threads, 0, stream, x, weight, (float*)out, rows, width, eps);
+      return launch_pdl(PDL_SMALL, rmsnorm_reg_kernel<float, VPT>, n_rows, reg_threads, 0, stream, x, weight, (float*)out, rows, width, eps);
     else
-      return launch_pdl(PDL_SMALL, rmsnorm_reg_kernel<__nv_bfloat16, 2>, n_rows, threads, 0, stream, x, weight, (__nv_bfloat16*)out, rows, width, eps);
+      return launch_pdl(PDL_SMALL, rmsnorm_reg_kernel<__nv_bfloat16, VPT>, n_rows, reg_threads, 0, stream, x, weight, (__nv_bfloat16*)out, rows, width, eps);
   } else if (out_dtype == LLMI_DTYPE_F32)
     return launch_pdl(PDL_SMALL, rmsnorm_kernel<float>, n_rows, threads, 0, stream, x, weight, (float*)out, rows, width, eps);
   else

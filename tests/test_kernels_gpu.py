@@ -125,6 +125,48 @@ def test_rope_store(dtype, nh, nkv, hd, rot):
     assert int(torch.isfinite(kc.float()).sum()) == 6 * nkv * hd        # nothing else was written
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd", [(6, 2, 48), (9, 3, 16), (5, 5, 64), (3, 1, 128)])
+def test_rope_store_long_prompt_same_bits(dtype, nh, nkv, hd):
+    """From 256 tokens on another kernel runs (sines and cosines shared among the heads of a token): it must
+    give the bits of the kernel that short steps use, and agree with the plain formulas."""
+    k = K()
+    T = 300
+    gen = torch.Generator(device="cuda").manual_seed(hd)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device="cuda", generator=gen).to(DT[dtype])
+    orig = qkv.clone()
+    # two sequences, the second one padding-free but short; one padding token in the middle
+    pos = torch.cat([torch.arange(0, 250), torch.arange(0, 50)]).to(torch.int32).cuda()
+    seq = torch.cat([torch.zeros(250), torch.ones(50)]).to(torch.int32).cuda()
+    seq[123] = -1
+    pages = torch.tensor([[5, 0, 3, 6], [2, -1, -1, -1]], dtype=torch.int32, device="cuda")
+    inv = torch.from_numpy(P.rope_inv_freq(hd, 54321.0)).cuda()
+    kc, vc = paged(7, nkv, hd, dtype)
+    k.rope_store(qkv, inv, hd, seq, pos, pages, 64, kc, vc, nh, nkv, hd, True)
+    # the same in pieces of fewer than 256 tokens
+    q2 = orig.clone()
+    kc2, vc2 = paged(7, nkv, hd, dtype)
+    for a in range(0, T, 100):
+        k.rope_store(q2[a:a + 100], inv, hd, seq[a:a + 100].contiguous(), pos[a:a + 100].contiguous(), pages, 64, kc2, vc2,
+                     nh, nkv, hd, True)
+    assert torch.equal(qkv, q2)
+    assert torch.equal(torch.nan_to_num(kc.float(), nan=-7.0), torch.nan_to_num(kc2.float(), nan=-7.0))
+    assert torch.equal(torch.nan_to_num(vc.float(), nan=-7.0), torch.nan_to_num(vc2.float(), nan=-7.0))
+    assert torch.equal(qkv[123], orig[123])
+    assert int(torch.isfinite(kc.float()).sum()) == 299 * nkv * hd
+    o = orig.double().cpu().numpy()
+    invn = P.rope_inv_freq(hd, 54321.0)
+    tol = 2e-6 if dtype == "float32" else 5e-3
+    for t in (0, 1, 63, 64, 200, 249, 250, 299):
+        q = P.rope(o[t, :nh * hd].reshape(1, nh, hd), [int(pos[t])], invn)
+        kk = P.rope(o[t, nh * hd:(nh + nkv) * hd].reshape(1, nkv, hd), [int(pos[t])], invn)
+        page = int(pages[int(seq[t]), int(pos[t]) // 64])
+        assert rel(qkv[t, :nh * hd].reshape(nh, hd), torch.from_numpy(q[0])) < tol
+        assert rel(kc[page, :, int(pos[t]) % 64], torch.from_numpy(kk[0])) < tol
+        assert torch.equal(vc[page, :, int(pos[t]) % 64].double().cpu(),
+                           torch.from_numpy(o[t, (nh + nkv) * hd:].reshape(nkv, hd)))
+
+
 def plain_attention_rows(q, keys, vals, group, scale, window):
     """q [nh, hd] at the last position of keys/vals [n, nkv, hd]."""
     out = np.zeros_like(q)
