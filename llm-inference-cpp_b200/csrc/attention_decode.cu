@@ -16,8 +16,14 @@
 //    the block that takes a sequence-head's last ticket merges the splits in split order and writes
 //    the output.  Nothing waits for another block.
 //
-// Softmax runs in fp32 with a running maximum; the merge order is fixed, so a sequence's result does
-// not depend on its batch-mates.  `window` > 0 keeps keys pos-window+1..pos.
+// Softmax runs in fp32 with a running maximum, in base 2 (scores are scaled by scale*log2(e) and the
+// exponential is one ex2 instruction); the merge order is fixed, so a sequence's result does not depend
+// on its batch-mates.  `window` > 0 keeps keys pos-window+1..pos.
+//
+// Launched as a programmatic dependent, the kernel starts while the kernels before it still run: of
+// everything it reads, they write only q and the cache row of each sequence's newest position, so the
+// producer fetches older pages at once and waits (griddepcontrol.wait) only before the newest page;
+// the consumers wait before they read q.
 #include <math.h>
 
 #include "common.cuh"
@@ -41,7 +47,7 @@ struct DecodeParams {
   const int32_t* seq_q_start; // [n_seqs] row of the sequence's token
   int pages_stride;
   int n_kv_heads;
-  float scale;
+  float scale_log2;          // softmax scale * log2(e)
   int window;
   int pages_per_split;
   int max_splits;            // gridDim.x
@@ -111,7 +117,6 @@ attention_decode_kernel(DecodeParams p, int n_items) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  pdl_wait();   // q and the newest cache entries come from the kernels before
 
   // The first non-empty item at or after `item` in this block's sequence of items (stride gridDim.x);
   // returns n_items when there is none.  Every warp role walks the same sequence.
@@ -143,11 +148,15 @@ attention_decode_kernel(DecodeParams p, int n_items) {
     if (lane == 0) {
       int it = 0;
       DecItem d;
-      bool ok = true;
+      bool ok = true, waited = false;
       for (int item = next_item(blockIdx.x, d); item < n_items && ok; item = next_item(item + gridDim.x, d)) {
         const int32_t* pages = p.seq_pages + (size_t)d.seq * p.pages_stride;
         for (int i = 0; i < d.n_pages; ++i, ++it) {
           const int s = it % C::STAGES;
+          if (!waited && (d.pg0 + i + 1) * DEC_PAGE > d.pos) {   // the page of the newest position: written by the kernel before
+            pdl_wait();
+            waited = true;
+          }
           if (it >= C::STAGES && !mbar_wait(empty_bar(s), ((it / C::STAGES) - 1) & 1, p.error_flag, 11)) { ok = false; break; }
           const size_t tile = ((size_t)pages[d.pg0 + i] * p.n_kv_heads + d.kvh) * (size_t)(DEC_PAGE * HD);
           mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
@@ -163,6 +172,7 @@ attention_decode_kernel(DecodeParams p, int n_items) {
     // ---- epilogue warp: items cut into several splits pass through here ----
     int n_split_items = 0;
     DecItem d;
+    pdl_wait();
     for (int item = next_item(blockIdx.x, d); item < n_items; item = next_item(item + gridDim.x, d)) {
       if (d.n_parts == 1) continue;
       const int b = n_split_items & 1;
@@ -185,37 +195,61 @@ attention_decode_kernel(DecodeParams p, int n_items) {
       const float* parts = p.partials + (((size_t)d.seq * p.n_kv_heads + d.kvh) * p.max_splits) * G * (HD + 2);
       constexpr int DPL = (HD + 31) / 32;   // output dims per lane
       for (int g = 0; g < G; ++g) {
-        float M = -INFINITY;
-        for (int z = lane; z < d.n_parts; z += 32) M = fmaxf(M, __ldcg(&parts[((size_t)z * G + g) * (HD + 2) + HD]));
-        M = warp_max(M);
         float L = 0.f, A[DPL];
 #pragma unroll
         for (int u = 0; u < DPL; ++u) A[u] = 0.f;
-        for (int z0 = 0; z0 < d.n_parts; z0 += 32) {
-          const int z = z0 + lane;
-          float wz = 0.f, lw = 0.f;
-          if (z < d.n_parts) {
-            const float* pz = parts + ((size_t)z * G + g) * (HD + 2);
-            const float mz = __ldcg(&pz[HD]);
-            wz = (mz == -INFINITY) ? 0.f : expf(mz - M);
-            lw = __ldcg(&pz[HD + 1]) * wz;
+        if (d.n_parts <= 8) {
+          // few splits: every load of the merge is issued before any is used — one round trip to L2
+          float mz[8], lz[8], v[8][DPL];
+#pragma unroll
+          for (int z = 0; z < 8; ++z) {
+            const float* pz = parts + ((size_t)min(z, d.n_parts - 1) * G + g) * (HD + 2);
+            mz[z] = __ldcg(&pz[HD]);
+            lz[z] = __ldcg(&pz[HD + 1]);
+#pragma unroll
+            for (int u = 0; u < DPL; ++u) v[z][u] = (lane + 32 * u < HD) ? __ldcg(&pz[lane + 32 * u]) : 0.f;
           }
-          const int nz = min(32, d.n_parts - z0);
-          for (int j0 = 0; j0 < nz; j0 += 4) {
-            float v[4][DPL];
+          float M = -INFINITY;
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-              const float* pj = parts + ((size_t)(z0 + min(j0 + jj, nz - 1)) * G + g) * (HD + 2);
+          for (int z = 0; z < 8; ++z)
+            if (z < d.n_parts) M = fmaxf(M, mz[z]);
 #pragma unroll
-              for (int u = 0; u < DPL; ++u) v[jj][u] = (lane + 32 * u < HD) ? __ldcg(&pj[lane + 32 * u]) : 0.f;
+          for (int z = 0; z < 8; ++z) {
+            const float w = (z < d.n_parts && mz[z] != -INFINITY) ? fast_exp2(mz[z] - M) : 0.f;
+            L = fmaf(lz[z], w, L);
+#pragma unroll
+            for (int u = 0; u < DPL; ++u) A[u] = fmaf(w, v[z][u], A[u]);
+          }
+        } else {
+          float M = -INFINITY;
+          for (int z = lane; z < d.n_parts; z += 32) M = fmaxf(M, __ldcg(&parts[((size_t)z * G + g) * (HD + 2) + HD]));
+          M = warp_max(M);
+          for (int z0 = 0; z0 < d.n_parts; z0 += 32) {
+            const int z = z0 + lane;
+            float wz = 0.f, lw = 0.f;
+            if (z < d.n_parts) {
+              const float* pz = parts + ((size_t)z * G + g) * (HD + 2);
+              const float mz = __ldcg(&pz[HD]);
+              wz = (mz == -INFINITY) ? 0.f : fast_exp2(mz - M);
+              lw = __ldcg(&pz[HD + 1]) * wz;
             }
+            const int nz = min(32, d.n_parts - z0);
+            for (int j0 = 0; j0 < nz; j0 += 4) {
+              float v[4][DPL];
 #pragma unroll
-            for (int jj = 0; jj < 4; ++jj) {
-              const int j = min(j0 + jj, nz - 1);
-              const float w = (j0 + jj < nz) ? __shfl_sync(0xffffffffu, wz, j) : 0.f;
-              L += (j0 + jj < nz) ? __shfl_sync(0xffffffffu, lw, j) : 0.f;
+              for (int jj = 0; jj < 4; ++jj) {
+                const float* pj = parts + ((size_t)(z0 + min(j0 + jj, nz - 1)) * G + g) * (HD + 2);
 #pragma unroll
-              for (int u = 0; u < DPL; ++u) A[u] = fmaf(w, v[jj][u], A[u]);
+                for (int u = 0; u < DPL; ++u) v[jj][u] = (lane + 32 * u < HD) ? __ldcg(&pj[lane + 32 * u]) : 0.f;
+              }
+#pragma unroll
+              for (int jj = 0; jj < 4; ++jj) {
+                const int j = min(j0 + jj, nz - 1);
+                const float w = (j0 + jj < nz) ? __shfl_sync(0xffffffffu, wz, j) : 0.f;
+                L += (j0 + jj < nz) ? __shfl_sync(0xffffffffu, lw, j) : 0.f;
+#pragma unroll
+                for (int u = 0; u < DPL; ++u) A[u] = fmaf(w, v[jj][u], A[u]);
+              }
             }
           }
         }
@@ -238,6 +272,7 @@ attention_decode_kernel(DecodeParams p, int n_items) {
   DecItem d, dn;
   int item = next_item(blockIdx.x, d);
   uint4 q_raw[G], q_next[G];
+  pdl_wait();   // q comes from the kernels before
   if (item < n_items) {
 #pragma unroll
     for (int g = 0; g < G; ++g)
@@ -267,6 +302,7 @@ attention_decode_kernel(DecodeParams p, int n_items) {
       if (!ok) break;
       const uint32_t k_tile = base + s * C::STAGE_BYTES, v_tile = k_tile + C::TILE_BYTES;
       const int page_pos0 = (d.pg0 + i) * DEC_PAGE;
+      const bool inside = page_pos0 >= d.lo && page_pos0 + DEC_PAGE - 1 <= d.pos;   // every key of the page counts
       float sc[C::NI][G];
       float pmax[G];
 #pragma unroll
@@ -281,7 +317,7 @@ attention_decode_kernel(DecodeParams p, int n_items) {
         float kf[8];
         bf16x8_to_f32(raw, kf);
         const int kpos = page_pos0 + row;
-        const bool valid = kpos >= d.lo && kpos <= d.pos;
+        const bool valid = inside || (kpos >= d.lo && kpos <= d.pos);
 #pragma unroll
         for (int g = 0; g < G; ++g) {
           float dot = 0.f;
@@ -289,7 +325,7 @@ attention_decode_kernel(DecodeParams p, int n_items) {
           for (int e = 0; e < 8; ++e) dot = fmaf(q[g][e], kf[e], dot);
 #pragma unroll
           for (int o = 1; o < C::LPR; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-          sc[j][g] = valid ? dot * p.scale : -INFINITY;
+          sc[j][g] = valid ? dot * p.scale_log2 : -INFINITY;
           pmax[g] = fmaxf(pmax[g], sc[j][g]);
         }
       }
@@ -298,11 +334,13 @@ attention_decode_kernel(DecodeParams p, int n_items) {
 #pragma unroll
         for (int o = C::LPR; o < 32; o <<= 1) pmax[g] = fmaxf(pmax[g], __shfl_xor_sync(0xffffffffu, pmax[g], o));
         const float m_new = fmaxf(m[g], pmax[g]);
-        const float corr = (m_new == -INFINITY) ? 1.f : expf(m[g] - m_new);
-        m[g] = m_new;
-        l[g] *= corr;
+        if (m_new != m[g]) {             // warp-uniform: every lane holds the same maxima
+          const float corr = fast_exp2(m[g] - m_new);     // 2^(-inf) = 0 on the first page
+          m[g] = m_new;
+          l[g] *= corr;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[g][e] *= corr;
+          for (int e = 0; e < 8; ++e) acc[g][e] *= corr;
+        }
       }
 #pragma unroll
       for (int j = 0; j < C::NI; ++j) {
@@ -313,14 +351,16 @@ attention_decode_kernel(DecodeParams p, int n_items) {
                      : "r"(v_tile + (uint32_t)(row * HD + c * 8) * 2));
         float vf[8];
         bf16x8_to_f32(raw, vf);
-        const int kpos = page_pos0 + row;
-        if (kpos < d.lo || kpos > d.pos) {   // whatever lies outside the sequence's positions counts as zero
+        if (!inside) {
+          const int kpos = page_pos0 + row;
+          if (kpos < d.lo || kpos > d.pos) {   // whatever lies outside the sequence's positions counts as zero
 #pragma unroll
-          for (int e = 0; e < 8; ++e) vf[e] = 0.f;
+            for (int e = 0; e < 8; ++e) vf[e] = 0.f;
+          }
         }
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-          const float pr = (sc[j][g] == -INFINITY) ? 0.f : expf(sc[j][g] - m[g]);
+          const float pr = (m[g] == -INFINITY) ? 0.f : fast_exp2(sc[j][g] - m[g]);   // masked keys: 2^(-inf) = 0
           l[g] += pr;
 #pragma unroll
           for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pr, vf[e], acc[g][e]);
@@ -365,7 +405,7 @@ attention_decode_kernel(DecodeParams p, int n_items) {
       float L = 0.f, A = 0.f;
 #pragma unroll
       for (int w = 0; w < DEC_CONSUMERS; ++w) {
-        const float f = (s_m[w][g] == -INFINITY) ? 0.f : expf(s_m[w][g] - M);
+        const float f = (s_m[w][g] == -INFINITY) ? 0.f : fast_exp2(s_m[w][g] - M);
         L += s_l[w][g] * f;
         A += s_acc[w][g][dd] * f;
       }
@@ -463,8 +503,8 @@ LLMI_EXPORT int llmi_attention_decode(const void* q, long ldq, void* out, long l
       (long)n_seqs * n_kv_heads > n_tickets)
     return LLMI_ERR_BAD_SIZE;
   DecodeParams p{(const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)k_cache,
-                 (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads, scale,
-                 window, pages_per_split, splits, partials, tickets, error_flag};
+                 (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads,
+                 scale * 1.4426950408889634f, window, pages_per_split, splits, partials, tickets, error_flag};
 #define LLMI_DEC(HD, G) \
   if (head_dim == HD && group == G) return launch_decode<HD, G>(p, n_seqs, stream)
   LLMI_DEC(64, 1); LLMI_DEC(64, 2); LLMI_DEC(64, 3); LLMI_DEC(64, 4); LLMI_DEC(64, 8);
@@ -541,8 +581,8 @@ LLMI_EXPORT int llmi_attention_decode_static(const void* q, long ldq, void* out,
     return LLMI_ERR_LAUNCH;
   const int splits = (max_pages + pages_per_split - 1) / pages_per_split;
   DecodeParams p{(const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)k_cache,
-                 (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads, scale,
-                 window, pages_per_split, splits, sc->partials, sc->tickets, &sc->error};
+                 (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads,
+                 scale * 1.4426950408889634f, window, pages_per_split, splits, sc->partials, sc->tickets, &sc->error};
   int rc = LLMI_ERR_UNSUPPORTED;
 #define LLMI_DEC(HD, G) \
   if (head_dim == HD && group == G) rc = launch_decode<HD, G>(p, n_seqs, stream)

@@ -20,14 +20,6 @@
 
 namespace llmi {
 
-// 2^x on the special-function unit, one instruction (ex2.approx: relative error about 2^-22; the results
-// here end up in bf16).  exp2f() costs several such instructions.
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 constexpr int PF_BM = 128;      // queries per block
 constexpr int PF_PAGE = 64;     // keys per step = the cache's page size
 constexpr int PF_THREADS = 256;

@@ -24,14 +24,6 @@
 
 namespace llmi {
 
-// 2^x on the special-function unit, one instruction (ex2.approx: relative error about 2^-22; the results
-// here end up in bf16).  exp2f() costs several such instructions.
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 constexpr int FT_BM = 128, FT_PAGE = 64, FT_HD = 64;
 constexpr int FT_STAGES = 3;
 constexpr int FT_THREADS = 192;

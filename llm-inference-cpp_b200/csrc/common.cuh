@@ -61,6 +61,14 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return total;
 }
 
+// 2^x on the special-function unit, one instruction (ex2.approx: relative error about 2^-22; the results
+// here end up in bf16).  exp2f() costs several such instructions.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 inline int launch_status() { return cudaPeekAtLastError() == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH; }
 
 // Programmatic dependent launch.  A kernel launched with launch_pdl may start while the kernel before
@@ -72,15 +80,16 @@ inline int launch_status() { return cudaPeekAtLastError() == cudaSuccess ? LLMI_
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// LLMI_PDL is a bit mask of the kernel kinds that launch this way.  The default leaves the decode
-// attention kernel out: launched early behind the rotary kernel it ran markedly slower at batch 64
-// (measured: 14.0 ms a step against 10.2 ms), and no faster at batch 1 and 8.
+// LLMI_PDL is a bit mask of the kernel kinds that launch this way (default: all).  One rule came from
+// measurement: the decode attention kernel must not start while the product before the rotary kernel
+// still runs (batch 16: 3.86 ms a step against 3.18 ms; batch 64: 13.6 against 10.5), so the rotary
+// kernel signals its dependents only after its own wait, where every other kernel signals at once.
 constexpr int PDL_SMALL = 1, PDL_GEMM = 2, PDL_ATTENTION = 4, PDL_ROPE = 8;
 inline bool pdl_enabled(int kind) {
   static int mask = -1;
   if (mask < 0) {
     const char* e = getenv("LLMI_PDL");
-    mask = e ? atoi(e) : (PDL_SMALL | PDL_GEMM | PDL_ROPE);
+    mask = e ? atoi(e) : (PDL_SMALL | PDL_GEMM | PDL_ATTENTION | PDL_ROPE);
   }
   return (mask & kind) != 0;
 }

@@ -32,8 +32,8 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32)
 rope_store_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ inv_freq, int rotary_dim,
                   const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ tok_pos, PagedKV kv,
                   T* __restrict__ k_cache, T* __restrict__ v_cache, int n_heads, int write_kv, long n_items) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();   // not earlier: the attention kernel behind this one must not start while the product before still runs
   const long item = (long)blockIdx.x * ROPE_WARPS + (threadIdx.x >> 5);
   if (item >= n_items) return;
   const int lane = threadIdx.x & 31;
@@ -93,8 +93,8 @@ __global__ void __launch_bounds__(256)
 rope_store_vec_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ inv_freq, const int32_t* __restrict__ tok_seq,
                       const int32_t* __restrict__ tok_pos, PagedKV kv, T* __restrict__ k_cache, T* __restrict__ v_cache,
                       int n_heads, int write_kv, long n_items) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();   // not earlier: the attention kernel behind this one must not start while the product before still runs
   const long item = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (item >= n_items) return;
   const int hd = kv.head_dim, half = hd / 2, per_head = half / 2;
@@ -178,8 +178,8 @@ rope_store_rows_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ i
                        const int32_t* __restrict__ tok_pos, PagedKV kv, T* __restrict__ k_cache, T* __restrict__ v_cache,
                        int n_heads, int write_kv, long n_items) {
   constexpr int N = Chunk<T>::N;
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();   // not earlier: the attention kernel behind this one must not start while the product before still runs
   const long item = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (item >= n_items) return;
   const int hd = kv.head_dim, half = hd / 2, n_chunks = half / N;
