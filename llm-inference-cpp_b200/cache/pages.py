@@ -49,6 +49,9 @@ class SlotTable:
     def is_live(self, slot: int) -> bool:
         return slot in self._live
 
+    def all_live(self, slots) -> bool:
+        return self._live.issuperset(slots)
+
     @property
     def live(self) -> set:
         return set(self._live)
@@ -106,6 +109,21 @@ class PagePool:
     def pages_needed(self, slot: int, n_new: int) -> int:
         have = len(self._pages[slot])
         return max(0, pages_for(self._length[slot] + n_new, self.page_size) - have)
+
+    def page_events(self, bases):
+        """For sequences of lengths ``bases`` (an integer array) that grow by one position: which of them
+        take a new page, and which give one back (a window's oldest page falling out of reach)."""
+        takes = (bases % self.page_size) == 0
+        if self.window > 0:
+            first_needed = bases - self.window + 1
+            gives = (first_needed > 0) & ((first_needed % self.page_size) == 0)
+        else:
+            gives = takes & False
+        return takes, gives
+
+    def grow_quietly(self, slot: int) -> None:
+        """One more position for a slot whose growth neither takes nor gives a page."""
+        self._length[slot] += 1
 
     def extend(self, slot: int, n_new: int) -> int:
         """Make room for ``n_new`` more positions; returns the position of the first of them."""

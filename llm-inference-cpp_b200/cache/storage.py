@@ -17,6 +17,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 
 from .pages import PAGE_SIZE, CacheError, PagePool, SlotTable, pages_for
@@ -131,6 +132,38 @@ class SequenceCache:
             g.pool.extend(slot, n_new)
         self._length[slot] = base + n_new
         return base
+
+    def extend_each_by_one(self, slots) -> "np.ndarray":
+        """One more position for every slot of ``slots`` (distinct, live): the decode step's growth, with the
+        checks of :meth:`can_extend` and without a loop over the slots that need no page.  Nothing changes
+        if it raises.  Returns the new positions."""
+        if not self.slots.all_live(slots):
+            bad = next(s for s in slots if not self.slots.is_live(s))
+            raise CacheError(f"cache: slot {bad} is not live")
+        length = self._length
+        bases = np.fromiter((length[s] for s in slots), dtype=np.int64, count=len(slots))
+        if int(bases.max()) + 1 > self.max_positions:
+            raise CacheError("sequence longer than the model's context")
+        events = []
+        for g in self.kv_groups:
+            takes, gives = g.pool.page_events(bases)
+            if g.pool.window == 0 and int(takes.sum()) > g.pool.n_free:
+                raise CacheError("cache is full")
+            events.append(takes | gives)
+        for g, ev in zip(self.kv_groups, events):
+            pool = g.pool
+            if ev.any():
+                for s, e in zip(slots, ev):
+                    if e:
+                        pool.extend(s, 1)
+                    else:
+                        pool.grow_quietly(s)
+            else:
+                for s in slots:
+                    pool.grow_quietly(s)
+        for s in slots:
+            length[s] += 1
+        return bases
 
     # -- accounting ------------------------------------------------------------------------
     def check(self) -> None:

@@ -44,10 +44,12 @@ class StepBuffers:
         self.events = [None, None]
         self.turn = 0
         self.dev = None
+        self.serial = 0          # counts staged blocks: tells whether anyone used the buffers in between
 
     def stage(self, n_int32: int):
         """-> (host block to fill, device block); call ``upload`` when the host block is filled."""
         self.turn ^= 1
+        self.serial += 1
         i = self.turn
         if self.events[i] is not None:
             self.events[i].synchronize()
@@ -216,4 +218,55 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
     ctx.seq_q_start, ctx.seq_kv_len, ctx.seq_slot = view("seq_q_start"), view("seq_kv_len"), view("seq_slot")
     for g, start, P in page_layout:
         ctx._pages[id(g)] = dev[start:start + n_seqs * P].view(n_seqs, P)
+    ctx.layout = StepLayout(off, page_layout, cur, host, tuple(slots))
     return ctx
+
+
+@dataclass
+class StepLayout:
+    """Where a step's arrays lie in its index block, and the host block that holds them."""
+    offsets: dict            # name -> (start, count)
+    pages: list              # (group, start, pages per sequence)
+    n_int32: int
+    host: torch.Tensor
+    slots: tuple
+
+
+def continue_decode_step(cache, prev: StepContext, tokens, vocab_size: int, buffers: StepBuffers) -> None:
+    """The index block of a decode step that continues ``prev`` (a decode step of the same slots, padded to
+    the same sizes) by one token each: only the token ids, the positions, the lengths and the page tables
+    change, so the block is copied and patched instead of being planned anew.  The checks are those of
+    :func:`plan_step`.  The caller makes sure that the page tables still fit ``prev``'s width."""
+    lay = prev.layout
+    n_real = len(lay.slots)
+    toks = np.asarray(tokens, dtype=np.int64)
+    if toks.shape != (n_real,):
+        raise StepError("step: one token for each sequence of the step before")
+    if toks.min() < 0 or toks.max() >= vocab_size:
+        bad = int(toks[(toks < 0) | (toks >= vocab_size)][0])
+        raise StepError(f"step: token id {bad} out of range")
+    bases = cache.extend_each_by_one(lay.slots)
+    host, _ = buffers.stage(lay.n_int32)
+    h = host.numpy()
+    h[:lay.n_int32] = lay.host.numpy()[:lay.n_int32]
+    a = lay.offsets["token_ids"][0]
+    h[a:a + n_real] = toks
+    a = lay.offsets["tok_pos"][0]
+    h[a:a + n_real] = bases
+    a = lay.offsets["seq_kv_len"][0]
+    h[a:a + n_real] = bases + 1
+    slot_index = np.asarray(lay.slots, dtype=np.int64)
+    n_seqs = prev.n_seqs
+    for g, start, P in lay.pages:
+        table = h[start:start + n_seqs * P].reshape(n_seqs, P)
+        m = g.pool.matrix
+        if m is not None and P <= m.shape[1] and slot_index.max() < m.shape[0]:
+            table[:n_real] = m[slot_index, :P]
+        else:
+            table[:n_real] = -1
+            for i, slot in enumerate(lay.slots):
+                pages = g.pool.table(slot)
+                table[i, :len(pages)] = pages
+    buffers.upload(lay.n_int32)
+    lay.host = host
+    prev.max_kv_len = int(bases.max()) + 1

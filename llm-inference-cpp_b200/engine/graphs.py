@@ -33,17 +33,33 @@ class DecodeGraphs:
         self.graphs = {}
         self.replays = 0
         self.kernels_per_graph = {}
+        self._last = None        # (cache, page bucket, context, buffer identity) of the step before
 
     def step(self, cache, seqs, sampler, streams=None):
         """A decode step (one token per sequence) followed by the choice; returns device int32 ids
         of the real sequences (valid until the next step)."""
-        from .batch import plan_step
+        from .batch import continue_decode_step, plan_step
         m = self.model
         n_real = len(seqs)
         B = bucket(n_real)
-        need_pages = max((cache.length(s.slot) + 1 + cache.page_size - 1) // cache.page_size for s in seqs)
-        P = max(need_pages, min(bucket(need_pages), cache.max_pages_per_seq))
-        ctx = plan_step(cache, seqs, m.spec.vocab_size, m.buffers, pad_seqs_to=B, pad_pages_to=P)
+        ctx = None
+        last = self._last
+        if last is not None:
+            l_cache, P, l_ctx, l_ident = last
+            slots = l_ctx.layout.slots
+            if (l_cache is cache and slots == tuple(s.slot for s in seqs) and cache.slots.all_live(slots)
+                    and l_ident == (m.rt.generation, m.buffers.dev.data_ptr(), m.buffers.serial)
+                    and (max(cache.length(s) for s in slots) + cache.page_size) // cache.page_size <= P):
+                # the same sequences one token on, and nobody used the index block in between:
+                # patch the step before instead of planning anew
+                continue_decode_step(cache, l_ctx, [s.tokens[0] for s in seqs], m.spec.vocab_size, m.buffers)
+                ctx = l_ctx
+        if ctx is None:
+            self._last = None
+            need_pages = max((cache.length(s.slot) + 1 + cache.page_size - 1) // cache.page_size for s in seqs)
+            P = max(need_pages, min(bucket(need_pages), cache.max_pages_per_seq))
+            ctx = plan_step(cache, seqs, m.spec.vocab_size, m.buffers, pad_seqs_to=B, pad_pages_to=P)
+        self._last = (cache, P, ctx, (m.rt.generation, m.buffers.dev.data_ptr(), m.buffers.serial))
         m._last_h2d = ctx.h2d_bytes
         sampler.prepare(B, streams)
         choice = (sampler.params.temperature, sampler.params.top_k, sampler.params.top_p)

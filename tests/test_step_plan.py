@@ -1,0 +1,115 @@
+"""The index block of a step, checked on the CPU: what plan_step writes, and that the patched block of a
+continued decode step (continue_decode_step) is the block that planning anew would give."""
+import numpy as np
+import pytest
+import torch
+
+from llmi_b200.cache.pages import CacheError
+from llmi_b200.cache.storage import KVRequest, SequenceCache
+from llmi_b200.engine.batch import SequenceStep, StepError, continue_decode_step, plan_step
+
+
+class HostBuffers:
+    """Stands in for StepBuffers without a GPU: two alternating host blocks and a 'device' block."""
+
+    def __init__(self, n=8192):
+        self.hosts = [torch.zeros(n, dtype=torch.int32), torch.zeros(n, dtype=torch.int32)]
+        self.dev = torch.zeros(n, dtype=torch.int32)
+        self.turn = 0
+        self.serial = 0
+
+    def stage(self, n):
+        self.turn ^= 1
+        self.serial += 1
+        self.hosts[self.turn].fill_(-99)            # whatever a block held before must not matter
+        return self.hosts[self.turn], self.dev
+
+    def upload(self, n):
+        self.dev[:n] = self.hosts[self.turn][:n]
+
+
+def make_cache(window=0, n_slots=6, max_tokens=64 * 24):
+    reqs = [(KVRequest(2, 16, 0), 2)]
+    if window:
+        reqs.append((KVRequest(1, 16, window), 1))
+    return SequenceCache(reqs, [], max_tokens=max_tokens, max_positions=1000, dtype=torch.float32, device="meta",
+                         page_size=64, n_slots=n_slots)
+
+
+def test_block_of_a_prompt_step():
+    cache = make_cache()
+    a, b = cache.alloc_slot(), cache.alloc_slot()
+    buf = HostBuffers()
+    ctx = plan_step(cache, [SequenceStep(a, [5, 6, 7], [0, 2]), SequenceStep(b, [9, 8], [1])], 50, buf)
+    assert ctx.token_ids.tolist() == [5, 6, 7, 9, 8]
+    assert ctx.tok_seq.tolist() == [0, 0, 0, 1, 1]
+    assert ctx.tok_pos.tolist() == [0, 1, 2, 0, 1]
+    assert ctx.want_rows.tolist() == [0, 2, 4]
+    assert ctx.seq_q_start.tolist() == [0, 3, 5]
+    assert ctx.seq_kv_len.tolist() == [3, 2]
+    assert ctx.seq_slot.tolist() == [a, b]
+    assert not ctx.decode and ctx.max_kv_len == 3
+    pages = ctx.pages_of(cache.kv_groups[0])
+    assert pages.shape == (2, 1) and pages[0, 0] != pages[1, 0]
+
+
+@pytest.mark.parametrize("window", [0, 100])
+def test_continued_decode_step_equals_planning_anew(window):
+    """Two caches in lockstep: one is stepped by plan_step every time, the other by continue_decode_step.
+    Lengths start near a page's end so that pages are taken (and, with a window, given back) on the way."""
+    caches = [make_cache(window), make_cache(window)]
+    bufs = [HostBuffers(), HostBuffers()]
+    starts = [60, 127, 3, 190]
+    slots = []
+    for c in caches:
+        ss = [c.alloc_slot() for _ in starts]
+        for s, n in zip(ss, starts):
+            c.extend(s, n)
+        slots.append(ss)
+    assert slots[0] == slots[1]
+    rng = np.random.default_rng(0)
+    prev = None
+    for step in range(140):
+        toks = rng.integers(0, 50, len(starts)).tolist()
+        seqs = [SequenceStep(s, [t], [0]) for s, t in zip(slots[0], toks)]
+        ref = plan_step(caches[0], seqs, 50, bufs[0], pad_seqs_to=4, pad_pages_to=8)
+        n = ref.layout.n_int32
+        if prev is None:
+            prev = plan_step(caches[1], seqs, 50, bufs[1], pad_seqs_to=4, pad_pages_to=8)
+        else:
+            continue_decode_step(caches[1], prev, toks, 50, bufs[1])
+        assert prev.layout.n_int32 == n
+        assert torch.equal(bufs[0].dev[:n], bufs[1].dev[:n]), f"step {step}"
+        assert prev.max_kv_len == ref.max_kv_len
+        for c in caches:
+            c.check()
+    for g0, g1 in zip(caches[0].kv_groups, caches[1].kv_groups):
+        assert g0.pool.n_free == g1.pool.n_free
+        for s in slots[0]:
+            assert g0.pool.table(s) == g1.pool.table(s) and g0.pool.length(s) == g1.pool.length(s)
+
+
+def test_continued_decode_step_refusals_change_nothing():
+    cache = make_cache(max_tokens=64 * 2, n_slots=2)
+    a, b = cache.alloc_slot(), cache.alloc_slot()
+    cache.extend(a, 63)
+    cache.extend(b, 64)                  # both pages are taken now; b's next token needs a third
+    buf = HostBuffers()
+    with pytest.raises(CacheError, match="cache is full"):
+        plan_step(cache, [SequenceStep(a, [1], [0]), SequenceStep(b, [1], [0])], 50, buf, pad_seqs_to=2, pad_pages_to=2)
+    cache.free_slot(b)
+    b = cache.alloc_slot()
+    cache.extend(b, 5)
+    ctx = plan_step(cache, [SequenceStep(a, [1], [0]), SequenceStep(b, [1], [0])], 50, buf, pad_seqs_to=2, pad_pages_to=2)
+    assert (cache.length(a), cache.length(b)) == (64, 6)
+    with pytest.raises(StepError, match="out of range"):
+        continue_decode_step(cache, ctx, [1, 50], 50, buf)
+    with pytest.raises(CacheError, match="cache is full"):      # a's next token needs a page, none is free
+        continue_decode_step(cache, ctx, [1, 2], 50, buf)
+    assert (cache.length(a), cache.length(b)) == (64, 6)
+    for g in cache.kv_groups:
+        assert g.pool.length(a) == 64 and g.pool.length(b) == 6
+    cache.check()
+    cache.free_slot(b)
+    with pytest.raises(CacheError, match="not live"):
+        continue_decode_step(cache, ctx, [1, 2], 50, buf)
