@@ -20,6 +20,9 @@
 // exponential is one ex2 instruction); the merge order is fixed, so a sequence's result does not depend
 // on its batch-mates.  `window` > 0 keeps keys pos-window+1..pos.
 //
+// With `fuse` the kernel also does the step's position encoding (rope_store.cu's work for one token per
+// sequence): one kernel less in a decode layer.  The arithmetic is rope_store.cu's, so are the bits.
+//
 // Launched as a programmatic dependent, the kernel starts while the kernels before it still run: of
 // everything it reads, they write only q and the cache row of each sequence's newest position, so the
 // producer fetches older pages at once and waits (griddepcontrol.wait) only before the newest page;
@@ -54,6 +57,17 @@ struct DecodeParams {
   float* partials;           // [n_seqs, n_kv_heads, max_splits, G, HD + 2]
   int* tickets;              // [n_seqs * n_kv_heads], zero between launches
   int* error_flag;
+  // Fused position encoding (optional: fuse == 0 leaves q and the cache as the caller prepared them).
+  // q then points at the step's un-rotated [q | k | v] rows; the kernel rotates q as it reads it, and the
+  // block that holds a sequence-head's newest page rotates the new k and appends it and the new v to that
+  // page before it fetches the page.  rotary_dim is head_dim (whole-head rotate-half) or 0 (append only).
+  int fuse;
+  const float* inv_freq;     // [head_dim / 2] when rotary_dim > 0
+  int rotary_dim;
+  int n_heads;
+  int write_kv;              // 0: the call reads a cache that another call has written
+  __nv_bfloat16* k_cache_w;  // the same caches, writable
+  __nv_bfloat16* v_cache_w;
 };
 
 template <int HD>
@@ -64,7 +78,9 @@ struct DecCfg {
   static constexpr int LPR = HD / 8;          // lanes per key row (16 bytes each)
   static constexpr int RPI = 32 / LPR;        // rows per warp instruction
   static constexpr int NI = 16 / RPI;         // instructions per warp per page (16 keys per warp)
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 128 /*align*/ + 8 * (2 * STAGES + 4) + 64 /*barriers*/;
+  static constexpr int BAR_BYTES = 8 * (2 * STAGES + 4) + 32;
+  static constexpr int ROT_BYTES = STAGES * HD * 4;       // per stage: sin[HD/2], cos[HD/2] of the item that starts there
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 128 /*align*/ + BAR_BYTES + ROT_BYTES;
 };
 
 __device__ __forceinline__ void bf16x8_to_f32(const uint4& raw, float* f) {
@@ -105,6 +121,8 @@ attention_decode_kernel(DecodeParams p, int n_items) {
   auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
   auto rfull_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + b); };
   auto rempty_bar = [&](int b) { return bars + 8u * (2 * C::STAGES + 2 + b); };
+  float* rot_tab = reinterpret_cast<float*>(smem_raw + (base - smem_u32(smem_raw)) + C::STAGES * C::STAGE_BYTES + C::BAR_BYTES);
+  const bool rotate = p.fuse && p.rotary_dim > 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(full_bar(s), 1);
@@ -144,25 +162,80 @@ attention_decode_kernel(DecodeParams p, int n_items) {
   };
 
   if (warp == DEC_CONSUMERS) {
-    // ---- producer ----
-    if (lane == 0) {
-      int it = 0;
-      DecItem d;
-      bool ok = true, waited = false;
-      for (int item = next_item(blockIdx.x, d); item < n_items && ok; item = next_item(item + gridDim.x, d)) {
-        const int32_t* pages = p.seq_pages + (size_t)d.seq * p.pages_stride;
-        for (int i = 0; i < d.n_pages; ++i, ++it) {
-          const int s = it % C::STAGES;
-          if (!waited && (d.pg0 + i + 1) * DEC_PAGE > d.pos) {   // the page of the newest position: written by the kernel before
-            pdl_wait();
-            waited = true;
-          }
-          if (it >= C::STAGES && !mbar_wait(empty_bar(s), ((it / C::STAGES) - 1) & 1, p.error_flag, 11)) { ok = false; break; }
-          const size_t tile = ((size_t)pages[d.pg0 + i] * p.n_kv_heads + d.kvh) * (size_t)(DEC_PAGE * HD);
-          mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
-          bulk_load(base + s * C::STAGE_BYTES, p.k_cache + tile, C::TILE_BYTES, full_bar(s));
-          bulk_load(base + s * C::STAGE_BYTES + C::TILE_BYTES, p.v_cache + tile, C::TILE_BYTES, full_bar(s));
+    // ---- producer (lane 0 issues the copies; the whole warp appends a sequence-head's new k and v) ----
+    int it = 0;
+    DecItem d;
+    bool ok = true, waited = false;
+    for (int item = next_item(blockIdx.x, d); item < n_items && ok; item = next_item(item + gridDim.x, d)) {
+      const int32_t* pages = p.seq_pages + (size_t)d.seq * p.pages_stride;
+      for (int i = 0; i < d.n_pages && ok; ++i, ++it) {
+        const int s = it % C::STAGES;
+        const bool newest = (d.pg0 + i + 1) * DEC_PAGE > d.pos;   // the page of the newest position
+        if (newest && !waited) {     // written by the kernel before (or, fused, made of what it wrote)
+          pdl_wait();
+          waited = true;
         }
+        constexpr int HALF = HD / 2;
+        if (rotate && (i == 0 || newest)) {
+          // sines and cosines of this sequence's position: for the consumers (q), left in the slot of the
+          // item's first stage, and for the new key below.  The slot is free: its stage's last reader released it.
+          if (i == 0 && it >= C::STAGES && lane == 0 &&
+              !mbar_wait(empty_bar(s), ((it / C::STAGES) - 1) & 1, p.error_flag, 15))
+            ok = false;
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) break;
+        }
+        float sn[(HALF + 31) / 32], cs[(HALF + 31) / 32];
+        if (rotate && (i == 0 || newest)) {
+#pragma unroll
+          for (int u = 0; u < (HALF + 31) / 32; ++u) {
+            const int j = lane + 32 * u;
+            if (j < HALF) {
+              sincosf((float)d.pos * p.inv_freq[j], &sn[u], &cs[u]);
+              if (i == 0) {
+                rot_tab[s * HD + j] = sn[u];
+                rot_tab[s * HD + HALF + j] = cs[u];
+              }
+            }
+          }
+          __syncwarp();      // lane 0's arrive on the stage's barrier below publishes the table
+        }
+        if (newest && p.fuse && p.write_kv) {
+          const __nv_bfloat16* row = p.q + (size_t)d.tok * p.ldq;
+          const __nv_bfloat16* ksrc = row + (size_t)(p.n_heads + d.kvh) * HD;
+          const __nv_bfloat16* vsrc = row + (size_t)(p.n_heads + p.n_kv_heads + d.kvh) * HD;
+          const size_t dst = (((size_t)pages[d.pos / DEC_PAGE] * p.n_kv_heads + d.kvh) * DEC_PAGE + (d.pos % DEC_PAGE)) * HD;
+#pragma unroll
+          for (int u = 0; u < (HALF + 31) / 32; ++u) {
+            const int j = lane + 32 * u;
+            if (j < HALF) {
+              if (rotate) {
+                const float a = __bfloat162float(ksrc[j]), b = __bfloat162float(ksrc[j + HALF]);
+                p.k_cache_w[dst + j] = __float2bfloat16_rn(rot_lo(a, b, cs[u], sn[u]));
+                p.k_cache_w[dst + j + HALF] = __float2bfloat16_rn(rot_hi(a, b, cs[u], sn[u]));
+              } else {
+                p.k_cache_w[dst + j] = ksrc[j];
+                p.k_cache_w[dst + j + HALF] = ksrc[j + HALF];
+              }
+              p.v_cache_w[dst + j] = vsrc[j];
+              p.v_cache_w[dst + j + HALF] = vsrc[j + HALF];
+            }
+          }
+          // the bulk copy below reads these rows through the async proxy
+          __threadfence();
+          asm volatile("fence.proxy.async;" ::: "memory");
+          __syncwarp();
+        }
+        if (lane == 0) {
+          if (it >= C::STAGES && !mbar_wait(empty_bar(s), ((it / C::STAGES) - 1) & 1, p.error_flag, 11)) ok = false;
+          if (ok) {
+            const size_t tile = ((size_t)pages[d.pg0 + i] * p.n_kv_heads + d.kvh) * (size_t)(DEC_PAGE * HD);
+            mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+            bulk_load(base + s * C::STAGE_BYTES, p.k_cache + tile, C::TILE_BYTES, full_bar(s));
+            bulk_load(base + s * C::STAGE_BYTES + C::TILE_BYTES, p.v_cache + tile, C::TILE_BYTES, full_bar(s));
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       }
     }
     return;
@@ -272,22 +345,25 @@ attention_decode_kernel(DecodeParams p, int n_items) {
   DecItem d, dn;
   int item = next_item(blockIdx.x, d);
   uint4 q_raw[G], q_next[G];
+  constexpr int HALF_CHUNKS = C::LPR / 2;
   pdl_wait();   // q comes from the kernels before
   if (item < n_items) {
 #pragma unroll
-    for (int g = 0; g < G; ++g)
-      q_raw[g] = *reinterpret_cast<const uint4*>(p.q + (size_t)d.tok * p.ldq + (size_t)(d.kvh * G + g) * HD + c * 8);
+    for (int g = 0; g < G; ++g) {
+      const __nv_bfloat16* qh = p.q + (size_t)d.tok * p.ldq + (size_t)(d.kvh * G + g) * HD;
+      q_raw[g] = *reinterpret_cast<const uint4*>(qh + c * 8);
+    }
   }
   while (item < n_items && ok) {
     const int item_next = next_item(item + gridDim.x, dn);
     if (item_next < n_items) {     // the next item's q is fetched while this item's pages are worked on
 #pragma unroll
-      for (int g = 0; g < G; ++g)
-        q_next[g] = *reinterpret_cast<const uint4*>(p.q + (size_t)dn.tok * p.ldq + (size_t)(dn.kvh * G + g) * HD + c * 8);
+      for (int g = 0; g < G; ++g) {
+        const __nv_bfloat16* qh = p.q + (size_t)dn.tok * p.ldq + (size_t)(dn.kvh * G + g) * HD;
+        q_next[g] = *reinterpret_cast<const uint4*>(qh + c * 8);
+      }
     }
     float q[G][8];
-#pragma unroll
-    for (int g = 0; g < G; ++g) bf16x8_to_f32(q_raw[g], q[g]);
     float m[G], l[G], acc[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -300,6 +376,33 @@ attention_decode_kernel(DecodeParams p, int n_items) {
       const int s = it % C::STAGES;
       ok = mbar_wait(full_bar(s), (it / C::STAGES) & 1, p.error_flag, 12);
       if (!ok) break;
+      if (i == 0) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) bf16x8_to_f32(q_raw[g], q[g]);
+        if (rotate) {
+          // rotate-half on this lane's 8 dims: (a, b) = (first-half value, second-half value) of each pair; the
+          // partner chunk in the other half of the head is held by the lane HALF_CHUNKS away; sines and cosines
+          // come from the producer warp (in the slot of this first stage); the result is rounded to bf16 as
+          // the separate kernel would have stored it
+          const float* tab = rot_tab + s * HD + (c % HALF_CHUNKS) * 8;
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            uint4 pair;
+            pair.x = __shfl_xor_sync(0xffffffffu, q_raw[g].x, HALF_CHUNKS);
+            pair.y = __shfl_xor_sync(0xffffffffu, q_raw[g].y, HALF_CHUNKS);
+            pair.z = __shfl_xor_sync(0xffffffffu, q_raw[g].z, HALF_CHUNKS);
+            pair.w = __shfl_xor_sync(0xffffffffu, q_raw[g].w, HALF_CHUNKS);
+            float other[8];
+            bf16x8_to_f32(pair, other);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float sn = tab[e], cs = tab[HD / 2 + e];
+              const float r = c < HALF_CHUNKS ? rot_lo(q[g][e], other[e], cs, sn) : rot_hi(other[e], q[g][e], cs, sn);
+              q[g][e] = __bfloat162float(__float2bfloat16_rn(r));
+            }
+          }
+        }
+      }
       const uint32_t k_tile = base + s * C::STAGE_BYTES, v_tile = k_tile + C::TILE_BYTES;
       const int page_pos0 = (d.pg0 + i) * DEC_PAGE;
       const bool inside = page_pos0 >= d.lo && page_pos0 + DEC_PAGE - 1 <= d.pos;   // every key of the page counts
@@ -466,6 +569,16 @@ int launch_decode(const DecodeParams& p, int n_seqs, cudaStream_t stream) {
   return launch_pdl(PDL_ATTENTION, attention_decode_kernel<HD, G>, grid, DEC_THREADS, C::SMEM_BYTES, stream, p, (int)n_items);
 }
 
+static int dispatch_decode(const DecodeParams& p, int n_seqs, int head_dim, int group, cudaStream_t stream) {
+#define LLMI_DEC(HD, G) \
+  if (head_dim == HD && group == G) return launch_decode<HD, G>(p, n_seqs, stream)
+  LLMI_DEC(64, 1); LLMI_DEC(64, 2); LLMI_DEC(64, 3); LLMI_DEC(64, 4); LLMI_DEC(64, 8);
+  LLMI_DEC(128, 1); LLMI_DEC(128, 2); LLMI_DEC(128, 3); LLMI_DEC(128, 4); LLMI_DEC(128, 8);
+  LLMI_DEC(32, 1); LLMI_DEC(32, 2); LLMI_DEC(32, 4);
+#undef LLMI_DEC
+  return LLMI_ERR_UNSUPPORTED;
+}
+
 }  // namespace llmi
 
 using namespace llmi;
@@ -504,14 +617,37 @@ LLMI_EXPORT int llmi_attention_decode(const void* q, long ldq, void* out, long l
     return LLMI_ERR_BAD_SIZE;
   DecodeParams p{(const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)k_cache,
                  (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads,
-                 scale * 1.4426950408889634f, window, pages_per_split, splits, partials, tickets, error_flag};
-#define LLMI_DEC(HD, G) \
-  if (head_dim == HD && group == G) return launch_decode<HD, G>(p, n_seqs, stream)
-  LLMI_DEC(64, 1); LLMI_DEC(64, 2); LLMI_DEC(64, 3); LLMI_DEC(64, 4); LLMI_DEC(64, 8);
-  LLMI_DEC(128, 1); LLMI_DEC(128, 2); LLMI_DEC(128, 3); LLMI_DEC(128, 4); LLMI_DEC(128, 8);
-  LLMI_DEC(32, 1); LLMI_DEC(32, 2); LLMI_DEC(32, 4);
-#undef LLMI_DEC
-  return LLMI_ERR_UNSUPPORTED;
+                 scale * 1.4426950408889634f, window, pages_per_split, splits, partials, tickets, error_flag,
+                 0, nullptr, 0, n_heads, 0, nullptr, nullptr};
+  return dispatch_decode(p, n_seqs, head_dim, group, stream);
+}
+
+// The same with the step's position encoding fused in: `qkv` holds the un-rotated [q | k | v] rows of the
+// step's tokens (one per sequence); q is rotated as it is read, and the new k (rotated) and v are appended
+// to the cache before the page they land in is fetched.  rotary_dim: head_dim (rotate-half over the whole
+// head, inv_freq[head_dim/2]) or 0 (append only).  write_kv 0: the cache already holds the new entries.
+LLMI_EXPORT int llmi_attention_decode_fused(const void* qkv, long ldq, void* out, long ldo, void* k_cache, void* v_cache,
+                                            const int32_t* seq_pages, int pages_stride, const int32_t* seq_kv_len,
+                                            const int32_t* seq_q_start, int n_seqs, int n_heads, int n_kv_heads,
+                                            int head_dim, float scale, int window, int max_pages, int pages_per_split,
+                                            const float* inv_freq, int rotary_dim, int write_kv, float* partials,
+                                            long partials_floats, int* tickets, int n_tickets, int* error_flag,
+                                            cudaStream_t stream) {
+  if (n_seqs <= 0 || n_heads <= 0 || n_kv_heads <= 0 || max_pages <= 0 || pages_per_split <= 0) return LLMI_ERR_BAD_SIZE;
+  if (n_heads % n_kv_heads) return LLMI_ERR_BAD_SIZE;
+  const int group = n_heads / n_kv_heads;
+  if (!llmi_attention_decode_supported(head_dim, group)) return LLMI_ERR_UNSUPPORTED;
+  if (rotary_dim != 0 && (rotary_dim != head_dim || !inv_freq)) return LLMI_ERR_UNSUPPORTED;
+  if (((uintptr_t)qkv & 15) || (ldq & 7) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15)) return LLMI_ERR_ALIGN;
+  const int splits = (max_pages + pages_per_split - 1) / pages_per_split;
+  if (llmi_attention_decode_workspace(n_seqs, n_heads, head_dim, max_pages, pages_per_split) > partials_floats ||
+      (long)n_seqs * n_kv_heads > n_tickets)
+    return LLMI_ERR_BAD_SIZE;
+  DecodeParams p{(const __nv_bfloat16*)qkv, ldq, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)k_cache,
+                 (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads,
+                 scale * 1.4426950408889634f, window, pages_per_split, splits, partials, tickets, error_flag,
+                 1, inv_freq, rotary_dim, n_heads, write_kv ? 1 : 0, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache};
+  return dispatch_decode(p, n_seqs, head_dim, group, stream);
 }
 
 LLMI_EXPORT int llmi_attention_decode_resident(int head_dim, int group) {
@@ -582,14 +718,9 @@ LLMI_EXPORT int llmi_attention_decode_static(const void* q, long ldq, void* out,
   const int splits = (max_pages + pages_per_split - 1) / pages_per_split;
   DecodeParams p{(const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, ldo, (const __nv_bfloat16*)k_cache,
                  (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads,
-                 scale * 1.4426950408889634f, window, pages_per_split, splits, sc->partials, sc->tickets, &sc->error};
-  int rc = LLMI_ERR_UNSUPPORTED;
-#define LLMI_DEC(HD, G) \
-  if (head_dim == HD && group == G) rc = launch_decode<HD, G>(p, n_seqs, stream)
-  LLMI_DEC(64, 1); LLMI_DEC(64, 2); LLMI_DEC(64, 3); LLMI_DEC(64, 4); LLMI_DEC(64, 8);
-  LLMI_DEC(128, 1); LLMI_DEC(128, 2); LLMI_DEC(128, 3); LLMI_DEC(128, 4); LLMI_DEC(128, 8);
-  LLMI_DEC(32, 1); LLMI_DEC(32, 2); LLMI_DEC(32, 4);
-#undef LLMI_DEC
+                 scale * 1.4426950408889634f, window, pages_per_split, splits, sc->partials, sc->tickets, &sc->error,
+                 0, nullptr, 0, n_heads, 0, nullptr, nullptr};
+  const int rc = dispatch_decode(p, n_seqs, head_dim, group, stream);
   if (rc != LLMI_OK) return rc;
   if (error_out && cudaMemcpyAsync(error_out, &sc->error, sizeof(int), cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
     return LLMI_ERR_LAUNCH;

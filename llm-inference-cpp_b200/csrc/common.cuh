@@ -69,6 +69,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// The rotation of one pair, with its roundings spelled out so that every kernel that rotates gives the
+// same bits whatever the compiler would contract: the result must not depend on which kernel a step's
+// size selects.
+__device__ __forceinline__ float rot_lo(float a, float b, float c, float s) { return __fmaf_rn(a, c, -__fmul_rn(b, s)); }
+__device__ __forceinline__ float rot_hi(float a, float b, float c, float s) { return __fmaf_rn(b, c, __fmul_rn(a, s)); }
 inline int launch_status() { return cudaPeekAtLastError() == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH; }
 
 // Programmatic dependent launch.  A kernel launched with launch_pdl may start while the kernel before

@@ -17,11 +17,6 @@ namespace llmi {
 
 constexpr int MAX_HALF = 256;
 
-// The rotation of one pair, with its roundings spelled out so that every kernel of this file gives the
-// same bits whatever the compiler would contract: the result must not depend on which kernel a step's
-// size selects.
-__device__ __forceinline__ float rot_lo(float a, float b, float c, float s) { return __fmaf_rn(a, c, -__fmul_rn(b, s)); }
-__device__ __forceinline__ float rot_hi(float a, float b, float c, float s) { return __fmaf_rn(b, c, __fmul_rn(a, s)); }
 constexpr int ROPE_WARPS = 4;
 constexpr int ROWS_MIN_TOKENS = 256;   // from here on the kernel that shares sines and cosines among the heads pays
 

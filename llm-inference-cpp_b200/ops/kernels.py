@@ -9,6 +9,7 @@ they raise.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_double, c_float, c_int, c_long, c_void_p
 
 import torch
@@ -84,6 +85,7 @@ def lib():
         for name in ("llmi_embed", "llmi_rmsnorm", "llmi_swiglu", "llmi_linear_simt", "llmi_rope_store",
                      "llmi_attention_generic", "llmi_argmax", "llmi_sample", "llmi_gemm_tc", "llmi_gemm_tc_splits",
                      "llmi_attention_decode", "llmi_attention_decode_supported", "llmi_attention_decode_resident",
+                     "llmi_attention_decode_fused",
                      "llmi_attention_prefill", "llmi_attention_prefill_supported", "llmi_gemm_skinny",
                      "llmi_gemm_skinny_max_tokens", "llmi_attention_prefill_tc", "llmi_attention_prefill_tc_supported"):
             getattr(l, name).restype = c_int
@@ -216,8 +218,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch
 
 
 SKINNY_MAX_TOKENS = 16
-_FORCE_SIMT = __import__("os").environ.get("LLMI_LINEAR", "") == "simt"
-_NO_SKINNY = __import__("os").environ.get("LLMI_LINEAR", "") == "tc"
+_FORCE_SIMT = os.environ.get("LLMI_LINEAR", "") == "simt"
+_NO_SKINNY = os.environ.get("LLMI_LINEAR", "") == "tc"
 
 
 def gemm_bf16(x, w, out, bias=None, mode: int = OUT_STORE) -> None:
@@ -387,26 +389,67 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, s
 
 # Which prompt-attention kernel runs for head size 64: "mma" (mma.sync, the faster of the two as measured:
 # 114 against 142 us for a 2,048-token prompt of 32 heads) or "tc" (tcgen05, kept selectable and tested).
-_PREFILL_ATTENTION = __import__("os").environ.get("LLMI_PREFILL_ATTENTION", "mma")
-_FORCE_GENERIC_ATTENTION = __import__("os").environ.get("LLMI_ATTENTION", "") == "generic"
+_PREFILL_ATTENTION = os.environ.get("LLMI_PREFILL_ATTENTION", "mma")
+_FORCE_GENERIC_ATTENTION = os.environ.get("LLMI_ATTENTION", "") == "generic"
+
+
+def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start,
+                           n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int, partials: torch.Tensor,
+                           pages_per_split: int, inv_freq, rotary_dim: int, write_kv: bool) -> None:
+    """:func:`attention_decode` with the step's position encoding done by the same kernel: ``qkv`` holds the
+    un-rotated [q | k | v] row of each sequence's token; the new k (rotated) and v are appended to the cache."""
+    _need_cuda(qkv, out, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start, partials)
+    S, P = seq_pages.shape
+    assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+    assert qkv.stride(1) == 1 and out.stride(1) == 1 and k_cache.shape[-2] == 64 and partials.dtype == torch.float32
+    assert rotary_dim == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2)
+    sc = tc_scratch(qkv.device)
+    _check("attention_decode_fused", lib().llmi_attention_decode_fused(
+        _ptr(qkv), c_long(qkv.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(seq_pages),
+        c_int(seq_pages.stride(0)), _ptr(seq_kv_len), _ptr(seq_q_start), c_int(S), c_int(n_heads), c_int(n_kv_heads),
+        c_int(head_dim), c_float(scale), c_int(window), c_int(P), c_int(pages_per_split),
+        _ptr(inv_freq) if rotary_dim else None, c_int(rotary_dim), c_int(1 if write_kv else 0), _ptr(partials),
+        c_long(partials.numel()), _ptr(sc.attn_tickets), c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), _stream()))
+
+
+_FUSE_ROPE = os.environ.get("LLMI_FUSE_ROPE", "1") != "0"
+
+
+def _decode_kernel_applies(qkv, ctx, seq_pages, page_size, n_heads, n_kv_heads, head_dim, rt) -> bool:
+    return bool(ctx.decode and qkv.dtype == torch.bfloat16 and page_size == 64 and rt is not None
+                and not _FORCE_GENERIC_ATTENTION and seq_pages.shape[0] * n_kv_heads <= _TcScratch.N_ATTN_TICKETS
+                and attention_decode_supported(head_dim, n_heads // n_kv_heads))
+
+
+def attention_fuses_rotation(qkv, ctx, seq_pages, page_size, n_heads, n_kv_heads, head_dim, rotary_dim, rt) -> bool:
+    """Whether :func:`attention` can do this step's rotation and cache append itself (``rope=``): a decode
+    step that goes to the split kernel, rotating the whole head or nothing."""
+    return bool(_FUSE_ROPE and rotary_dim in (0, head_dim)
+                and _decode_kernel_applies(qkv, ctx, seq_pages, page_size, n_heads, n_kv_heads, head_dim, rt))
 
 
 def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_pages, page_size: int, n_heads: int,
-              n_kv_heads: int, head_dim: int, scale: float, window: int = 0, rt=None) -> None:
+              n_kv_heads: int, head_dim: int, scale: float, window: int = 0, rt=None, rope=None) -> None:
     """Attention of a step's tokens over the cache; q is the first n_heads*head_dim columns of ``qkv``.
 
     In bf16, a decode step goes to the split kernel and a prompt step to the flash kernel when they
     have the head size; everything else (the 32-bit path, other head sizes) goes to the generic kernel.
+    ``rope=(inv_freq, rotary_dim, write_kv)``: q, k are not rotated yet and k, v not appended — the kernel
+    does it (only where :func:`attention_fuses_rotation` says so).
     """
-    if (ctx.decode and qkv.dtype == torch.bfloat16 and page_size == 64 and rt is not None and not _FORCE_GENERIC_ATTENTION
-            and seq_pages.shape[0] * n_kv_heads <= _TcScratch.N_ATTN_TICKETS
-            and attention_decode_supported(head_dim, n_heads // n_kv_heads)):
+    if _decode_kernel_applies(qkv, ctx, seq_pages, page_size, n_heads, n_kv_heads, head_dim, rt):
         S, P = seq_pages.shape
         pps = decode_pages_per_split(S, n_kv_heads, P, head_dim, n_heads // n_kv_heads)
         partials = rt.scratch("attn_partials", (attention_decode_workspace(S, n_heads, head_dim, P, pps),), torch.float32)
-        attention_decode(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_kv_len, ctx.seq_q_start, n_heads, n_kv_heads,
-                         head_dim, scale, window, partials, pps)
+        if rope is not None:
+            attention_decode_fused(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_kv_len, ctx.seq_q_start, n_heads,
+                                   n_kv_heads, head_dim, scale, window, partials, pps, rope[0], rope[1], rope[2])
+        else:
+            attention_decode(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_kv_len, ctx.seq_q_start, n_heads, n_kv_heads,
+                             head_dim, scale, window, partials, pps)
         return
+    if rope is not None:
+        raise RuntimeError("attention: rotation can only be fused into the decode kernel (ask attention_fuses_rotation)")
     if (not ctx.decode and qkv.dtype == torch.bfloat16 and page_size == 64 and not _FORCE_GENERIC_ATTENTION
             and attention_prefill_supported(head_dim)):
         if head_dim == 64 and _PREFILL_ATTENTION == "tc" and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:

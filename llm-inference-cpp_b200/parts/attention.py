@@ -63,9 +63,15 @@ class GQAttention:
         nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         qkv = self.rt.scratch("qkv", (T, (nh + 2 * nkv) * hd))
         kernels.linear(h, self.w_qkv, qkv, self.b_qkv)
-        self.position.rotate_and_store(qkv, ctx, binding, nh, nkv, hd)
         attn = self.rt.scratch("attn_out", (T, nh * hd))
         g = binding.group
-        kernels.attention(qkv, attn, g.k[binding.index], g.v[binding.index], ctx, ctx.pages_of(g), g.page_size,
-                          nh, nkv, hd, self.scale, self.window, rt=self.rt)
+        pages = ctx.pages_of(g)
+        fused = self.position.fused_rotation()
+        if fused is not None and kernels.attention_fuses_rotation(qkv, ctx, pages, g.page_size, nh, nkv, hd, fused[1], self.rt):
+            rope = (fused[0], fused[1], binding.writes)        # a decode step: the attention kernel rotates and appends
+        else:
+            rope = None
+            self.position.rotate_and_store(qkv, ctx, binding, nh, nkv, hd)
+        kernels.attention(qkv, attn, g.k[binding.index], g.v[binding.index], ctx, pages, g.page_size,
+                          nh, nkv, hd, self.scale, self.window, rt=self.rt, rope=rope)
         kernels.linear(attn, self.w_o, x, None, kernels.OUT_ADD_F32)

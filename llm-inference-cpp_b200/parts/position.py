@@ -28,6 +28,14 @@ class PositionEncoding:
     def at_embedding(self, x, ctx) -> None:
         """Hook after the embedding lookup; the default adds nothing."""
 
+    def fused_rotation(self):
+        """(inv_freq, rotary_dim) if all this part does to q, k, v is the rotation of pairs and the append that
+        :meth:`rotate_and_store` does — a mixer may then let its attention kernel do both; None for a
+        subclass with a ``rotate_and_store`` of its own."""
+        if type(self).rotate_and_store is not PositionEncoding.rotate_and_store:
+            return None
+        return self.inv_freq, self.rotary_dim
+
     def rotate_and_store(self, qkv, ctx, binding, n_heads, n_kv_heads, head_dim) -> None:
         """Rotate q (in place) and k by position and append k, v to the call's cache pages."""
         g = binding.group

@@ -167,6 +167,10 @@ def test_rope_store_long_prompt_same_bits(dtype, nh, nkv, hd):
                            torch.from_numpy(o[t, (nh + nkv) * hd:].reshape(nkv, hd)))
 
 
+def P_inv(hd, theta=23456.0):
+    return P.rope_inv_freq(hd, theta)
+
+
 def plain_attention_rows(q, keys, vals, group, scale, window):
     """q [nh, hd] at the last position of keys/vals [n, nkv, hd]."""
     out = np.zeros_like(q)
@@ -381,6 +385,59 @@ def test_attention_decode_ragged(nh, nkv, hd, pps, window):
         ref = plain_attention_rows(q[s_, :nh * hd].double().cpu().numpy().reshape(nh, hd), keys[:n].double().numpy(),
                                    vals[:n].double().numpy(), nh // nkv, scale, window)
         assert rel(out[s_].reshape(nh, hd), torch.from_numpy(ref)) < 1e-2, (s_, n)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(32, 32, 64), (15, 5, 64), (8, 2, 128), (8, 8, 32), (16, 2, 64)])
+@pytest.mark.parametrize("pps,window,rot,write", [(1, 0, True, True), (4, 0, True, True), (64, 0, False, True),
+                                                  (2, 200, True, True), (4, 0, True, False)])
+def test_attention_decode_fused_rotation_same_bits(nh, nkv, hd, pps, window, rot, write):
+    """The decode kernel with the position encoding fused in (q rotated on the fly, the new k and v appended
+    by the block that reads their page) gives the bits of the two kernels it replaces: outputs and caches."""
+    kk = K()
+    rng = np.random.default_rng(2)
+    lens = [1, 64, 65, 700, 0, 129, 1000, 128]       # lengths AFTER this step (0: padding)
+    P, n_pages = 16, 56
+    gen = torch.Generator().manual_seed(3)
+    kc, vc = paged(n_pages, nkv, hd, "bfloat16")
+    perm = rng.permutation(n_pages).tolist()
+    pages = torch.full((len(lens), P), -1, dtype=torch.int32)
+    for s_, n in enumerate(lens):
+        for pg_i in range((n + 63) // 64):
+            pg = perm.pop()
+            pages[s_, pg_i] = pg
+            m_ = min(64, n - 1 - 64 * pg_i)           # positions before the newest one are in the cache already
+            if m_ > 0:
+                kc[pg, :, :m_] = torch.randn(nkv, m_, hd, generator=gen).to(torch.bfloat16).cuda()
+                vc[pg, :, :m_] = torch.randn(nkv, m_, hd, generator=gen).to(torch.bfloat16).cuda()
+    S = len(lens)
+    qkv = torch.randn(S, (nh + 2 * nkv) * hd, generator=gen).to(torch.bfloat16).cuda()
+    kvlen = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    qstart = torch.arange(S, dtype=torch.int32, device="cuda")
+    tok_seq = torch.tensor([i if n > 0 else -1 for i, n in enumerate(lens)], dtype=torch.int32, device="cuda")
+    tok_pos = torch.tensor([max(n - 1, 0) for n in lens], dtype=torch.int32, device="cuda")
+    inv = torch.from_numpy(P_inv(hd)).cuda() if rot else None
+    rdim = hd if rot else 0
+    scale = 1 / math.sqrt(hd)
+    part = torch.empty(kk.attention_decode_workspace(S, nh, hd, P, pps), device="cuda")
+    pages_d = pages.cuda()
+    # two kernels: rotate and append, then attend
+    q2, kc2, vc2 = qkv.clone(), kc.clone(), vc.clone()
+    out2 = torch.full((S, nh * hd), 7.0, device="cuda", dtype=torch.bfloat16)
+    kk.rope_store(q2, inv, rdim, tok_seq, tok_pos, pages_d, 64, kc2, vc2, nh, nkv, hd, True)
+    kk.attention_decode(q2, out2, kc2, vc2, pages_d, kvlen, qstart, nh, nkv, hd, scale, window, part, pps)
+    # one kernel (write=False: the cache holds the new entries already, as for a call that reads another call's cache)
+    q1 = qkv.clone()
+    kc1, vc1 = (kc.clone(), vc.clone()) if write else (kc2.clone(), vc2.clone())
+    out1 = torch.full((S, nh * hd), 7.0, device="cuda", dtype=torch.bfloat16)
+    for _ in range(2):      # a second run over the cache it has written itself gives the same
+        kk.attention_decode_fused(q1, out1, kc1, vc1, pages_d, kvlen, qstart, nh, nkv, hd, scale, window, part, pps,
+                                  inv, rdim, write)
+    kk.check_device_errors("cuda:0")
+    assert torch.equal(q1, qkv)                                  # the fused kernel leaves its input alone
+    assert torch.equal(out1, out2)
+    assert torch.equal(torch.nan_to_num(kc1.float(), nan=-7.0), torch.nan_to_num(kc2.float(), nan=-7.0))
+    assert torch.equal(torch.nan_to_num(vc1.float(), nan=-7.0), torch.nan_to_num(vc2.float(), nan=-7.0))
+    assert int(kk.tc_scratch("cuda:0").attn_tickets.abs().sum()) == 0
 
 
 @pytest.mark.parametrize("kernel", ["mma", "tc"])
