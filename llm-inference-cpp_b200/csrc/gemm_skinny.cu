@@ -13,6 +13,12 @@
 //   * at the end of a row tile the four partial sums are added in warp order through shared memory and
 //     the epilogue (bias, store / fp32 store / residual add / silu(gate)·up on interleaved rows) writes
 //     token-major output.
+// Two optional extras fold the RMSNorm between two products of a decode layer into them (a norm of 8 rows is
+// all launch and latency).  The product BEFORE the norm (residual add) also writes, for the x it has just
+// updated, h = bf16(norm_weight * x) and the sum of x^2 over its 16 rows, per tile and token; the product
+// AFTER the norm takes h as its input, adds the tiles' sums in tile order, and multiplies its accumulators
+// by 1/sqrt(sum/k + eps) before the bias: y = scale * (h . W) is the normalised product with the scale
+// applied in fp32 at the end instead of before the rounding of h.
 // Blocks are persistent over row tiles and the ring runs on across tiles.  The k order of the additions is
 // fixed (it does not depend on the number of tokens), and programmatic dependent launch lets the first
 // weight tiles be requested before the kernel that produces x has finished.
@@ -29,6 +35,8 @@ constexpr int SK_STAGES = 6;
 constexpr int SK_CONSUMERS = 4;
 constexpr int SK_THREADS = (SK_CONSUMERS + 1) * 32;
 
+constexpr int SK_SS_STRIDE = 32;     // floats per tile in the sums of squares (tokens <= 32)
+
 constexpr int SK_STORE = 0, SK_STORE_F32 = 1, SK_ADD_F32 = 2, SK_SWIGLU = 3;
 
 struct SkinnyParams {
@@ -38,6 +46,15 @@ struct SkinnyParams {
   const float* bias;
   int mode;
   int* error_flag;
+  // the norm AFTER this product (mode SK_ADD_F32 only): null or
+  const float* emit_w;        // [m_out] weight of that norm
+  __nv_bfloat16* emit_h;      // [n_tok, emit_ldh]: bf16(emit_w * x_new)
+  long emit_ldh;
+  float* emit_ss;             // [m_tiles, SK_SS_STRIDE]: sum over the tile's rows of x_new^2, per token
+  // the norm BEFORE this product: null or
+  const float* in_ss;         // [in_tiles, SK_SS_STRIDE] as written by the product before
+  int in_tiles;
+  float in_eps;
 };
 
 // One copy fetches [4 k slices][rows][64 k]: the matrix is seen as a 3-D tensor (k within a slice, row, slice).
@@ -66,6 +83,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
   extern __shared__ uint8_t smem_raw[];
   __shared__ float s_part[SK_CONSUMERS][32][NT * 4];
+  __shared__ float s_scale[NPAD];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bars = base + SK_STAGES * STAGE_BYTES;
   auto full_bar = [&](int s) { return bars + 8u * s; };
@@ -120,6 +138,23 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   // ---- consumers ----
   pdl_wait();   // the output (residual add) and the bias of a previous layer's step are safe to touch from here
+  if (p.in_ss) {
+    // scale of each token's row: the tiles' sums of squares added in tile order (one partial sum per thread
+    // over every (128 / NPAD)-th tile, then those in thread order), as the norm kernel would: 1/sqrt(mean + eps)
+    constexpr int PARTS = SK_CONSUMERS * 32 / NPAD;
+    float* red = &s_part[0][0][0];        // free until the first tile's end
+    const int tok = threadIdx.x % NPAD, part = threadIdx.x / NPAD;
+    float a = 0.f;
+    for (int t = part; t < p.in_tiles; t += PARTS) a += __ldcg(&p.in_ss[(size_t)t * SK_SS_STRIDE + tok]);
+    red[part * NPAD + tok] = a;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (threadIdx.x < NPAD) {
+      float sum = 0.f;
+      for (int q = 0; q < PARTS; ++q) sum += red[q * NPAD + threadIdx.x];
+      s_scale[threadIdx.x] = 1.0f / sqrtf(sum / (float)p.k + p.in_eps);
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+  }
   int it = 0;
   bool ok = true;
   const int g = lane >> 2, tq = lane & 3;
@@ -174,6 +209,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       for (int idx = threadIdx.x; idx < NPAD * 8; idx += SK_CONSUMERS * 32) {
         const int tok = idx >> 3, f = idx & 7;
         if (tok >= p.n_tok || m0 + 2 * f + 1 >= p.m_out) continue;
+        const float sc = p.in_ss ? s_scale[tok] : 1.0f;
         float gu[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -182,25 +218,41 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           float v = 0.f;
 #pragma unroll
           for (int w = 0; w < SK_CONSUMERS; ++w) v += s_part[w][ln][n * 4 + e];
-          gu[h] = v;
+          gu[h] = v * sc;
         }
         ((__nv_bfloat16*)p.out)[(size_t)tok * p.ldo + (m0 >> 1) + f] =
             __float2bfloat16_rn(__fdividef(gu[0], 1.0f + __expf(-gu[0])) * gu[1]);
       }
     } else {
+      // NPAD * 16 is a multiple of the 128 consumer threads: every thread makes the same number of rounds, and
+      // the 16 rows of one token sit in 16 neighbouring lanes (the sum of squares below relies on both)
       for (int idx = threadIdx.x; idx < NPAD * SK_ROWS; idx += SK_CONSUMERS * 32) {
         const int tok = idx >> 4, row = idx & 15;
         const int m = m0 + row;
-        if (tok >= p.n_tok || m >= p.m_out) continue;
+        const bool live = tok < p.n_tok && m < p.m_out;
         const int ln = (row & 7) * 4 + ((tok & 7) >> 1), e = (row >> 3) * 2 + (tok & 1), n = tok >> 3;
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < SK_CONSUMERS; ++w) v += s_part[w][ln][n * 4 + e];
-        if (p.bias) v += p.bias[m];
-        const size_t o = (size_t)tok * p.ldo + m;
-        if (p.mode == SK_STORE) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
-        else if (p.mode == SK_STORE_F32) ((float*)p.out)[o] = v;
-        else ((float*)p.out)[o] += v;
+        if (p.in_ss) v *= s_scale[tok];
+        float xn = 0.f;
+        if (live) {
+          if (p.bias) v += p.bias[m];
+          const size_t o = (size_t)tok * p.ldo + m;
+          if (p.mode == SK_STORE) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
+          else if (p.mode == SK_STORE_F32) ((float*)p.out)[o] = v;
+          else {
+            xn = ((float*)p.out)[o] + v;
+            ((float*)p.out)[o] = xn;
+          }
+        }
+        if (p.emit_w) {      // only with SK_ADD_F32
+          if (live) p.emit_h[(size_t)tok * p.emit_ldh + m] = __float2bfloat16_rn(p.emit_w[m] * xn);
+          float sq = xn * xn;
+#pragma unroll
+          for (int o = 8; o >= 1; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+          if (row == 0) p.emit_ss[(size_t)t * SK_SS_STRIDE + tok] = sq;
+        }
       }
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");   // s_part is free for the next tile
@@ -262,20 +314,28 @@ LLMI_EXPORT int llmi_gemm_skinny_max_tokens() { return 32; }
 
 // y[n_tok, m_out] (mode) = x[n_tok, k] · w[m_out, k]ᵀ + bias for n_tok <= 32 and k % 64 == 0; bf16 inputs; pitches in elements;
 // modes as llmi_gemm_tc (0 store, 1 fp32 store, 2 fp32 add, 3 gated with alternating gate/up rows).
+// emit_w/emit_h/emit_ss (mode 2 only, or all null): also write h = bf16(emit_w * y_new) and the per-tile sums of
+// y_new^2, emit_ss[ceil(m_out/16), 32].  in_ss/in_tiles/in_eps (or null): x is such an h; the accumulators are
+// multiplied by 1/sqrt(sum of the tiles' sums / k + in_eps) before the bias.
 LLMI_EXPORT int llmi_gemm_skinny(const void* x, long ldx, const void* w, long ldw, const float* bias, void* y, long ldy,
-                                 int n_tok, int m_out, int k, int mode, int* error_flag, cudaStream_t stream) {
+                                 int n_tok, int m_out, int k, int mode, const float* emit_w, void* emit_h, long emit_ldh,
+                                 float* emit_ss, const float* in_ss, int in_tiles, float in_eps, int* error_flag,
+                                 cudaStream_t stream) {
   if (n_tok <= 0 || n_tok > 32 || m_out <= 0 || k <= 0) return LLMI_ERR_BAD_SIZE;
   if (mode < 0 || mode > 3) return LLMI_ERR_UNSUPPORTED;
   if (mode == SK_SWIGLU && ((m_out & 1) || bias)) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (ldw & 7)) return LLMI_ERR_ALIGN;
   if (k % 64) return LLMI_ERR_UNSUPPORTED;   // the 3-D view of the matrices needs whole 64-wide k slices
+  if (emit_w && (mode != SK_ADD_F32 || !emit_h || !emit_ss)) return LLMI_ERR_UNSUPPORTED;
+  if (in_ss && in_tiles <= 0) return LLMI_ERR_BAD_SIZE;
   const int nt = n_tok <= 8 ? 1 : (n_tok <= 16 ? 2 : 4);
   CUtensorMap mw, mx;
   int rc = sk_make_map(&mw, w, m_out, k, ldw, SK_ROWS);
   if (rc != LLMI_OK) return rc;
   rc = sk_make_map(&mx, x, n_tok, k, ldx, nt * 8);
   if (rc != LLMI_OK) return rc;
-  SkinnyParams p{m_out, n_tok, k, y, ldy, bias, mode, error_flag};
+  SkinnyParams p{m_out, n_tok, k, y, ldy, bias, mode, error_flag, emit_w, (__nv_bfloat16*)emit_h, emit_ldh, emit_ss,
+                 in_ss, in_tiles, in_eps};
   const int m_tiles = (m_out + SK_ROWS - 1) / SK_ROWS;
   if (nt == 1) return launch_skinny<1>(mw, mx, p, m_tiles, stream);
   if (nt == 2) return launch_skinny<2>(mw, mx, p, m_tiles, stream);

@@ -122,8 +122,17 @@ class Model:
         x = self.embedding.forward(ctx.token_ids, ctx)
         if trace is not None:
             trace.append(x.clone())
-        for call, binding in zip(self.spec.schedule, cache.bindings):
-            self.layers[call.layer].block.forward(x, ctx, binding)
+        # A block may hand the next one its first norm half done (norm deferral, see parts/block.py): `entry`
+        # is that norm's deferred form, filled by the block before; blocks without the extras run as ever.
+        blocks = [self.layers[call.layer].block for call in self.spec.schedule]
+        entry = None
+        for i, (block, binding) in enumerate(zip(blocks, cache.bindings)):
+            if hasattr(block, "entry_norm"):
+                nxt = getattr(blocks[i + 1], "entry_norm", None) if i + 1 < len(blocks) else None
+                entry = block.forward(x, ctx, binding, entry=entry, next_norm=nxt)
+            else:
+                block.forward(x, ctx, binding)
+                entry = None
             if trace is not None:
                 trace.append(x.clone())
         if trace is not None:

@@ -200,9 +200,37 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Ten
         c_int(sc.N_TICKETS), _ptr(sc.error), _stream()))
 
 
+class DeferredNorm:
+    """A row-wise norm y = weight * x / sqrt(mean(x^2) + eps) split over the two products around it.
+
+    The product that last updates x (a residual add) fills ``h`` = compute-type(weight * x) and ``ss`` — the sum
+    of x^2 over each 16-row tile of its output, per token — and the product that reads the norm's output
+    takes ``h`` as its input and multiplies its accumulators by 1/sqrt(sum(ss)/width + eps).  A norm of a
+    handful of rows is all launch and latency; this way it costs no kernel.  Made by a norm part
+    (``deferred``), filled by ``linear(..., then_norm=)``, consumed by passing it as ``linear``'s input.
+    """
+    SS_STRIDE = 32
+
+    def __init__(self, weight: torch.Tensor, eps: float, h: torch.Tensor, ss: torch.Tensor):
+        self.weight, self.eps, self.h, self.ss = weight, float(eps), h, ss
+        self.n_tiles = (h.shape[1] + 15) // 16
+        assert ss.dtype == torch.float32 and ss.numel() >= self.n_tiles * self.SS_STRIDE and weight.dtype == torch.float32
+
+    @property
+    def shape(self):
+        return self.h.shape
+
+    @property
+    def dtype(self):
+        return self.h.dtype
+
+
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
-                mode: int = OUT_STORE) -> None:
-    """The same product for at most 32 tokens: the weight-streaming kernel (``csrc/gemm_skinny.cu``)."""
+                mode: int = OUT_STORE, then_norm: DeferredNorm | None = None, scale_from: DeferredNorm | None = None) -> None:
+    """The same product for at most 32 tokens: the weight-streaming kernel (``csrc/gemm_skinny.cu``).
+
+    ``then_norm`` (mode OUT_ADD_F32): also fill that deferred norm from the updated ``out``.
+    ``scale_from``: ``x`` is that deferred norm's ``h``; apply its scale to the accumulators."""
     _need_cuda(x, w, out, bias)
     M, K = x.shape
     N = w.shape[0]
@@ -211,33 +239,64 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch
     assert out.dtype == (torch.bfloat16 if mode in (OUT_STORE, OUT_SWIGLU) else torch.float32)
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == N
+    if then_norm is not None:
+        assert mode == OUT_ADD_F32 and then_norm.h.shape == (M, N) and then_norm.h.dtype == torch.bfloat16
+        assert then_norm.weight.numel() == N and then_norm.h.stride(1) == 1
+    if scale_from is not None:
+        assert scale_from.h.data_ptr() == x.data_ptr() and scale_from.h.shape == (M, K)
     sc = tc_scratch(x.device)
+    e, f = then_norm, scale_from
     _check("gemm_skinny", lib().llmi_gemm_skinny(
         _ptr(x), c_long(x.stride(0)), _ptr(w), c_long(w.stride(0)), _ptr(bias), _ptr(out), c_long(out.stride(0)),
-        c_int(M), c_int(N), c_int(K), c_int(mode), _ptr(sc.error), _stream()))
+        c_int(M), c_int(N), c_int(K), c_int(mode),
+        _ptr(e.weight if e else None), _ptr(e.h if e else None), c_long(e.h.stride(0) if e else 0), _ptr(e.ss if e else None),
+        _ptr(f.ss if f else None), c_int(f.n_tiles if f else 0), c_float(f.eps if f else 0.0),
+        _ptr(sc.error), _stream()))
 
 
 SKINNY_MAX_TOKENS = 16
 _FORCE_SIMT = os.environ.get("LLMI_LINEAR", "") == "simt"
 _NO_SKINNY = os.environ.get("LLMI_LINEAR", "") == "tc"
+_FUSE_NORM = os.environ.get("LLMI_FUSE_NORM", "1") != "0"
 
 
-def gemm_bf16(x, w, out, bias=None, mode: int = OUT_STORE) -> None:
+def skinny_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the product x·wᵀ goes to the weight-streaming kernel."""
+    return bool(not _FORCE_SIMT and not _NO_SKINNY and gemm_tc_eligible(x, w) and x.shape[0] <= SKINNY_MAX_TOKENS
+                and x.shape[1] % 64 == 0)
+
+
+def norm_deferrable(n_tokens: int, width: int, dtype) -> bool:
+    """Whether a norm over ``width`` of ``n_tokens`` rows can be split over the products around it."""
+    return bool(_FUSE_NORM and not _FORCE_SIMT and not _NO_SKINNY and dtype == torch.bfloat16
+                and n_tokens <= SKINNY_MAX_TOKENS and width % 64 == 0)
+
+
+def gemm_bf16(x, w, out, bias=None, mode: int = OUT_STORE, then_norm: DeferredNorm | None = None) -> bool:
     """The bf16 tensor-core product: the weight-streaming kernel for a handful of tokens, the tcgen05
-    kernel for more."""
-    if x.shape[0] <= SKINNY_MAX_TOKENS and x.shape[1] % 64 == 0 and not _NO_SKINNY:
-        gemm_skinny(x, w, out, bias, mode)
-    else:
-        gemm_tc(x, w, out, bias, mode)
+    kernel for more.  ``x`` may be a filled :class:`DeferredNorm`; returns whether ``then_norm`` was filled."""
+    pending = x if isinstance(x, DeferredNorm) else None
+    xin = pending.h if pending is not None else x
+    if skinny_applies(xin, w):
+        gemm_skinny(xin, w, out, bias, mode, then_norm, pending)
+        return then_norm is not None
+    if pending is not None:
+        raise KernelError("a deferred norm can only feed the weight-streaming product")
+    gemm_tc(xin, w, out, bias, mode)
+    return False
 
 
-def linear(x, w, out, bias=None, mode: int = OUT_STORE) -> None:
-    """The matrix product of the step: the tensor-core kernel for bf16 operands it can take (16-byte
-    aligned rows), the fp32 FMA kernel for the 32-bit path and for everything else."""
-    if not _FORCE_SIMT and gemm_tc_eligible(x, w):
-        gemm_bf16(x, w, out, bias, mode)
-    else:
-        linear_simt(x, w, out, bias, mode)
+def linear(x, w, out, bias=None, mode: int = OUT_STORE, then_norm: DeferredNorm | None = None) -> bool:
+    """The matrix product of the step: the tensor-core kernels for bf16 operands they can take (16-byte
+    aligned rows), the fp32 FMA kernel for the 32-bit path and for everything else.  ``x`` may be a filled
+    :class:`DeferredNorm`; returns whether ``then_norm`` was filled (False: run that norm the plain way)."""
+    xin = x.h if isinstance(x, DeferredNorm) else x
+    if not _FORCE_SIMT and gemm_tc_eligible(xin, w):
+        return gemm_bf16(x, w, out, bias, mode, then_norm)
+    if isinstance(x, DeferredNorm):
+        raise KernelError("a deferred norm can only feed the weight-streaming product")
+    linear_simt(x, w, out, bias, mode)
+    return False
 
 
 def rope_store(qkv: torch.Tensor, inv_freq: torch.Tensor | None, rotary_dim: int, tok_seq, tok_pos, seq_pages,

@@ -58,7 +58,9 @@ class GQAttention:
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_qkv, self.w_o))
 
-    def forward(self, h, x, ctx, binding) -> None:
+    defers_norm = True
+
+    def forward(self, h, x, ctx, binding, then_norm=None) -> bool:
         T = h.shape[0]
         nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
         qkv = self.rt.scratch("qkv", (T, (nh + 2 * nkv) * hd))
@@ -74,4 +76,4 @@ class GQAttention:
             self.position.rotate_and_store(qkv, ctx, binding, nh, nkv, hd)
         kernels.attention(qkv, attn, g.k[binding.index], g.v[binding.index], ctx, pages, g.page_size,
                           nh, nkv, hd, self.scale, self.window, rt=self.rt, rope=rope)
-        kernels.linear(attn, self.w_o, x, None, kernels.OUT_ADD_F32)
+        return kernels.linear(attn, self.w_o, x, None, kernels.OUT_ADD_F32, then_norm)

@@ -35,10 +35,12 @@ class SwiGLU:
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
-    def forward(self, h, x, ctx) -> None:
+    defers_norm = True
+
+    def forward(self, h, x, ctx, then_norm=None) -> bool:
         T = h.shape[0]
         act = self.rt.scratch("ffn_act", (T, self.inner))
-        if self.fused_gate and kernels.gemm_tc_eligible(h, self.w_gate_up):
+        if self.fused_gate and kernels.gemm_tc_eligible(getattr(h, "h", h), self.w_gate_up):
             kernels.gemm_bf16(h, self.w_gate_up, act, None, kernels.OUT_SWIGLU)
         else:
             if self.fused_gate:
@@ -46,4 +48,4 @@ class SwiGLU:
             gate_up = self.rt.scratch("ffn_gate_up", (T, 2 * self.inner))
             kernels.linear(h, self.w_gate_up, gate_up)
             kernels.swiglu(gate_up, act)
-        kernels.linear(act, self.w_down, x, None, kernels.OUT_ADD_F32)
+        return kernels.linear(act, self.w_down, x, None, kernels.OUT_ADD_F32, then_norm)

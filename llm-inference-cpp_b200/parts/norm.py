@@ -2,6 +2,8 @@
 computes it (scale first, then weight; plain weight, not 1 + weight), the sum of squares in fp32."""
 from __future__ import annotations
 
+import torch
+
 from ..ops import kernels
 from .registry import TensorDecl, part
 
@@ -26,3 +28,14 @@ class RMSNorm:
         out = self.rt.scratch(scratch_name, (n, self.width))
         kernels.rmsnorm(x, self.weight, out, self.eps, rows)
         return out
+
+    def deferred(self, n_tokens: int, name: str):
+        """This norm for ``n_tokens`` rows as a :class:`kernels.DeferredNorm` — to be filled by the product
+        that updates x and read by the product after the norm — or None when the step's size or type does
+        not allow it (then :meth:`forward` is the way).  ``name`` keeps apart the buffers of norms that are
+        in flight at the same time."""
+        if not kernels.norm_deferrable(n_tokens, self.width, self.rt.dtype):
+            return None
+        h = self.rt.scratch(name + "_h", (n_tokens, self.width))
+        ss = self.rt.scratch(name + "_ss", ((self.width + 15) // 16, kernels.DeferredNorm.SS_STRIDE), torch.float32)
+        return kernels.DeferredNorm(self.weight, self.eps, h, ss)

@@ -167,6 +167,53 @@ def test_rope_store_long_prompt_same_bits(dtype, nh, nkv, hd):
                            torch.from_numpy(o[t, (nh + nkv) * hd:].reshape(nkv, hd)))
 
 
+@pytest.mark.parametrize("T,H,K1,M2,mode2", [(5, 320, 192, 96, 0), (8, 2048, 128, 512, 3), (13, 192, 448, 64, 1), (1, 64, 64, 48, 2)])
+def test_deferred_norm_between_two_products(T, H, K1, M2, mode2):
+    """A norm split over the products around it: the first (residual add) also writes weight*x and the tiles'
+    sums of squares, the second scales its accumulators.  Against the plain formulas in float64."""
+    kk = K()
+    gen = torch.Generator(device="cuda").manual_seed(T * H)
+    a = torch.randn(T, K1, device="cuda", generator=gen).to(torch.bfloat16)
+    w1 = (torch.randn(H, K1, device="cuda", generator=gen) * 0.1).to(torch.bfloat16)
+    b1 = torch.randn(H, device="cuda", generator=gen) * 0.1
+    x = torch.randn(T, H, device="cuda", generator=gen) * 2
+    nw = 1 + 0.2 * torch.randn(H, device="cuda", generator=gen)
+    w2 = (torch.randn(M2, H, device="cuda", generator=gen) * 0.1).to(torch.bfloat16)
+    eps = 3e-5
+    x_ref = x.double() + a.double() @ w1.double().T + b1.double()
+    d = kk.DeferredNorm(nw, eps, torch.full((T, H), float("nan"), device="cuda", dtype=torch.bfloat16),
+                        torch.full(((H + 15) // 16, 32), float("nan"), device="cuda"))
+    assert kk.linear(a, w1, x, b1, kk.OUT_ADD_F32, then_norm=d)
+    assert rel(x, x_ref) < 1e-6 * 50
+    assert rel(d.h, nw.double() * x_ref) < 5e-3
+    assert rel(d.ss[:, :T].sum(0), (x_ref ** 2).sum(1)) < 1e-5
+    normed = nw.double() * (x_ref / torch.sqrt((x_ref ** 2).mean(1, keepdim=True) + eps))
+    if mode2 == 3:
+        out = torch.empty(T, M2 // 2, device="cuda", dtype=torch.bfloat16)
+        kk.gemm_bf16(d, w2, out, None, kk.OUT_SWIGLU)
+        y = normed @ w2.double().T
+        g, u = y[:, 0::2], y[:, 1::2]
+        ref = g / (1 + torch.exp(-g)) * u
+    elif mode2 == 2:
+        out = torch.ones(T, M2, device="cuda")
+        kk.linear(d, w2, out, None, kk.OUT_ADD_F32)
+        ref = 1 + normed @ w2.double().T
+    else:
+        out = torch.empty(T, M2, device="cuda", dtype=torch.bfloat16 if mode2 == 0 else torch.float32)
+        b2 = torch.randn(M2, device="cuda", generator=gen)
+        kk.linear(d, w2, out, b2, mode2)
+        ref = normed @ w2.double().T + b2.double()
+    kk.check_device_errors("cuda:0")
+    assert rel(out, ref) < 1e-2
+    # and against the norm kernel followed by the same product: the same up to the rounding of h
+    hn = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+    kk.rmsnorm(x, nw, hn, eps)
+    if mode2 in (0, 1):
+        out2 = torch.empty_like(out)
+        kk.linear(hn, w2, out2, b2, mode2)
+        assert rel(out, out2) < 1e-2
+
+
 def P_inv(hd, theta=23456.0):
     return P.rope_inv_freq(hd, theta)
 
