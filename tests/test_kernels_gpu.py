@@ -346,7 +346,8 @@ def test_sample_distribution():
 
 
 @pytest.mark.parametrize("n_tok,m_out,k", [(1, 200, 72), (5, 64, 64), (16, 128, 64), (17, 384, 120), (70, 129, 1000),
-                                           (300, 520, 136), (64, 2048, 8192), (8, 256, 4096), (1000, 136, 264)])
+                                           (300, 520, 136), (64, 2048, 8192), (8, 256, 4096), (1000, 136, 264),
+                                           (33, 300, 2048), (100, 2048, 2048), (20, 640, 512), (128, 136, 1024)])
 def test_gemm_tc_all_modes(n_tok, m_out, k):
     """The tcgen05 product against fp64 on ragged shapes, with and without split-K."""
     kk = K()
@@ -368,7 +369,7 @@ def test_gemm_tc_all_modes(n_tok, m_out, k):
     # the same rows whatever else is in the call (a row's value does not depend on the batch)
     y1 = torch.empty(1, m_out, device="cuda")
     kk.gemm_tc(x[n_tok - 1:], w, y1, None, kk.OUT_STORE_F32)
-    if kk.lib().llmi_gemm_tc_splits(n_tok, m_out, k) == kk.lib().llmi_gemm_tc_splits(1, m_out, k):
+    if kk.lib().llmi_gemm_tc_k_per_cta(n_tok, m_out, k) == kk.lib().llmi_gemm_tc_k_per_cta(1, m_out, k):
         assert torch.equal(y1, y32[n_tok - 1:])
     else:
         assert rel(y1, y32[n_tok - 1:]) < 1e-5
@@ -541,7 +542,8 @@ def test_attention_prefill_ragged(nh, nkv, hd, window, kernel):
             assert rel(got, torch.from_numpy(ref)) < 1.5e-2, (s_, row)
 
 
-@pytest.mark.parametrize("n_tok,inner,k", [(1, 100, 72), (8, 8192, 2048), (70, 176, 64), (300, 320, 120), (2048, 512, 256)])
+@pytest.mark.parametrize("n_tok,inner,k", [(1, 100, 72), (8, 8192, 2048), (70, 176, 64), (300, 320, 120), (2048, 512, 256),
+                                           (40, 1024, 1024), (24, 72, 2048), (100, 300, 768)])
 def test_gemm_tc_gated_epilogue(n_tok, inner, k):
     """silu(gate)·up finished inside the product, rows alternating gate and up; with and without split-K."""
     kk = K()
