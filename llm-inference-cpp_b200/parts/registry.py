@@ -20,6 +20,20 @@ Every member also has ``declare(spec) -> {local tensor name: TensorDecl}`` (a
 classmethod: what it reads from the weight file under ``spec.prefix``) and is
 constructed as ``cls(spec, tensors, rt, **context)`` with its declared tensors.
 No part knows which model it is in.
+
+Optional extras, for fusions that cross two parts.  A part without them works unchanged; the caller falls
+back to the plain path.
+
+``position``   ``fused_rotation() -> (inv_freq, rotary_dim) | None``: all the part does to q, k, v is the
+               rotation of pairs and the append of ``rotate_and_store``, so a mixer may let its attention
+               kernel do both.
+``norm``       ``deferred(n_tokens, name) -> kernels.DeferredNorm | None``: the norm split over the products
+               around it (the one before fills it, the one after applies the scale).
+``mixer``/``ffn``  class attribute ``defers_norm = True``: ``forward`` accepts a filled ``DeferredNorm`` as
+               ``h`` and a keyword ``then_norm=`` (a ``DeferredNorm`` to fill with the part's last,
+               residual-adding product) and returns whether it filled it.
+``block``      property ``entry_norm`` (the norm it applies first, if the block before may fill its deferred
+               form) and ``forward(x, ctx, binding, entry=None, next_norm=None) -> DeferredNorm | None``.
 """
 from __future__ import annotations
 
