@@ -56,11 +56,13 @@ class ClockSampler:
 
     def __init__(self):
         self.rows, self.proc = [], None
+        self.begin = self.end = None
 
     def start(self):
+        """Start sampling (the tool takes a moment to come up: call this before the warm-up)."""
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
-                                          "-i", "0", "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-i", "0", "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -69,15 +71,25 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([x.strip() for x in line.split(",")])
 
+    def mark_begin(self):
+        self.begin = len(self.rows)
+
+    def mark_end(self):
+        self.end = len(self.rows)
+
     def stop(self):
         if self.proc is not None:
             self.proc.terminate()
-        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
-        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        rows = self.rows[self.begin:self.end] if self.begin is not None and self.end is not None else self.rows
+        where = "timed region"
+        if not rows:                      # a region shorter than one sampling period: the samples around it
+            rows, where = self.rows[max(0, (self.begin or 0) - 2):(self.end or 0) + 2], "around the timed region"
+        sm = sorted(int(r[0]) for r in rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in rows if len(r) > 1 and r[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        reasons = sorted({n for r in rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
-                "samples": len(sm)}
+                "samples": len(sm), "sampled": where}
 
 
 def fill_cache(cache, model, batch, start_len):
@@ -117,7 +129,7 @@ def decode_run(model, batch, context, steps, warmup, e2e=False, clocks=None):
         if i == warmup:
             torch.cuda.synchronize()
             if clocks:
-                clocks.start()
+                clocks.mark_begin()
             launches0 = kernels.launch_count()
             e0.record()
         seqs = [SequenceStep(s, [t], [0]) for s, t in zip(slots, toks)]
@@ -131,6 +143,8 @@ def decode_run(model, batch, context, steps, warmup, e2e=False, clocks=None):
             model._graphs.step(cache, seqs, sampler)
     e1.record()
     torch.cuda.synchronize()
+    if clocks:
+        clocks.mark_end()
     ms = e0.elapsed_time(e1) / steps
     launches = kernels.launch_count() - launches0
     kernels.check_device_errors(model.device)
@@ -173,7 +187,7 @@ def prefill_flops(cfg, layers, T):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the full model (named in config)")
@@ -214,6 +228,7 @@ def main():
         return 0
 
     clocks = ClockSampler()
+    clocks.start()
     ms, launches, _, _, cache_bytes = decode_run(model, args.batch, args.context, steps, warmup, clocks=clocks)
     clock_info = clocks.stop()
     value = args.batch * 1000.0 / ms

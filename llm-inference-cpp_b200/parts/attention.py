@@ -15,7 +15,7 @@ import torch
 
 from ..cache.storage import KVRequest
 from ..ops import kernels
-from .registry import TensorDecl, get_part, part
+from .registry import TensorDecl, nested_build, nested_declare, part
 
 
 @part("mixer", "gqa")
@@ -32,6 +32,7 @@ class GQAttention:
         if p.get("bias", False):
             d.update({"q_proj.bias": TensorDecl((q,), "bias"), "k_proj.bias": TensorDecl((kv,), "bias"),
                       "v_proj.bias": TensorDecl((kv,), "bias")})
+        d.update(nested_declare("position", p["position"]))      # a position part may have tensors of its own
         return d
 
     def __init__(self, spec, tensors, rt, **_):
@@ -49,8 +50,7 @@ class GQAttention:
         if p.get("bias", False):
             self.b_qkv = rt.to_f32(torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]]))
         self.w_o = rt.to_compute(tensors["o_proj.weight"])
-        pos_spec = p["position"]
-        self.position = get_part("position", pos_spec.kind)(pos_spec, {}, rt)
+        self.position = nested_build("position", p["position"], tensors, rt)
 
     def cache_request(self):
         return KVRequest(self.n_kv_heads, self.head_dim, self.window)

@@ -9,21 +9,27 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels
-from .registry import TensorDecl, part
+from .registry import TensorDecl, nested_build, nested_declare, part
 
 
 @part("embedding", "token_table")
 class TokenTable:
-    """params: ``vocab``, ``width``.  tensors: ``weight [vocab, width]``."""
+    """params: ``vocab``, ``width``, optional ``position`` (a PartSpec of the position family whose
+    ``at_embedding`` acts on the looked-up rows).  tensors: ``weight [vocab, width]`` and the position part's."""
 
     @classmethod
     def declare(cls, spec):
-        return {"weight": TensorDecl((spec.params["vocab"], spec.params["width"]), "table")}
+        d = {"weight": TensorDecl((spec.params["vocab"], spec.params["width"]), "table")}
+        if spec.params.get("position") is not None:
+            d.update(nested_declare("position", spec.params["position"]))
+        return d
 
     def __init__(self, spec, tensors, rt, **_):
         self.rt = rt
         self.vocab, self.width = int(spec.params["vocab"]), int(spec.params["width"])
         self.weight = rt.to_compute(tensors["weight"])
+        pos = spec.params.get("position")
+        self.position = nested_build("position", pos, tensors, rt) if pos is not None else None
 
     def table(self):
         return self.weight
@@ -34,6 +40,8 @@ class TokenTable:
     def forward(self, token_ids, ctx):
         x = self.rt.scratch("residual", (token_ids.shape[0], self.width), torch.float32)
         kernels.embed(self.weight, token_ids, x)
+        if self.position is not None:
+            self.position.at_embedding(x, ctx)
         return x
 
 

@@ -6,9 +6,10 @@ Families and what the engine calls on their members (``rt`` is the
 ``[tokens, width]``, ``h`` a normalised copy of it in the compute type):
 
 ``norm``       ``forward(x, rows=None) -> h``
-``position``   ``at_embedding(x, ctx)`` (may add to ``x``; default nothing) and
-               ``rotate_and_store(qkv, ctx, binding, n_heads, n_kv_heads, head_dim)``
-               for mixers that keep keys and values
+``position``   held by another part through its params (``"position": PartSpec``), with tensors of its
+               own if it declares any: by a mixer that keeps keys and values, which calls
+               ``rotate_and_store(qkv, ctx, binding, n_heads, n_kv_heads, head_dim)``, or by the
+               embedding, which calls ``at_embedding(x, ctx)`` after the lookup (may add to ``x``)
 ``mixer``      ``cache_request() -> KVRequest | StateRequest | None`` and
                ``forward(h, x, ctx, binding)``: adds its output to ``x``
 ``ffn``        ``forward(h, x, ctx)``: adds its output to ``x``
@@ -63,6 +64,18 @@ def get_part(family: str, kind: str) -> type:
     except KeyError:
         known = ", ".join(sorted(_PARTS.get(family, {}))) or "none"
         raise KeyError(f"no {family} part of kind {kind!r} is registered (known: {known})") from None
+
+
+def nested_declare(family: str, ps) -> dict:
+    """The tensors of a part that another part holds in its params (a mixer's or an embedding's position
+    part): its own declarations under its own prefix, which is relative to the holder's."""
+    return {ps.prefix + name: decl for name, decl in get_part(family, ps.kind).declare(ps).items()}
+
+
+def nested_build(family: str, ps, tensors: dict, rt, **context):
+    """Build such a part from the holder's tensors (see :func:`nested_declare`)."""
+    cls = get_part(family, ps.kind)
+    return cls(ps, {name: tensors[ps.prefix + name] for name in cls.declare(ps)}, rt, **context)
 
 
 def part(family: str, kind: str):

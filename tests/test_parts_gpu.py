@@ -321,3 +321,108 @@ def test_attention_mixer_part_alone(dtype, nh, nkv, hd, bias):
     a = P.attention(P.rope(q, np.arange(n), inv), P.rope(k, np.arange(n), inv), v).reshape(n, nh * hd)
     ref = P.linear(a, w64["o_proj.weight"])
     assert H.rel_to_max(got, ref) < (2e-5 if dtype == torch.float32 else 1.5e-2)
+
+
+# -- a feed-forward with routing and another position encoding, both defined here ------------------
+
+def test_toy_routed_ffn_and_learned_positions(tmp_path):
+    """Two more toy parts registered from outside the library: a feed-forward that routes every token to
+    the best of three experts (router logits in 32-bit) and a position encoding that is a learned table
+    added after the embedding lookup (held by the embedding part, with a tensor of its own; keys are
+    stored unrotated).  The library's model, cache, step and replay run them unchanged; whole prompts,
+    token-by-token decoding and unequal batches agree with the plain formulas."""
+    import llmi_b200 as L
+    from llmi_b200.config.registry import Architecture
+    from llmi_b200.parts import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorDecl
+    from llmi_b200.parts.position import PositionEncoding
+    from llmi_b200.parts.registry import register_part
+
+    W, NH, NKV, HD, F, V, E, MAXPOS = 64, 4, 2, 16, 48, 120, 3, 256
+
+    class LearnedPositions(PositionEncoding):
+        @classmethod
+        def declare(cls, spec):
+            return {"table": TensorDecl((spec.params["max_pos"], spec.params["width"]), "table")}
+
+        def __init__(self, spec, tensors, rt, **_):
+            self.table = rt.to_f32(tensors["table"])
+
+        def at_embedding(self, x, ctx):
+            live = ctx.tok_seq >= 0                                   # padding tokens stay zero
+            x[live] += self.table[ctx.tok_pos[live].long()]
+
+    class Top1Experts:
+        @classmethod
+        def declare(cls, spec):
+            w, f, e = spec.params["width"], spec.params["inner"], spec.params["experts"]
+            d = {"router.weight": TensorDecl((e, w))}
+            for i in range(e):
+                d[f"experts.{i}.up.weight"] = TensorDecl((f, w))
+                d[f"experts.{i}.down.weight"] = TensorDecl((w, f))
+            return d
+
+        def __init__(self, spec, tensors, rt, **_):
+            self.e = spec.params["experts"]
+            self.router = rt.to_f32(tensors["router.weight"])
+            self.up = [rt.to_f32(tensors[f"experts.{i}.up.weight"]) for i in range(self.e)]
+            self.down = [rt.to_f32(tensors[f"experts.{i}.down.weight"]) for i in range(self.e)]
+
+        def forward(self, h, x, ctx):
+            h = h.float()
+            choice = (h @ self.router.T).argmax(dim=1)                 # router logits in 32-bit
+            for i in range(self.e):                                    # experts in a fixed order
+                rows = (choice == i).nonzero().flatten()
+                if rows.numel():
+                    x[rows] += torch.relu(h[rows] @ self.up[i].T) @ self.down[i].T
+
+    register_part("position", "toy_learned", LearnedPositions, replace=True)
+    register_part("ffn", "toy_top1", Top1Experts, replace=True)
+
+    def toy_spec(c):
+        layers = tuple(LayerSpec("prenorm", PartSpec("rms", {"width": W, "eps": 1e-5}, f"l{i}.n1."),
+                                 PartSpec("gqa", {"width": W, "n_heads": NH, "n_kv_heads": NKV, "head_dim": HD, "bias": False,
+                                                  "position": PartSpec("none", {})}, f"l{i}.attn."),
+                                 PartSpec("rms", {"width": W, "eps": 1e-5}, f"l{i}.n2."),
+                                 PartSpec("toy_top1", {"width": W, "inner": F, "experts": E}, f"l{i}.moe.")) for i in range(2))
+        emb = PartSpec("token_table", {"vocab": V, "width": W,
+                                       "position": PartSpec("toy_learned", {"max_pos": MAXPOS, "width": W}, "pos.")}, "emb.")
+        return ModelSpec("ToyRoutedLM", V, W, MAXPOS, emb, layers, (ScheduleEntry(0), ScheduleEntry(1)),
+                         PartSpec("rms", {"width": W, "eps": 1e-5}, "final."),
+                         PartSpec("linear_head", {"vocab": V, "width": W, "tied": False}, "head."))
+
+    L.register_architecture(Architecture("ToyRoutedLM", lambda root: dict(root), toy_spec), replace=True)
+    L.write_random_model(str(tmp_path), {"architectures": ["ToyRoutedLM"]}, 11, torch.float32)
+    model = L.load(str(tmp_path), "float32")
+    w = P.read_safetensors(str(tmp_path / "model.safetensors"))
+    assert w["emb.pos.table"].shape == (MAXPOS, W) and w["l1.moe.experts.2.down.weight"].shape == (W, F)
+
+    used = set()
+
+    def plain(tokens):
+        T = len(tokens)
+        x = P.embedding(w["emb.weight"], tokens) + w["emb.pos.table"][:T].astype(np.float64)
+        for i in range(2):
+            p = f"l{i}."
+            h = P.rmsnorm(x, w[p + "n1.weight"], 1e-5)
+            q = P.linear(h, w[p + "attn.q_proj.weight"]).reshape(T, NH, HD)
+            k = P.linear(h, w[p + "attn.k_proj.weight"]).reshape(T, NKV, HD)
+            v = P.linear(h, w[p + "attn.v_proj.weight"]).reshape(T, NKV, HD)
+            x = x + P.linear(P.attention(q, k, v, 0).reshape(T, NH * HD), w[p + "attn.o_proj.weight"])
+            h = P.rmsnorm(x, w[p + "n2.weight"], 1e-5)
+            choice = P.linear(h, w[p + "moe.router.weight"]).argmax(axis=1)
+            for t in range(T):
+                e = int(choice[t])
+                used.add((i, e))
+                up = np.maximum(P.linear(h[t:t + 1], w[p + f"moe.experts.{e}.up.weight"]), 0)
+                x[t] = x[t] + P.linear(up, w[p + f"moe.experts.{e}.down.weight"])[0]
+        return P.linear(P.rmsnorm(x, w["final.weight"], 1e-5), w["head.weight"])
+
+    rng = np.random.default_rng(5)
+    reqs = {"a": rng.integers(0, V, 90).tolist(), "b": rng.integers(0, V, 33).tolist(), "c": rng.integers(0, V, 140).tolist()}
+    refs = {r: plain(t) for r, t in reqs.items()}
+    assert len(used) == 2 * E                                           # every expert of every layer saw tokens
+    for steps, most in (H.trace_whole(reqs), H.trace_last_decoded(reqs, 32), H.trace_batches(reqs, 2, {"a": 30, "b": 33, "c": 70})):
+        got = H.collect(steps, H.replay(model, steps, max(most, 512)), V)
+        for r in reqs:
+            assert np.isfinite(got[r]).all()
+            assert H.rel_to_max(got[r], refs[r]) < 2e-5, r
