@@ -5,17 +5,22 @@
 // one sequence and one query head and walks the pages (64 keys) the queries can see:
 //
 //   S_j = Q · K_jᵀ        tcgen05.mma, M = 128 queries on TMEM lanes, N = 64 keys on TMEM columns
-//   softmax               four warps, ONE QUERY ROW PER THREAD: tcgen05.ld of the row, mask, running
-//                         maximum, exp2, sum — no shuffles; P_j goes to shared memory as bf16 in the
-//                         swizzled layout an MMA A-operand wants
-//   O_j = P_j · V_j       tcgen05.mma again (V is the MN-major B operand, straight from the cache page)
-//   O  += O_j             the row's thread reads O_j from TMEM and adds it to its fp32 registers, scaled
-//                         by the running-maximum correction — the accumulator never lives in TMEM, so
-//                         nothing there is read, rescaled and written back
+//   softmax               four warps, ONE QUERY ROW PER THREAD: tcgen05.ld of the row, mask, maximum, exp2,
+//                         sum — no shuffles; P_j goes to shared memory as bf16 in the swizzled layout an MMA
+//                         A-operand wants
+//   O += P_j · V_j        tcgen05.mma again (V is the MN-major B operand, straight from the cache page),
+//                         ACCUMULATING in TMEM over the pages
 //
-// Roles: warp 0 = TMA producer (Q once, then K_j / V_j pages into a ring), warp 1 = TMEM allocation and MMA
-// issue, warps 2..5 = softmax and output.  S and O_j are double-buffered in TMEM and P in shared memory, so
-// S_{j+1} is computed while the softmax of S_j runs.  Every wait is bounded (see sm100.cuh).
+// The accumulator is scaled lazily: P_j and O are kept relative to a reference maximum that follows the
+// row's running maximum only when that has grown by more than 8 (in base 2), so P stays below 256 and the
+// read-multiply-write of O in TMEM happens a few times per row instead of once per page; the final division
+// by the row sum makes the result the same.
+//
+// A block is small on purpose (64 KB of shared memory, 128 TMEM columns, 192 threads): three are resident
+// per SM and hide one another's chain S -> softmax -> PV.  Roles: warp 0 = TMA producer (Q once, then
+// K_j / V_j pages into a ring of two), warp 1 = TMEM allocation and MMA issue, warps 2..5 = softmax and
+// output.  S_{j+1} is computed while the softmax of S_j runs (the softmax frees S as soon as it has read
+// it).  Every wait is bounded (see sm100.cuh).
 #include <cuda.h>
 #include <math.h>
 
@@ -25,12 +30,14 @@
 namespace llmi {
 
 constexpr int FT_BM = 128, FT_PAGE = 64, FT_HD = 64;
-constexpr int FT_STAGES = 3;
+constexpr int FT_STAGES = 2;
 constexpr int FT_THREADS = 192;
 constexpr int FT_TILE = FT_PAGE * FT_HD * 2;          // 8 KB: one K or V page tile
 constexpr int FT_QBYTES = FT_BM * FT_HD * 2;          // 16 KB
 constexpr int FT_PBYTES = FT_BM * FT_PAGE * 2;        // 16 KB
-constexpr int FT_SMEM = FT_QBYTES + FT_STAGES * 2 * FT_TILE + 2 * FT_PBYTES + 1024 + 256;
+constexpr int FT_SMEM = FT_QBYTES + FT_STAGES * 2 * FT_TILE + FT_PBYTES + 1024 + 128;
+constexpr int FT_TMEM_COLS = 128;                     // S at columns 0..63, O at 64..127
+constexpr float FT_LAZY = 8.0f;                       // the reference maximum follows the running one in steps of 2^8
 
 struct PrefillTcParams {
   __nv_bfloat16* out;
@@ -79,26 +86,34 @@ __device__ __forceinline__ void ft_ld16(uint32_t taddr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ void ft_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 16 consecutive fp32 columns of this thread's TMEM lane, written; no wait
+__device__ __forceinline__ void ft_st16(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+      : "memory");
+}
+__device__ __forceinline__ void ft_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-__global__ void __launch_bounds__(FT_THREADS, 2)
+__global__ void __launch_bounds__(FT_THREADS, 3)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, PrefillTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem = base;
   const uint32_t kv_smem = base + FT_QBYTES;                        // stage s: K at +s*16K, V at +s*16K+8K
-  const uint32_t p_smem = kv_smem + FT_STAGES * 2 * FT_TILE;        // two P buffers
-  const uint32_t bars = p_smem + 2 * FT_PBYTES;
-  // barriers: q_full, kv_full[3], kv_empty[3], s_full[2], s_free[2], p_ready[2], o_full[2], o_free[2], tmem slot
+  const uint32_t p_smem = kv_smem + FT_STAGES * 2 * FT_TILE;
+  const uint32_t bars = p_smem + FT_PBYTES;
+  // barriers: q_full, kv_full[2], kv_empty[2], s_full, s_free, p_ready, o_done, tmem slot
   const uint32_t q_full = bars;
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bars + 8u * (1 + FT_STAGES + s); };
-  auto s_full = [&](int b) { return bars + 8u * (1 + 2 * FT_STAGES + b); };
-  auto s_free = [&](int b) { return bars + 8u * (3 + 2 * FT_STAGES + b); };
-  auto p_ready = [&](int b) { return bars + 8u * (5 + 2 * FT_STAGES + b); };
-  auto o_full = [&](int b) { return bars + 8u * (7 + 2 * FT_STAGES + b); };
-  auto o_free = [&](int b) { return bars + 8u * (9 + 2 * FT_STAGES + b); };
-  const uint32_t tmem_slot = bars + 8u * (11 + 2 * FT_STAGES);
+  const uint32_t s_full = bars + 8u * (1 + 2 * FT_STAGES);
+  const uint32_t s_free = s_full + 8u, p_ready = s_full + 16u, o_done = s_full + 24u;
+  const uint32_t tmem_slot = s_full + 32u;
 
   pdl_launch_dependents();
   // which sequence and which block of 128 queries (late blocks, which see more keys, come first)
@@ -134,17 +149,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(s_full(b), 1);
-      mbar_init(s_free(b), 4);
-      mbar_init(p_ready(b), 4);
-      mbar_init(o_full(b), 1);
-      mbar_init(o_free(b), 4);
-    }
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 4);
+    mbar_init(p_ready, 4);
+    mbar_init(o_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(256));
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(FT_TMEM_COLS));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -152,11 +164,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   uint32_t tmem;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(tmem_slot));
-  // TMEM columns: S buffers at 0 and 64, O_j buffers at 128 and 192
+  const uint32_t tmem_s = tmem, tmem_o = tmem + 64;
 
   if (warp == 0) {
     if (lane == 0) {
       // ---- producer ----
+      pdl_wait();   // q and the cache pages of this step come from the kernels before
       mbar_expect_tx(q_full, FT_QBYTES);
       ft_tma(q_smem, &map_q, head * FT_HD, q_start + m0, q_full);
       for (int j = 0; j < n_pg; ++j) {
@@ -171,14 +184,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   } else if (warp == 1) {
     if (lane == 0) {
       // ---- MMA issuer ----
-      // S: A = Q (K-major), B = K page (K-major), N = 64.  O_j: A = P (K-major), B = V page (MN-major), N = 64.
+      // S: A = Q (K-major), B = K page (K-major), N = 64.  O: A = P (K-major), B = V page (MN-major), N = 64.
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
       const uint32_t idesc_o = idesc_s | (1u << 16);
       auto issue_s = [&](int j) {
         const uint64_t a = ft_desc(q_smem), b = ft_desc(kv_smem + (j % FT_STAGES) * 2 * FT_TILE);
 #pragma unroll
-        for (int k4 = 0; k4 < FT_HD / 16; ++k4) ft_mma(tmem + (uint32_t)((j & 1) * 64), a + 2 * k4, b + 2 * k4, idesc_s, k4 > 0);
-        ft_commit(s_full(j & 1));
+        for (int k4 = 0; k4 < FT_HD / 16; ++k4) ft_mma(tmem_s, a + 2 * k4, b + 2 * k4, idesc_s, k4 > 0);
+        ft_commit(s_full);
       };
       bool ok = mbar_wait(q_full, 0, p.error_flag, 42) && mbar_wait(kv_full(0), 0, p.error_flag, 43);
       if (ok) {
@@ -187,22 +200,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       for (int j = 0; j < n_pg && ok; ++j) {
         if (j + 1 < n_pg) {
-          ok = mbar_wait(kv_full((j + 1) % FT_STAGES), ((j + 1) / FT_STAGES) & 1, p.error_flag, 44);
-          if (ok && j + 1 >= 2) ok = mbar_wait(s_free((j + 1) & 1), (((j + 1) >> 1) - 1) & 1, p.error_flag, 45);
+          // S_{j+1} as soon as its page is here and the softmax has read S_j
+          ok = mbar_wait(kv_full((j + 1) % FT_STAGES), ((j + 1) / FT_STAGES) & 1, p.error_flag, 44) &&
+               mbar_wait(s_free, j & 1, p.error_flag, 45);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           issue_s(j + 1);
         }
-        ok = mbar_wait(p_ready(j & 1), (j >> 1) & 1, p.error_flag, 46);
-        if (ok && j >= 2) ok = mbar_wait(o_free(j & 1), ((j >> 1) - 1) & 1, p.error_flag, 47);
+        ok = mbar_wait(p_ready, j & 1, p.error_flag, 46);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t a = ft_desc(p_smem + (j & 1) * FT_PBYTES);
+        const uint64_t a = ft_desc(p_smem);
         const uint64_t b = ft_desc(kv_smem + (j % FT_STAGES) * 2 * FT_TILE + FT_TILE);
 #pragma unroll
         for (int k4 = 0; k4 < FT_PAGE / 16; ++k4)   // 16 keys further: +32 bytes in a P row, +16 rows of 128 bytes in V
-          ft_mma(tmem + (uint32_t)(128 + (j & 1) * 64), a + 2 * k4, b + (uint64_t)(k4 * ((16 * 128) >> 4)), idesc_o, k4 > 0);
-        ft_commit(o_full(j & 1));
+          ft_mma(tmem_o, a + 2 * k4, b + (uint64_t)(k4 * ((16 * 128) >> 4)), idesc_o, (j > 0 || k4 > 0) ? 1u : 0u);
+        ft_commit(o_done);
         ft_commit(kv_empty(j % FT_STAGES));
       }
     }
@@ -213,53 +226,71 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int qrow = m0 + row;
     const bool row_ok = qrow < q_len;
     const int qpos = pos0 + qrow;
-    const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
-    float o[FT_HD];
-#pragma unroll
-    for (int d = 0; d < FT_HD; ++d) o[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, corr = 1.f;
+    const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
+    float m_run = -INFINITY, m_ref = -INFINITY, l_run = 0.f;   // maxima in base 2, scaled
     bool ok = true;
     for (int j = 0; j < n_pg && ok; ++j) {
-      const int b = j & 1;
-      ok = mbar_wait(s_full(b), (j >> 1) & 1, p.error_flag, 48);
+      ok = mbar_wait(s_full, j & 1, p.error_flag, 48);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       float sc[FT_PAGE];
 #pragma unroll
-      for (int c = 0; c < FT_PAGE; c += 16) ft_ld16(t_lane + (uint32_t)(b * 64 + c), sc + c);
+      for (int c = 0; c < FT_PAGE; c += 16) ft_ld16(tmem_s + t_lane + (uint32_t)c, sc + c);
       ft_ld_wait();
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(s_free(b));
+      if (lane == 0) mbar_arrive(s_free);
       const int key0 = (pg_first + j) * FT_PAGE;
       const bool need_mask = (key0 + FT_PAGE - 1 > first_q) || (p.window > 0);
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < FT_PAGE; ++c) {
+          const int key = key0 + c;
+          if (key > qpos || (p.window > 0 && key < qpos - p.window + 1)) sc[c] = -INFINITY;
+        }
+      }
       float mx = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < FT_PAGE; ++c) {
-        float v = sc[c] * p.scale_log2;
-        const int key = key0 + c;
-        if (need_mask && (key > qpos || (p.window > 0 && key < qpos - p.window + 1))) v = -INFINITY;
-        sc[c] = v;
-        mx = fmaxf(mx, v);
+      for (int c = 0; c < FT_PAGE; c += 2) mx = fmaxf(mx, fmaxf(sc[c], sc[c + 1]));
+      m_run = fmaxf(m_run, mx * p.scale_log2);
+      float corr = 1.f;
+      if (m_run > m_ref + FT_LAZY || m_ref == -INFINITY) {     // (both -inf: nothing seen yet, nothing to scale)
+        corr = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_run);
+        m_ref = m_run;
+        l_run *= corr;
       }
-      const float m_new = fmaxf(m_run, mx);
-      corr = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run - m_new);
-      m_run = m_new;
+      const float neg_ref = (m_ref == -INFINITY) ? 0.f : -m_ref;
       float sum = 0.f;
       uint32_t packed[FT_PAGE / 2];
 #pragma unroll
       for (int c = 0; c < FT_PAGE; c += 2) {
-        const float p0 = (m_new == -INFINITY) ? 0.f : fast_exp2(sc[c] - m_new);
-        const float p1 = (m_new == -INFINITY) ? 0.f : fast_exp2(sc[c + 1] - m_new);
+        const float p0 = fast_exp2(fmaf(sc[c], p.scale_log2, neg_ref));     // 2^(-inf) = 0 for masked keys
+        const float p1 = fast_exp2(fmaf(sc[c + 1], p.scale_log2, neg_ref));
         sum += p0 + p1;
         __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
         packed[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
       }
-      l_run = l_run * corr + sum;
+      l_run += sum;
+      if (j >= 1) {
+        // O += P_{j-1} V_{j-1} has to be finished: P's buffer is written below, and O may be rescaled
+        ok = mbar_wait(o_done, (j - 1) & 1, p.error_flag, 49);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll
-      for (int d = 0; d < FT_HD; ++d) o[d] *= corr;
+          for (int c = 0; c < FT_HD; c += 16) {
+            float t[16];
+            ft_ld16(tmem_o + t_lane + (uint32_t)c, t);
+            ft_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) t[e] *= corr;
+            ft_st16(tmem_o + t_lane + (uint32_t)c, t);
+          }
+          ft_st_wait();
+        }
+      }
       // P row -> shared memory, swizzled as an MMA operand (chunk c of row r at r*128 + ((c ^ (r & 7)) << 4))
-      const uint32_t prow = p_smem + b * FT_PBYTES + (uint32_t)row * 128;
+      const uint32_t prow = p_smem + (uint32_t)row * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c)
         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(prow + (uint32_t)(((c ^ (row & 7)) << 4))),
@@ -276,53 +307,30 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA's reads
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready(b));
-      if (j >= 1) {
-        // O_{j-1} = P_{j-1} V_{j-1} is relative to the maximum before this page: scale it like the registers
-        const int pb = (j - 1) & 1;
-        ok = mbar_wait(o_full(pb), ((j - 1) >> 1) & 1, p.error_flag, 49);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-        for (int c = 0; c < FT_HD; c += 16) {
-          float t[16];
-          ft_ld16(t_lane + (uint32_t)(128 + pb * 64 + c), t);
-          ft_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 16; ++e) o[c + e] = fmaf(corr, t[e], o[c + e]);
-        }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(o_free(pb));
-      }
+      if (lane == 0) mbar_arrive(p_ready);
     }
-    if (ok) {
-      const int pb = (n_pg - 1) & 1;
-      ok = mbar_wait(o_full(pb), ((n_pg - 1) >> 1) & 1, p.error_flag, 50);
-      if (ok) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok && mbar_wait(o_done, (n_pg - 1) & 1, p.error_flag, 50)) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float inv = 1.f / l_run;
+      __nv_bfloat16* dst = p.out + (size_t)(q_start + qrow) * p.ldo + (size_t)head * FT_HD;
 #pragma unroll
-        for (int c = 0; c < FT_HD; c += 16) {
-          float t[16];
-          ft_ld16(t_lane + (uint32_t)(128 + pb * 64 + c), t);
-          ft_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 16; ++e) o[c + e] += t[e];
-        }
+      for (int c = 0; c < FT_HD; c += 16) {
+        float t[16];
+        ft_ld16(tmem_o + t_lane + (uint32_t)c, t);
+        ft_ld_wait();
         if (row_ok) {
-          const float inv = 1.f / l_run;
-          __nv_bfloat16* dst = p.out + (size_t)(q_start + qrow) * p.ldo + (size_t)head * FT_HD;
 #pragma unroll
-          for (int c = 0; c < FT_HD; c += 8) {
+          for (int e = 0; e < 16; e += 8) {
             uint4 v;
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv), h1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv), h3 = __floats2bfloat162_rn(o[c + 6] * inv, o[c + 7] * inv);
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(t[e] * inv, t[e + 1] * inv), h1 = __floats2bfloat162_rn(t[e + 2] * inv, t[e + 3] * inv);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(t[e + 4] * inv, t[e + 5] * inv), h3 = __floats2bfloat162_rn(t[e + 6] * inv, t[e + 7] * inv);
             v.x = *reinterpret_cast<uint32_t*>(&h0);
             v.y = *reinterpret_cast<uint32_t*>(&h1);
             v.z = *reinterpret_cast<uint32_t*>(&h2);
             v.w = *reinterpret_cast<uint32_t*>(&h3);
-            *reinterpret_cast<uint4*>(dst + c) = v;
+            *reinterpret_cast<uint4*>(dst + c + e) = v;
           }
         }
       }
@@ -330,7 +338,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256));
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(FT_TMEM_COLS));
 }
 
 typedef CUresult (*FtEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
