@@ -35,15 +35,27 @@ linear_simt_kernel(const T* __restrict__ x, long ldx, const T* __restrict__ w, l
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
-  for (int k0 = 0; k0 < K; k0 += BK) {
+  // The next k block is fetched into registers while the current one is multiplied, so that a block pays the
+  // latency of global memory once, not once per k block.  The order of the additions is untouched.
+  const int m_ld = m0 + lr, n_ld = n0 + lr;
+  float a_next[4], b_next[4];
+  auto fetch = [&](int k0) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int k = k0 + lk + e;
-      const int m = m0 + lr, n = n0 + lr;
-      As[lk + e][lr] = (m < M && k < K) ? to_f32(x[(long)m * ldx + k]) : 0.f;
-      Bs[lk + e][lr] = (n < N && k < K) ? to_f32(w[(long)n * ldw + k]) : 0.f;
+      a_next[e] = (m_ld < M && k < K) ? to_f32(x[(long)m_ld * ldx + k]) : 0.f;
+      b_next[e] = (n_ld < N && k < K) ? to_f32(w[(long)n_ld * ldw + k]) : 0.f;
+    }
+  };
+  fetch(0);
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      As[lk + e][lr] = a_next[e];
+      Bs[lk + e][lr] = b_next[e];
     }
     __syncthreads();
+    if (k0 + BK < K) fetch(k0 + BK);
 #pragma unroll
     for (int kk = 0; kk < BK; ++kk) {
       float a[4], b[4];
