@@ -19,6 +19,10 @@
 // AFTER the norm takes h as its input, adds the tiles' sums in tile order, and multiplies its accumulators
 // by 1/sqrt(sum/k + eps) before the bias: y = scale * (h . W) is the normalised product with the scale
 // applied in fp32 at the end instead of before the rounding of h.
+// The token rows are fetched as they are (a TMA box of exactly n_tok rows, packed [slice][token][64 k]): what a
+// block can take in through TMA is the bound (about 59 GB/s an SM), and at one token eight padded rows would be
+// a third of it.  The MMA's B fragment still spans 8 (16, 32) rows; the rows past n_tok are whatever follows
+// in shared memory and feed output columns that nobody stores.
 // Blocks are persistent over row tiles and the ring runs on across tiles.  The k order of the additions is
 // fixed (it does not depend on the number of tokens), and programmatic dependent launch lets the first
 // weight tiles be requested before the kernel that produces x has finished.
@@ -46,6 +50,7 @@ struct SkinnyParams {
   const float* bias;
   int mode;
   int* error_flag;
+  int x_rows;                 // rows of the token box: n_tok
   // the norm AFTER this product (mode SK_ADD_F32 only): null or
   const float* emit_w;        // [m_out] weight of that norm
   __nv_bfloat16* emit_h;      // [n_tok, emit_ldh]: bf16(emit_w * x_new)
@@ -116,7 +121,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (int ks = 0; ks < kstages; ++ks, ++it) {
           const int s = it % SK_STAGES;
           if (it >= SK_STAGES && !mbar_wait(empty_bar(s), ((it / SK_STAGES) - 1) & 1, p.error_flag, 31)) { ok = false; break; }
-          mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          mbar_expect_tx(full_bar(s), W_BYTES + 4 * p.x_rows * 128);
           const uint32_t dst = base + s * STAGE_BYTES;
           sk_tma(dst, &map_w, t * SK_ROWS, ks * 4, full_bar(s));
           if (it < ahead) {
@@ -169,7 +174,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       ok = mbar_wait(full_bar(s), (it / SK_STAGES) & 1, p.error_flag, 32);
       if (!ok) break;
       const uint32_t w_slice = base + s * STAGE_BYTES + warp * W_SLICE;
-      const uint32_t x_slice = base + s * STAGE_BYTES + W_BYTES + warp * X_SLICE;
+      const uint32_t x_base = base + s * STAGE_BYTES + W_BYTES;
+      const int x_row0 = warp * p.x_rows;                  // this warp's slice starts at this row of the packed box
 #pragma unroll
       for (int c = 0; c < 4; ++c) {       // four k16 chunks of this warp's 64-wide slice
         uint32_t a[4];
@@ -185,10 +191,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           uint32_t b0, b1;
           {
             const int mtx = (lane >> 3) & 1, r = lane & 7;       // lanes 16..31 repeat the addresses of 0..15 (x2)
-            const int row = n * 8 + r, kch = c * 2 + mtx;
+            const int row = x_row0 + n * 8 + r, kch = c * 2 + mtx;     // the swizzle follows the physical row
             asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];"
                          : "=r"(b0), "=r"(b1)
-                         : "r"(x_slice + (uint32_t)(row * 128 + ((kch ^ (row & 7)) << 4))));
+                         : "r"(x_base + (uint32_t)(row * 128 + ((kch ^ (row & 7)) << 4))));
           }
           sk_mma(acc[n], a, b0, b1);
         }
@@ -332,9 +338,9 @@ LLMI_EXPORT int llmi_gemm_skinny(const void* x, long ldx, const void* w, long ld
   CUtensorMap mw, mx;
   int rc = sk_make_map(&mw, w, m_out, k, ldw, SK_ROWS);
   if (rc != LLMI_OK) return rc;
-  rc = sk_make_map(&mx, x, n_tok, k, ldx, nt * 8);
+  rc = sk_make_map(&mx, x, n_tok, k, ldx, n_tok);
   if (rc != LLMI_OK) return rc;
-  SkinnyParams p{m_out, n_tok, k, y, ldy, bias, mode, error_flag, emit_w, (__nv_bfloat16*)emit_h, emit_ldh, emit_ss,
+  SkinnyParams p{m_out, n_tok, k, y, ldy, bias, mode, error_flag, n_tok, emit_w, (__nv_bfloat16*)emit_h, emit_ldh, emit_ss,
                  in_ss, in_tiles, in_eps};
   const int m_tiles = (m_out + SK_ROWS - 1) / SK_ROWS;
   if (nt == 1) return launch_skinny<1>(mw, mx, p, m_tiles, stream);
