@@ -271,23 +271,31 @@ attention_decode_kernel(DecodeParams p, int n_items) {
         float L = 0.f, A[DPL];
 #pragma unroll
         for (int u = 0; u < DPL; ++u) A[u] = 0.f;
-        if (d.n_parts <= 8) {
+        constexpr int NZ = DPL <= 2 ? 16 : 8;      // splits merged in one go (registers: NZ * DPL values)
+        if (d.n_parts <= NZ) {
           // few splits: every load of the merge is issued before any is used — one round trip to L2
-          float mz[8], lz[8], v[8][DPL];
+          float mz[NZ], lz[NZ], v[NZ][DPL];
 #pragma unroll
-          for (int z = 0; z < 8; ++z) {
-            const float* pz = parts + ((size_t)min(z, d.n_parts - 1) * G + g) * (HD + 2);
-            mz[z] = __ldcg(&pz[HD]);
-            lz[z] = __ldcg(&pz[HD + 1]);
+          for (int z = 0; z < NZ; ++z) {
+            if (z < 8 || d.n_parts > 8) {        // (warp-uniform) the second eight only when there are that many
+              const float* pz = parts + ((size_t)min(z, d.n_parts - 1) * G + g) * (HD + 2);
+              mz[z] = __ldcg(&pz[HD]);
+              lz[z] = __ldcg(&pz[HD + 1]);
 #pragma unroll
-            for (int u = 0; u < DPL; ++u) v[z][u] = (lane + 32 * u < HD) ? __ldcg(&pz[lane + 32 * u]) : 0.f;
+              for (int u = 0; u < DPL; ++u) v[z][u] = (lane + 32 * u < HD) ? __ldcg(&pz[lane + 32 * u]) : 0.f;
+            } else {
+              mz[z] = -INFINITY;
+              lz[z] = 0.f;
+#pragma unroll
+              for (int u = 0; u < DPL; ++u) v[z][u] = 0.f;
+            }
           }
           float M = -INFINITY;
 #pragma unroll
-          for (int z = 0; z < 8; ++z)
+          for (int z = 0; z < NZ; ++z)
             if (z < d.n_parts) M = fmaxf(M, mz[z]);
 #pragma unroll
-          for (int z = 0; z < 8; ++z) {
+          for (int z = 0; z < NZ; ++z) {
             const float w = (z < d.n_parts && mz[z] != -INFINITY) ? fast_exp2(mz[z] - M) : 0.f;
             L = fmaf(lz[z], w, L);
 #pragma unroll
