@@ -249,9 +249,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           if (key > qpos || (p.window > 0 && key < qpos - p.window + 1)) sc[c] = -INFINITY;
         }
       }
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one long one
 #pragma unroll
-      for (int c = 0; c < FT_PAGE; c += 2) mx = fmaxf(mx, fmaxf(sc[c], sc[c + 1]));
+      for (int c = 0; c < FT_PAGE; c += 8) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], fmaxf(sc[c + 2 * u], sc[c + 2 * u + 1]));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       m_run = fmaxf(m_run, mx * p.scale_log2);
       float corr = 1.f;
       if (m_run > m_ref + FT_LAZY || m_ref == -INFINITY) {     // (both -inf: nothing seen yet, nothing to scale)
@@ -260,17 +264,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         l_run *= corr;
       }
       const float neg_ref = (m_ref == -INFINITY) ? 0.f : -m_ref;
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[FT_PAGE / 2];
 #pragma unroll
       for (int c = 0; c < FT_PAGE; c += 2) {
         const float p0 = fast_exp2(fmaf(sc[c], p.scale_log2, neg_ref));     // 2^(-inf) = 0 for masked keys
         const float p1 = fast_exp2(fmaf(sc[c + 1], p.scale_log2, neg_ref));
-        sum += p0 + p1;
+        sum4[(c >> 1) & 3] += p0 + p1;
         __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
         packed[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
       }
-      l_run += sum;
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       if (j >= 1) {
         // O += P_{j-1} V_{j-1} has to be finished: P's buffer is written below, and O may be rescaled
         ok = mbar_wait(o_done, (j - 1) & 1, p.error_flag, 49);
