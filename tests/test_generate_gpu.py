@@ -131,3 +131,62 @@ def test_command_line(model_dirs):
     assert r.returncode == 2
     r = subprocess.run([sys.executable, cli, d, "--ids", "1", "--bogus"], capture_output=True, text=True, timeout=600)
     assert r.returncode == 2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_recorded_decode_steps_survive_other_steps_in_between(model_dirs, dtype):
+    """Decode steps run as recorded graphs and, when they continue the step before, patch that step's index
+    block.  Whatever happens between two of them — a prompt of another sequence through the same buffers,
+    a sequence that joins, one that leaves, a slot that is freed and used again, a page boundary — the logits
+    of the chosen tokens must be those of the plain implementation."""
+    import llmi_b200 as L
+    from llmi_b200.sampling import Sampler
+    d = model_dirs("C", STORAGE[dtype])            # the long-context tiny configuration
+    cfg, w = P.read_model(d)
+    model = L.load(d, dtype)
+    V = cfg["vocab_size"]
+    cache = model.new_cache(64 * 8, n_slots=4)
+    sampler = Sampler(L.SamplingParams(), model.rt)
+    rng = np.random.default_rng(9)
+    hist = {}
+
+    def prefill(name, n):
+        slot = cache.alloc_slot()
+        toks = rng.integers(0, V, n).tolist()
+        logits = model.step(cache, [L.SequenceStep(slot, toks, [n - 1])]).cpu().numpy()
+        hist[name] = [slot, toks, int(np.argmax(logits[0]))]
+
+    def decode(names):
+        ids = model.step_and_choose(cache, [L.SequenceStep(hist[n][0], [hist[n][2]], [0]) for n in names], sampler).tolist()
+        for n, i in zip(names, ids):
+            hist[n][1].append(hist[n][2])
+            hist[n][2] = int(i)
+
+    def check(name):
+        slot, toks, nxt = hist[name]
+        logits = P.forward(cfg, w, toks)[-1]
+        top = np.sort(logits)[-2:]
+        if dtype == "float32" or top[1] - top[0] > 0.05:
+            assert nxt == int(np.argmax(logits)), (name, len(toks))
+
+    prefill("a", 60)
+    for _ in range(3):
+        decode(["a"])                   # continued steps (patched index block)
+    prefill("b", 10)                    # another step uses the buffers in between
+    decode(["a"])                       # ... so this one is planned anew; it crosses a's page boundary at 64
+    decode(["a"])
+    check("a")
+    decode(["a", "b"])                  # b joins: another batch shape
+    decode(["a", "b"])
+    check("a"), check("b")
+    cache.free_slot(hist.pop("a")[0])   # a leaves; its slot is used again by a longer sequence
+    prefill("c", 130)
+    assert hist["c"][0] != hist["b"][0]
+    decode(["b", "c"])
+    decode(["b", "c"])
+    decode(["c", "b"])                  # the same sequences in another order: not a continuation
+    decode(["c", "b"])
+    check("b"), check("c")
+    for n in list(hist):
+        cache.free_slot(hist.pop(n)[0])
+    cache.check()
