@@ -63,55 +63,83 @@ argmax_kernel(const float* __restrict__ logits, long ld, int vocab, int32_t* __r
   }
 }
 
+// Block-wide reductions in a fixed order: lanes by butterfly, then the warps' results by butterfly again in
+// every warp (no thread walks over 32 values one by one).  Every thread gets the result.
 struct BlockReduce {
   double* d;   // [32]
   long long* n;  // [32]
   __device__ double sum(double v) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     __syncthreads();
     if (lane == 0) d[warp] = v;
     __syncthreads();
-    double t = 0;
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += d[w];
+    double t = lane < nw ? d[lane] : 0.0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
     return t;
   }
   __device__ long long count(long long v) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     __syncthreads();
     if (lane == 0) n[warp] = v;
     __syncthreads();
-    long long t = 0;
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += n[w];
+    long long t = lane < nw ? n[lane] : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
     return t;
   }
   __device__ float max(float v) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     v = warp_max(v);
     __syncthreads();
     if (lane == 0) d[warp] = (double)v;
     __syncthreads();
-    float t = -INFINITY;
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t = fmaxf(t, (float)d[w]);
-    return t;
+    return warp_max(lane < nw ? (float)d[lane] : -INFINITY);
+  }
+  // Exclusive prefix sums over the threads of the block in thread order (and the total): lanes by shuffles,
+  // then the warps' totals the same way.  `buf` holds 32 values.
+  template <typename V>
+  __device__ V exclusive_scan(V v, V* buf, V* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    V incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const V up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    __syncthreads();
+    if (lane == 31) buf[warp] = incl;
+    __syncthreads();
+    V w = lane < nw ? buf[lane] : V(0);
+    V wincl = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const V up = __shfl_up_sync(0xffffffffu, wincl, o);
+      if (lane >= o) wincl += up;
+    }
+    const V warp_base = __shfl_sync(0xffffffffu, wincl - w, warp);
+    *total = __shfl_sync(0xffffffffu, wincl, nw - 1);
+    return warp_base + (incl - v);
   }
 };
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, long ld, int vocab, float temperature, int top_k, float top_p,
-              const double* __restrict__ uniforms, float* __restrict__ probs, int32_t* __restrict__ out) {
+              const double* __restrict__ uniforms, float* __restrict__ probs, int32_t* __restrict__ out, int probs_in_smem) {
   __shared__ double red_d[32];
   __shared__ long long red_n[32];
-  __shared__ double scan_mass[SAMPLE_THREADS];
-  __shared__ int scan_eq[SAMPLE_THREADS];
   __shared__ int result_first, result_last;
   BlockReduce red{red_d, red_n};
   const int tid = threadIdx.x, nthr = blockDim.x;
   const float* row = logits + (size_t)blockIdx.x * ld;
-  float* p = probs + (size_t)blockIdx.x * vocab;
+  // The probabilities are read some seventy times (two threshold searches bit by bit, scans): they live in
+  // shared memory when the vocabulary fits there (`probs_in_smem`), else in the caller's scratch.
+  extern __shared__ float smem_probs[];
+  float* p = probs_in_smem ? smem_probs : probs + (size_t)blockIdx.x * vocab;
   const uint32_t* pb = reinterpret_cast<const uint32_t*>(p);
 
   // softmax(logits / temperature), denominator in double
@@ -193,32 +221,21 @@ sample_kernel(const float* __restrict__ logits, long ld, int vocab, float temper
   const int i0 = tid * chunk, i1 = min(vocab, i0 + chunk);
   int eq_local = 0;
   for (int i = i0; i < i1; ++i) eq_local += pb[i] == thr;
-  scan_eq[tid] = eq_local;
-  __syncthreads();
-  if (tid == 0) {
-    int run = 0;
-    for (int w = 0; w < nthr; ++w) { const int c = scan_eq[w]; scan_eq[w] = run; run += c; }
-  }
-  __syncthreads();
-  int eq_rank = scan_eq[tid];
+  long long eq_total;
+  int eq_rank = (int)red.exclusive_scan<long long>((long long)eq_local, red_n, &eq_total);
+  const int eq_rank0 = eq_rank;
   double local = 0;
   for (int i = i0; i < i1; ++i) {
     if (pb[i] > thr) local += (double)p[i];
     else if (pb[i] == thr) { if (eq_rank < n_eq) local += (double)p[i]; ++eq_rank; }
   }
-  scan_mass[tid] = local;
   if (tid == 0) { result_first = 0x7fffffff; result_last = -1; }
-  __syncthreads();
-  if (tid == 0) {
-    double run = 0;
-    for (int w = 0; w < nthr; ++w) { const double c = scan_mass[w]; scan_mass[w] = run; run += c; }
-    red_d[0] = run;  // kept mass
-  }
-  __syncthreads();
-  const double kept = red_d[0];
+  double kept;
+  const double mass_before = red.exclusive_scan<double>(local, red_d, &kept);
   const double target = uniforms[blockIdx.x] * kept;
-  double cum = scan_mass[tid];
-  eq_rank = scan_eq[tid];
+  __syncthreads();        // result_first / result_last are set
+  double cum = mass_before;
+  eq_rank = eq_rank0;
   int first = 0x7fffffff, last = -1;
   for (int i = i0; i < i1; ++i) {
     bool in = false;
@@ -254,7 +271,19 @@ LLMI_EXPORT int llmi_sample(const float* logits, long ld, int n_rows, int vocab,
                             cudaStream_t stream) {
   if (n_rows <= 0 || vocab <= 0) return LLMI_ERR_BAD_SIZE;
   if (!(temperature > 0.f)) return LLMI_ERR_UNSUPPORTED;
-  sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, temperature, top_k, top_p, uniforms,
-                                                       probs_scratch, out);
+  // up to 200 KB of shared memory for a row's probabilities (one block per SM; a step has few rows)
+  const size_t bytes = (size_t)vocab * sizeof(float);
+  static int smem_max = -1;
+  if (smem_max < 0) {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    smem_max = v - 20 * 1024;     // the kernel's static arrays take 12.6 KB
+    if (smem_max < 0) smem_max = 0;
+    if (cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max) != cudaSuccess) smem_max = 0;
+  }
+  const int in_smem = bytes <= (size_t)smem_max ? 1 : 0;
+  sample_kernel<<<n_rows, SAMPLE_THREADS, in_smem ? bytes : 0, stream>>>(logits, ld, vocab, temperature, top_k, top_p, uniforms,
+                                                                         probs_scratch, out, in_smem);
   return launch_status();
 }
