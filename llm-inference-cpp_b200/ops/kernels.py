@@ -446,8 +446,8 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, s
         _ptr(sc.error), _stream()))
 
 
-# Which prompt-attention kernel runs for head size 64: "mma" (mma.sync, the faster of the two as measured:
-# 114 against 142 us for a 2,048-token prompt of 32 heads) or "tc" (tcgen05, kept selectable and tested).
+# Which prompt-attention kernel runs for head size 64: "tc" (tcgen05: about 55 us for a 2,048-token prompt of 32
+# heads) or "mma" (mma.sync: 95 us; the kernel for head size 128).
 _PREFILL_ATTENTION = os.environ.get("LLMI_PREFILL_ATTENTION", "tc")     # "mma": the mma.sync kernel for every head size
 _FORCE_GENERIC_ATTENTION = os.environ.get("LLMI_ATTENTION", "") == "generic"
 
