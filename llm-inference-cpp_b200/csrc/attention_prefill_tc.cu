@@ -16,6 +16,11 @@
 // read-multiply-write of O in TMEM happens a few times per row instead of once per page; the final division
 // by the row sum makes the result the same.
 //
+// A causal prompt's query blocks differ 16-fold in the keys they see, and the kernel is as long as its longest
+// block: with `split_pages` > 0 a block's key range is cut into parts of that many pages, each part a block of
+// its own that leaves (reference maximum, sum, unnormalised output) per row in a workspace; the part that takes
+// a (query block, head)'s last ticket adds the parts in key order and writes the output.
+//
 // A block is small on purpose (64 KB of shared memory, 128 TMEM columns, 192 threads): three are resident
 // per SM and hide one another's chain S -> softmax -> PV.  Roles: warp 0 = TMA producer (Q once, then
 // K_j / V_j pages into a ring of two), warp 1 = TMEM allocation and MMA issue, warps 2..5 = softmax and
@@ -51,6 +56,10 @@ struct PrefillTcParams {
   float scale_log2;
   int window;
   int* error_flag;
+  int n_tiles;              // blocks of 128 queries over all sequences
+  int split_pages;          // 0: a query block's keys are one job; else jobs of at most this many pages
+  float* partials;          // [job (gridDim.x)][head][66][128]: per row m_ref, l, O[64], when split
+  int* tickets;             // [n_tiles * n_heads], zero before and after the launch
 };
 
 __device__ __forceinline__ void ft_tma(uint32_t dst, const CUtensorMap* map, int col, int row, uint32_t bar) {
@@ -116,28 +125,47 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t tmem_slot = s_full + 32u;
 
   pdl_launch_dependents();
-  // which sequence and which block of 128 queries (late blocks, which see more keys, come first)
-  int mb = gridDim.x - 1 - blockIdx.x;
-  int seq = 0, q_start = 0, q_len = 0;
-  for (; seq < p.n_seqs; ++seq) {
-    q_start = p.seq_q_start[seq];
-    q_len = p.seq_q_start[seq + 1] - q_start;
-    const int nb = (q_len + FT_BM - 1) / FT_BM;
-    if (mb < nb) break;
-    mb -= nb;
+  // which sequence, which block of 128 queries and which part of its keys: jobs are counted from the last
+  // block of the last sequence backwards (late blocks, which see more keys, come first), a block's parts in key order
+  int seq = p.n_seqs - 1, mb = 0, part = 0, n_parts = 1, tile_id = p.n_tiles;
+  int q_start = 0, q_len = 0, kv_len = 0, pos0 = 0, m0 = 0, rows_here = 0, first_q = 0, last_q = 0, pg_first = 0, n_pg = 0;
+  {
+    int x = blockIdx.x;
+    bool found = false;
+    for (; seq >= 0 && !found; --seq) {
+      q_start = p.seq_q_start[seq];
+      q_len = p.seq_q_start[seq + 1] - q_start;
+      kv_len = p.seq_kv_len[seq];
+      pos0 = kv_len - q_len;
+      for (mb = (q_len + FT_BM - 1) / FT_BM - 1; mb >= 0; --mb) {
+        --tile_id;
+        m0 = mb * FT_BM;
+        rows_here = min(FT_BM, q_len - m0);
+        first_q = pos0 + m0;
+        last_q = first_q + rows_here - 1;
+        const int lo_key = (p.window > 0 && first_q - p.window + 1 > 0) ? first_q - p.window + 1 : 0;
+        pg_first = lo_key / FT_PAGE;
+        n_pg = last_q / FT_PAGE - pg_first + 1;
+        n_parts = p.split_pages > 0 ? (n_pg + p.split_pages - 1) / p.split_pages : 1;
+        if (x < n_parts) {
+          part = x;
+          found = true;
+          break;
+        }
+        x -= n_parts;
+      }
+      if (found) break;
+    }
+    if (!found) return;
   }
-  if (seq >= p.n_seqs) return;
+  if (n_parts > 1) {                       // this block's part of the key range
+    pg_first += part * p.split_pages;
+    n_pg = min(p.split_pages, n_pg - part * p.split_pages);
+  }
   const int head = blockIdx.y;
   const int kvh = head / (p.n_heads / p.n_kv_heads);
-  const int kv_len = p.seq_kv_len[seq];
-  const int pos0 = kv_len - q_len;
-  const int m0 = mb * FT_BM;
-  const int rows_here = min(FT_BM, q_len - m0);
-  const int first_q = pos0 + m0, last_q = pos0 + m0 + rows_here - 1;
-  const int lo_key = (p.window > 0 && first_q - p.window + 1 > 0) ? first_q - p.window + 1 : 0;
-  const int pg_first = lo_key / FT_PAGE, pg_last = last_q / FT_PAGE;
-  const int n_pg = pg_last - pg_first + 1;
   const int32_t* pages = p.seq_pages + (size_t)seq * p.pages_stride;
+  __shared__ int s_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -315,27 +343,63 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       __syncwarp();
       if (lane == 0) mbar_arrive(p_ready);
     }
-    if (ok && mbar_wait(o_done, (n_pg - 1) & 1, p.error_flag, 50)) {
+    {
+      // (a warp whose wait gave up still goes through the barriers below: nobody is left waiting for it)
+      const bool fine = ok && mbar_wait(o_done, (n_pg - 1) & 1, p.error_flag, 50);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float inv = 1.f / l_run;
-      __nv_bfloat16* dst = p.out + (size_t)(q_start + qrow) * p.ldo + (size_t)head * FT_HD;
+      float o[FT_HD];
 #pragma unroll
-      for (int c = 0; c < FT_HD; c += 16) {
-        float t[16];
-        ft_ld16(tmem_o + t_lane + (uint32_t)c, t);
-        ft_ld_wait();
-        if (row_ok) {
+      for (int c = 0; c < FT_HD; c += 16) ft_ld16(tmem_o + t_lane + (uint32_t)c, o + c);
+      ft_ld_wait();
+      bool write_out = fine;
+      if (n_parts > 1) {
+        // this part's (m_ref, l, O) to the workspace; the part that comes last adds them all in key order
+        const size_t slot_floats = (size_t)(FT_HD + 2) * FT_BM;
+        float* mine = p.partials + ((size_t)blockIdx.x * p.n_heads + head) * slot_floats + row;
+        mine[0] = m_ref;
+        mine[FT_BM] = l_run;
 #pragma unroll
-          for (int e = 0; e < 16; e += 8) {
-            uint4 v;
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(t[e] * inv, t[e + 1] * inv), h1 = __floats2bfloat162_rn(t[e + 2] * inv, t[e + 3] * inv);
-            __nv_bfloat162 h2 = __floats2bfloat162_rn(t[e + 4] * inv, t[e + 5] * inv), h3 = __floats2bfloat162_rn(t[e + 6] * inv, t[e + 7] * inv);
-            v.x = *reinterpret_cast<uint32_t*>(&h0);
-            v.y = *reinterpret_cast<uint32_t*>(&h1);
-            v.z = *reinterpret_cast<uint32_t*>(&h2);
-            v.w = *reinterpret_cast<uint32_t*>(&h3);
-            *reinterpret_cast<uint4*>(dst + c + e) = v;
+        for (int c = 0; c < FT_HD; ++c) mine[(size_t)(2 + c) * FT_BM] = o[c];
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");          // the four softmax warps
+        int* ticket = p.tickets + tile_id * p.n_heads + head;
+        if (threadIdx.x == 64) s_last = (atomicAdd(ticket, 1) == n_parts - 1);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        write_out = fine && s_last != 0;
+        if (s_last != 0) {
+          __threadfence();
+          const float* first = p.partials + ((size_t)(blockIdx.x - part) * p.n_heads + head) * slot_floats + row;
+          const size_t part_stride = (size_t)p.n_heads * slot_floats;
+          float M = -INFINITY;
+          for (int z = 0; z < n_parts; ++z) M = fmaxf(M, __ldcg(first + z * part_stride));
+          float L = 0.f;
+#pragma unroll
+          for (int c = 0; c < FT_HD; ++c) o[c] = 0.f;
+          for (int z = 0; z < n_parts; ++z) {
+            const float* pz = first + z * part_stride;
+            const float mz = __ldcg(pz);
+            const float w = (mz == -INFINITY) ? 0.f : fast_exp2(mz - M);
+            L = fmaf(__ldcg(pz + FT_BM), w, L);
+#pragma unroll
+            for (int c = 0; c < FT_HD; ++c) o[c] = fmaf(w, __ldcg(pz + (size_t)(2 + c) * FT_BM), o[c]);
           }
+          l_run = L;
+          if (threadIdx.x == 64) *ticket = 0;
+        }
+      }
+      if (write_out && row_ok) {
+        const float inv = 1.f / l_run;
+        __nv_bfloat16* dst = p.out + (size_t)(q_start + qrow) * p.ldo + (size_t)head * FT_HD;
+#pragma unroll
+        for (int c = 0; c < FT_HD; c += 8) {
+          uint4 v;
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv), h1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv), h3 = __floats2bfloat162_rn(o[c + 6] * inv, o[c + 7] * inv);
+          v.x = *reinterpret_cast<uint32_t*>(&h0);
+          v.y = *reinterpret_cast<uint32_t*>(&h1);
+          v.z = *reinterpret_cast<uint32_t*>(&h2);
+          v.w = *reinterpret_cast<uint32_t*>(&h3);
+          *reinterpret_cast<uint4*>(dst + c) = v;
         }
       }
     }
@@ -382,7 +446,8 @@ LLMI_EXPORT int llmi_attention_prefill_tc(const void* q, long ldq, long n_tokens
                                           const void* v_cache, long n_cache_pages, const int32_t* seq_pages,
                                           int pages_stride, const int32_t* seq_q_start, const int32_t* seq_kv_len,
                                           int n_seqs, int n_blocks, int n_heads, int n_kv_heads, int head_dim, float scale,
-                                          int window, int* error_flag, cudaStream_t stream) {
+                                          int window, int n_jobs, int split_pages, float* partials, long partials_floats,
+                                          int* tickets, int n_tickets, int* error_flag, cudaStream_t stream) {
   if (n_seqs <= 0 || n_blocks <= 0 || n_heads <= 0 || n_kv_heads <= 0 || n_cache_pages <= 0 || n_tokens <= 0) return LLMI_ERR_BAD_SIZE;
   if (n_heads % n_kv_heads || n_heads > 65535) return LLMI_ERR_BAD_SIZE;
   if (head_dim != FT_HD) return LLMI_ERR_UNSUPPORTED;
@@ -404,9 +469,18 @@ LLMI_EXPORT int llmi_attention_prefill_tc(const void* q, long ldq, long n_tokens
       return LLMI_ERR_LAUNCH;
     configured = true;
   }
+  // n_jobs: blocks along x — n_blocks without a split, else the sum over the query blocks of their parts (the caller
+  // counts them with the same rule as the kernel); the workspace holds one slot per job and head
+  if (split_pages > 0) {
+    if (n_jobs < n_blocks || !partials || !tickets || (long)n_jobs * n_heads * (FT_HD + 2) * FT_BM > partials_floats ||
+        (long)n_blocks * n_heads > n_tickets)
+      return LLMI_ERR_BAD_SIZE;
+  } else {
+    n_jobs = n_blocks;
+  }
   PrefillTcParams p{(__nv_bfloat16*)out, ldo, seq_pages, seq_q_start, seq_kv_len, pages_stride, n_seqs, n_heads,
-                    n_kv_heads, scale * 1.4426950408889634f, window, error_flag};
-  dim3 grid(n_blocks, n_heads);
+                    n_kv_heads, scale * 1.4426950408889634f, window, error_flag, n_blocks, split_pages, partials, tickets};
+  dim3 grid(n_jobs, n_heads);
   attention_prefill_tc_kernel<<<grid, FT_THREADS, FT_SMEM, stream>>>(mq, mk, mv, p);
   return launch_status();
 }

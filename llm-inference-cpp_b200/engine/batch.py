@@ -208,6 +208,7 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
     ctx.max_kv_len = max_kv
     ctx.decode = decode
     ctx.n_q_blocks = sum((n + 127) // 128 for n in lens)     # 128-query blocks of the prompt kernel
+    ctx.host_q_lens, ctx.host_kv_lens = (None, None) if decode else (list(lens), list(kv_lens))   # for kernels that plan on the host
     ctx.h2d_bytes = cur * 4
 
     def view(name):

@@ -431,25 +431,52 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_
         _ptr(sc.error), _stream()))
 
 
+PREFILL_SPLIT_PAGES = 16      # key pages per job when the prompt attention cuts its long query blocks
+
+
+def prefill_split_jobs(q_lens, kv_lens, window: int, split_pages: int) -> int:
+    """How many jobs the prompt attention has along its first grid dimension when every block of 128 queries
+    is cut into parts of ``split_pages`` key pages (the kernel's own rule, counted on the host)."""
+    jobs = 0
+    for q_len, kv_len in zip(q_lens, kv_lens):
+        pos0 = kv_len - q_len
+        for mb in range((q_len + 127) // 128):
+            first_q = pos0 + mb * 128
+            last_q = first_q + min(128, q_len - mb * 128) - 1
+            lo_key = first_q - window + 1 if (window > 0 and first_q - window + 1 > 0) else 0
+            n_pg = last_q // 64 - lo_key // 64 + 1
+            jobs += (n_pg + split_pages - 1) // split_pages
+    return jobs
+
+
 def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_q_start, seq_kv_len,
-                         n_blocks: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
-    """The same prompt attention on the tcgen05 tensor cores (head size 64); arguments as ``attention_prefill``."""
+                         n_blocks: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0,
+                         split=None) -> None:
+    """The same prompt attention on the tcgen05 tensor cores (head size 64); arguments as ``attention_prefill``.
+    ``split = (n_jobs, split_pages, workspace)``: cut the key range of every query block into jobs of
+    ``split_pages`` pages (``n_jobs`` from :func:`prefill_split_jobs`, ``workspace`` fp32 of
+    n_jobs * n_heads * 66 * 128 floats)."""
     _need_cuda(q, out, k_cache, v_cache, seq_pages, seq_q_start, seq_kv_len)
     S = seq_pages.shape[0]
     assert q.dtype == out.dtype == k_cache.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
     assert k_cache.shape[-2] == 64 and k_cache.is_contiguous() and v_cache.is_contiguous()
     sc = tc_scratch(q.device)
+    n_jobs, split_pages, ws = split if split is not None else (n_blocks, 0, None)
+    if ws is not None:
+        assert ws.dtype == torch.float32 and ws.is_cuda
     _check("attention_prefill_tc", lib().llmi_attention_prefill_tc(
         _ptr(q), c_long(q.stride(0)), c_long(q.shape[0]), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
         c_long(k_cache.shape[0]), _ptr(seq_pages), c_int(seq_pages.stride(0)), _ptr(seq_q_start), _ptr(seq_kv_len),
         c_int(S), c_int(n_blocks), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window),
-        _ptr(sc.error), _stream()))
+        c_int(n_jobs), c_int(split_pages), _ptr(ws), c_long(ws.numel() if ws is not None else 0), _ptr(sc.attn_tickets),
+        c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), _stream()))
 
 
 # Which prompt-attention kernel runs for head size 64: "tc" (tcgen05: about 55 us for a 2,048-token prompt of 32
 # heads) or "mma" (mma.sync: 95 us; the kernel for head size 128).
 _PREFILL_ATTENTION = os.environ.get("LLMI_PREFILL_ATTENTION", "tc")     # "mma": the mma.sync kernel for every head size
 _FORCE_GENERIC_ATTENTION = os.environ.get("LLMI_ATTENTION", "") == "generic"
+_PREFILL_SPLIT = os.environ.get("LLMI_PREFILL_SPLIT", "1") != "0"
 
 
 def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start,
@@ -512,8 +539,18 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
     if (not ctx.decode and qkv.dtype == torch.bfloat16 and page_size == 64 and not _FORCE_GENERIC_ATTENTION
             and attention_prefill_supported(head_dim)):
         if head_dim == 64 and _PREFILL_ATTENTION == "tc" and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
+            # A step with fewer (query block, head) jobs than the device holds blocks (3 per SM) leaves SMs idle and
+            # is as long as its longest job: then the key ranges are cut (see the kernel's head).  With more jobs
+            # the cut gains nothing (measured: 2,048 tokens x 32 heads, 8.43 ms a prefill with it, 8.37 without).
+            split = None
+            q_lens, kv_lens = getattr(ctx, "host_q_lens", None), getattr(ctx, "host_kv_lens", None)
+            if _PREFILL_SPLIT and rt is not None and q_lens is not None and ctx.n_q_blocks * n_heads < 3 * 148:
+                jobs = prefill_split_jobs(q_lens, kv_lens, window, PREFILL_SPLIT_PAGES)
+                if jobs > ctx.n_q_blocks:
+                    ws = rt.scratch("attn_prefill_partials", (jobs * n_heads * 66 * 128,), torch.float32)
+                    split = (jobs, PREFILL_SPLIT_PAGES, ws)
             attention_prefill_tc(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_q_start, ctx.seq_kv_len, ctx.n_q_blocks,
-                                 n_heads, n_kv_heads, head_dim, scale, window)
+                                 n_heads, n_kv_heads, head_dim, scale, window, split)
             return
         attention_prefill(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_q_start, ctx.seq_kv_len, ctx.n_q_blocks,
                           n_heads, n_kv_heads, head_dim, scale, window)

@@ -489,15 +489,15 @@ def test_attention_decode_fused_rotation_same_bits(nh, nkv, hd, pps, window, rot
     assert int(kk.tc_scratch("cuda:0").attn_tickets.abs().sum()) == 0
 
 
-@pytest.mark.parametrize("kernel", ["mma", "tc"])
+@pytest.mark.parametrize("kernel", ["mma", "tc", "tc-split2", "tc-split3"])
 @pytest.mark.parametrize("nh,nkv,hd,window", [(4, 4, 64, 0), (6, 2, 64, 0), (4, 1, 128, 0), (3, 3, 64, 100), (2, 2, 128, 70)])
 def test_attention_prefill_ragged(nh, nkv, hd, window, kernel):
     """The flash prompt kernel against the plain formula: prompts of 1..600 tokens in one launch, one of
     them continuing a sequence that already holds 300 positions, scrambled pages, a poisoned cache."""
     kk = K()
-    if kernel == "tc" and hd != 64:
+    if kernel.startswith("tc") and hd != 64:
         pytest.skip("the tcgen05 prompt kernel has head size 64 only")
-    run = kk.attention_prefill_tc if kernel == "tc" else kk.attention_prefill
+    run = kk.attention_prefill_tc if kernel.startswith("tc") else kk.attention_prefill
     rng = np.random.default_rng(2)
     q_lens = [1, 127, 128, 129, 600, 200]
     bases = [0, 0, 0, 0, 0, 300]
@@ -530,7 +530,17 @@ def test_attention_prefill_ragged(nh, nkv, hd, window, kernel):
     kvlen = torch.tensor([n + b for n, b in zip(q_lens, bases)], dtype=torch.int32, device="cuda")
     n_blocks = sum((n + 127) // 128 for n in q_lens)
     scale = 1 / math.sqrt(hd)
-    run(q, out, kc, vc, pages.cuda(), qstart, kvlen, n_blocks, nh, nkv, hd, scale, window)
+    if "split" in kernel:
+        # the key range of every query block cut into jobs of 2 or 3 pages, merged by the last one to finish
+        sp = int(kernel[-1])
+        jobs = kk.prefill_split_jobs(q_lens, [n + b for n, b in zip(q_lens, bases)], window, sp)
+        assert jobs > n_blocks
+        ws = torch.full((jobs * nh * 66 * 128,), float("nan"), device="cuda")
+        for _ in range(2):      # twice: the tickets must come back to zero
+            run(q, out, kc, vc, pages.cuda(), qstart, kvlen, n_blocks, nh, nkv, hd, scale, window, (jobs, sp, ws))
+        assert int(kk.tc_scratch("cuda:0").attn_tickets.abs().sum()) == 0
+    else:
+        run(q, out, kc, vc, pages.cuda(), qstart, kvlen, n_blocks, nh, nkv, hd, scale, window)
     kk.check_device_errors("cuda:0")
     assert torch.isfinite(out.float()).all()
     for s_, (n, b) in enumerate(zip(q_lens, bases)):
