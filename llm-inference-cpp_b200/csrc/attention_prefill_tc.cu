@@ -292,17 +292,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         l_run *= corr;
       }
       const float neg_ref = (m_ref == -INFINITY) ? 0.f : -m_ref;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      // two keys per instruction where the hardware has it (fma.rn.f32x2, add.rn.f32x2)
+      float2 sum2[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg2 = make_float2(neg_ref, neg_ref);
       uint32_t packed[FT_PAGE / 2];
 #pragma unroll
       for (int c = 0; c < FT_PAGE; c += 2) {
-        const float p0 = fast_exp2(fmaf(sc[c], p.scale_log2, neg_ref));     // 2^(-inf) = 0 for masked keys
-        const float p1 = fast_exp2(fmaf(sc[c + 1], p.scale_log2, neg_ref));
-        sum4[(c >> 1) & 3] += p0 + p1;
-        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+        const float2 x = __ffma2_rn(make_float2(sc[c], sc[c + 1]), scale2, neg2);
+        const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));          // 2^(-inf) = 0 for masked keys
+        sum2[(c >> 1) & 3] = __fadd2_rn(sum2[(c >> 1) & 3], e);
+        __nv_bfloat162 h = __floats2bfloat162_rn(e.x, e.y);
         packed[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
       }
-      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      {
+        const float2 a = __fadd2_rn(sum2[0], sum2[1]), b = __fadd2_rn(sum2[2], sum2[3]);
+        const float2 t = __fadd2_rn(a, b);
+        l_run += t.x + t.y;
+      }
       if (j >= 1) {
         // O += P_{j-1} V_{j-1} has to be finished: P's buffer is written below, and O may be rescaled
         ok = mbar_wait(o_done, (j - 1) & 1, p.error_flag, 49);
