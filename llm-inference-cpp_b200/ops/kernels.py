@@ -85,7 +85,8 @@ def lib():
         for name in ("llmi_embed", "llmi_rmsnorm", "llmi_swiglu", "llmi_linear_simt", "llmi_rope_store",
                      "llmi_attention_generic", "llmi_argmax", "llmi_sample", "llmi_gemm_tc", "llmi_gemm_tc_splits",
                      "llmi_attention_decode", "llmi_attention_decode_supported", "llmi_attention_decode_resident",
-                     "llmi_attention_decode_fused",
+                     "llmi_attention_decode_fused", "llmi_attention_decode_mma", "llmi_attention_decode_mma_supported",
+                     "llmi_attention_decode_mma_resident",
                      "llmi_attention_prefill", "llmi_attention_prefill_supported", "llmi_gemm_skinny",
                      "llmi_gemm_skinny_max_tokens", "llmi_attention_prefill_tc", "llmi_attention_prefill_tc_supported"):
             getattr(l, name).restype = c_int
@@ -354,6 +355,17 @@ DECODE_PAGES_PER_SPLIT = 8     # default split of the decode kernel: 512 positio
 _resident_cache: dict = {}
 
 
+# Which decode kernel takes grouped queries (group = query heads per kv head >= 2) of head size 64 or 128: "mma"
+# (the group's heads as rows of tensor-core tiles: the work per page does not grow with the group) or "simt"
+# (the CUDA-core kernel, which always takes group 1).
+_DECODE_ATTENTION = os.environ.get("LLMI_DECODE_ATTENTION", "mma")
+
+
+def decode_uses_mma(head_dim: int, group: int) -> bool:
+    return bool(_DECODE_ATTENTION == "mma" and group >= 2
+                and lib().llmi_attention_decode_mma_supported(c_int(head_dim), c_int(group)))
+
+
 def decode_pages_per_split(n_seqs: int, n_kv_heads: int, max_pages: int, head_dim: int = 64, group: int = 1) -> int:
     """How many pages one work item of the decode kernel covers.
 
@@ -364,9 +376,28 @@ def decode_pages_per_split(n_seqs: int, n_kv_heads: int, max_pages: int, head_di
     """
     key = (head_dim, group)
     if key not in _resident_cache:
-        _resident_cache[key] = max(1, int(lib().llmi_attention_decode_resident(c_int(head_dim), c_int(group))))
+        fn = lib().llmi_attention_decode_mma_resident if decode_uses_mma(head_dim, group) else lib().llmi_attention_decode_resident
+        _resident_cache[key] = max(1, int(fn(c_int(head_dim), c_int(group))))
     resident = _resident_cache[key]
     pairs = max(1, n_seqs * n_kv_heads)
+    if decode_uses_mma(head_dim, group):
+        # The tensor-core kernel: the end of an item that is one of several splits costs about six pages of streaming
+        # (four warps merged, the partial result written, a ticket), of a whole sequence-head two; the last split to
+        # arrive merges two heads and NZ splits per round trip to L2 (about 1.5 pages of head size 64 each).
+        # Measured at 4,096 positions: 8 kv heads of size 64, batch 1: 8.7 us at 4 pages a split, 10.6 at 2, 13.1 at
+        # 16; batch 64: 84 us without splits, 91 at 16 pages, 119 at 8.
+        nz = 16 if head_dim <= 64 else 8
+        best, best_cost = max_pages, float("inf")
+        for splits in range(1, max(1, max_pages // 4) + 1):
+            pps = -(-max_pages // splits)
+            n_parts = -(-max_pages // pps)
+            rounds = -(-pairs * n_parts // resident)
+            cost = rounds * (pps + (2 if n_parts == 1 else 6))
+            if n_parts > 1:
+                cost += -(-group // 2) * -(-n_parts // nz) * 1.5 * 64 / head_dim
+            if cost < best_cost - 1e-9:
+                best, best_cost = pps, cost
+        return best
     best, best_score = max_pages, -1.0
     for splits in range(1, max(1, max_pages // 4) + 1):
         pps = -(-max_pages // splits)
@@ -380,7 +411,29 @@ def decode_pages_per_split(n_seqs: int, n_kv_heads: int, max_pages: int, head_di
 
 
 def attention_decode_supported(head_dim: int, group: int) -> bool:
-    return bool(lib().llmi_attention_decode_supported(c_int(head_dim), c_int(group)))
+    return decode_uses_mma(head_dim, group) or bool(lib().llmi_attention_decode_supported(c_int(head_dim), c_int(group)))
+
+
+def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start,
+                         n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int, partials: torch.Tensor,
+                         pages_per_split: int, rope=None) -> None:
+    """:func:`attention_decode` (``rope`` None) or :func:`attention_decode_fused` (``rope = (inv_freq, rotary_dim,
+    write_kv)``, ``q`` the un-rotated [q | k | v] rows) by the tensor-core kernel for grouped queries."""
+    _need_cuda(q, out, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start, partials)
+    S, P = seq_pages.shape
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+    assert q.stride(1) == 1 and out.stride(1) == 1 and k_cache.shape[-2] == 64 and partials.dtype == torch.float32
+    assert k_cache.is_contiguous() and v_cache.is_contiguous()
+    inv_freq, rotary_dim, write_kv = rope if rope is not None else (None, 0, False)
+    assert rotary_dim == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2)
+    sc = tc_scratch(q.device)
+    _check("attention_decode_mma", lib().llmi_attention_decode_mma(
+        _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
+        c_long(k_cache.shape[0]), _ptr(seq_pages), c_int(seq_pages.stride(0)), _ptr(seq_kv_len), _ptr(seq_q_start), c_int(S),
+        c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window), c_int(P), c_int(pages_per_split),
+        c_int(0 if rope is None else 1), _ptr(inv_freq) if rotary_dim else None, c_int(rotary_dim),
+        c_int(1 if write_kv else 0), _ptr(partials), c_long(partials.numel()), _ptr(sc.attn_tickets),
+        c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), _stream()))
 
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start,
@@ -527,7 +580,10 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
         S, P = seq_pages.shape
         pps = decode_pages_per_split(S, n_kv_heads, P, head_dim, n_heads // n_kv_heads)
         partials = rt.scratch("attn_partials", (attention_decode_workspace(S, n_heads, head_dim, P, pps),), torch.float32)
-        if rope is not None:
+        if decode_uses_mma(head_dim, n_heads // n_kv_heads):
+            attention_decode_mma(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_kv_len, ctx.seq_q_start, n_heads,
+                                 n_kv_heads, head_dim, scale, window, partials, pps, rope)
+        elif rope is not None:
             attention_decode_fused(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_kv_len, ctx.seq_q_start, n_heads,
                                    n_kv_heads, head_dim, scale, window, partials, pps, rope[0], rope[1], rope[2])
         else:

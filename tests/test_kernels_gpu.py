@@ -391,12 +391,33 @@ def test_gemm_tc_strided_input_and_refusals():
                    torch.empty(4, 8, device="cuda"), None, kk.OUT_STORE_F32)
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(32, 32, 64), (15, 5, 64), (8, 2, 128), (8, 8, 32), (16, 2, 64)])
+DECODE_SHAPES = [("simt", 32, 32, 64), ("simt", 15, 5, 64), ("simt", 8, 2, 128), ("simt", 8, 8, 32), ("simt", 16, 2, 64),
+                 ("mma", 15, 5, 64), ("mma", 8, 2, 128), ("mma", 16, 2, 64), ("mma", 28, 4, 128), ("mma", 32, 2, 64),
+                 ("mma", 12, 1, 128), ("mma", 10, 5, 64), ("mma", 3, 3, 64)]
+
+
+def decode_kernel(kk, kernel):
+    """(unfused, fused) launchers of one of the two decode kernels, with the same arguments."""
+    if kernel == "simt":
+        return kk.attention_decode, kk.attention_decode_fused
+
+    def plain(q, out, kc, vc, pages, kvlen, qstart, nh, nkv, hd, scale, window, part, pps):
+        kk.attention_decode_mma(q, out, kc, vc, pages, kvlen, qstart, nh, nkv, hd, scale, window, part, pps, None)
+
+    def fused(q, out, kc, vc, pages, kvlen, qstart, nh, nkv, hd, scale, window, part, pps, inv, rdim, write):
+        kk.attention_decode_mma(q, out, kc, vc, pages, kvlen, qstart, nh, nkv, hd, scale, window, part, pps, (inv, rdim, write))
+
+    return plain, fused
+
+
+@pytest.mark.parametrize("kernel,nh,nkv,hd", DECODE_SHAPES)
 @pytest.mark.parametrize("pps,window", [(1, 0), (4, 0), (64, 0), (2, 200)])
-def test_attention_decode_ragged(nh, nkv, hd, pps, window):
-    """The split decode kernel against the plain formula: sequences of very different lengths, a
-    padding sequence, scrambled pages, poisoned cache outside the sequences, several split sizes."""
+def test_attention_decode_ragged(kernel, nh, nkv, hd, pps, window):
+    """The split decode kernels (CUDA cores; tensor cores for grouped queries) against the plain formula: sequences
+    of very different lengths, a padding sequence, scrambled pages, poisoned cache outside the sequences,
+    several split sizes."""
     kk = K()
+    attend, _ = decode_kernel(kk, kernel)
     rng = np.random.default_rng(1)
     lens = [1, 64, 65, 700, 0, 129, 1000]
     P = 16
@@ -423,7 +444,7 @@ def test_attention_decode_ragged(nh, nkv, hd, pps, window):
     part = torch.empty(kk.attention_decode_workspace(S, nh, hd, P, pps), device="cuda")
     scale = 1 / math.sqrt(hd)
     for _ in range(2):          # twice: the tickets must come back to zero
-        kk.attention_decode(q, out, kc, vc, pages.cuda(), kvlen, qstart, nh, nkv, hd, scale, window, part, pps)
+        attend(q, out, kc, vc, pages.cuda(), kvlen, qstart, nh, nkv, hd, scale, window, part, pps)
     kk.check_device_errors("cuda:0")
     assert int(kk.tc_scratch("cuda:0").attn_tickets.abs().sum()) == 0
     for s_, n in enumerate(lens):
@@ -436,13 +457,14 @@ def test_attention_decode_ragged(nh, nkv, hd, pps, window):
         assert rel(out[s_].reshape(nh, hd), torch.from_numpy(ref)) < 1e-2, (s_, n)
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(32, 32, 64), (15, 5, 64), (8, 2, 128), (8, 8, 32), (16, 2, 64)])
+@pytest.mark.parametrize("kernel,nh,nkv,hd", DECODE_SHAPES)
 @pytest.mark.parametrize("pps,window,rot,write", [(1, 0, True, True), (4, 0, True, True), (64, 0, False, True),
                                                   (2, 200, True, True), (4, 0, True, False)])
-def test_attention_decode_fused_rotation_same_bits(nh, nkv, hd, pps, window, rot, write):
-    """The decode kernel with the position encoding fused in (q rotated on the fly, the new k and v appended
+def test_attention_decode_fused_rotation_same_bits(kernel, nh, nkv, hd, pps, window, rot, write):
+    """A decode kernel with the position encoding fused in (q rotated on the fly, the new k and v appended
     by the block that reads their page) gives the bits of the two kernels it replaces: outputs and caches."""
     kk = K()
+    attend, attend_fused = decode_kernel(kk, kernel)
     rng = np.random.default_rng(2)
     lens = [1, 64, 65, 700, 0, 129, 1000, 128]       # lengths AFTER this step (0: padding)
     P, n_pages = 16, 56
@@ -473,14 +495,13 @@ def test_attention_decode_fused_rotation_same_bits(nh, nkv, hd, pps, window, rot
     q2, kc2, vc2 = qkv.clone(), kc.clone(), vc.clone()
     out2 = torch.full((S, nh * hd), 7.0, device="cuda", dtype=torch.bfloat16)
     kk.rope_store(q2, inv, rdim, tok_seq, tok_pos, pages_d, 64, kc2, vc2, nh, nkv, hd, True)
-    kk.attention_decode(q2, out2, kc2, vc2, pages_d, kvlen, qstart, nh, nkv, hd, scale, window, part, pps)
+    attend(q2, out2, kc2, vc2, pages_d, kvlen, qstart, nh, nkv, hd, scale, window, part, pps)
     # one kernel (write=False: the cache holds the new entries already, as for a call that reads another call's cache)
     q1 = qkv.clone()
     kc1, vc1 = (kc.clone(), vc.clone()) if write else (kc2.clone(), vc2.clone())
     out1 = torch.full((S, nh * hd), 7.0, device="cuda", dtype=torch.bfloat16)
     for _ in range(2):      # a second run over the cache it has written itself gives the same
-        kk.attention_decode_fused(q1, out1, kc1, vc1, pages_d, kvlen, qstart, nh, nkv, hd, scale, window, part, pps,
-                                  inv, rdim, write)
+        attend_fused(q1, out1, kc1, vc1, pages_d, kvlen, qstart, nh, nkv, hd, scale, window, part, pps, inv, rdim, write)
     kk.check_device_errors("cuda:0")
     assert torch.equal(q1, qkv)                                  # the fused kernel leaves its input alone
     assert torch.equal(out1, out2)

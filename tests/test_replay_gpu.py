@@ -167,14 +167,16 @@ def test_causality(loaded):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_smollm2_135m_layer_sizes(tmp_path, dtype):
-    """Two layers at SmolLM2-135M sizes (9 heads over 3 kv heads of 64, width 576, vocabulary 49,152): the
-    kernels' fast paths for real head shapes (group of 3, vocabulary that is no power of two) against the
-    plain implementation, prompt whole and then decoded."""
+@pytest.mark.parametrize("sizes", [(576, 9, 3, 64, 1536), (320, 14, 2, 128, 520)])
+def test_smollm2_135m_layer_sizes(tmp_path, dtype, sizes):
+    """Two layers at SmolLM2-135M sizes (9 heads over 3 kv heads of 64, width 576, vocabulary 49,152), and two
+    with 14 heads over 2 kv heads of 128: the kernels' fast paths for real head shapes (groups of 3 and 7,
+    a vocabulary that is no power of two) against the plain implementation, prompt whole and then decoded."""
     import torch
     import llmi_b200 as L
-    cfg = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 576, "num_attention_heads": 9,
-           "num_key_value_heads": 3, "intermediate_size": 1536, "vocab_size": 49152, "rope_theta": 100000.0,
+    width, nh, nkv, hd, ffn = sizes
+    cfg = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": width, "num_attention_heads": nh,
+           "num_key_value_heads": nkv, "head_dim": hd, "intermediate_size": ffn, "vocab_size": 49152, "rope_theta": 100000.0,
            "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 8192, "hidden_act": "silu",
            "eos_token_id": 0}
     L.write_random_model(str(tmp_path), cfg, 8, torch.float32 if dtype == "float32" else torch.bfloat16)
