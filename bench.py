@@ -196,6 +196,8 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print its numbers (for profiling one kernel class; not a bench line)")
+    ap.add_argument("--kv-heads", type=int, default=None,
+                    help="with --only: another number of key/value heads (grouped queries), to profile their kernels")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -213,6 +215,11 @@ def main():
     import llmi_b200 as L
     pk, pk_kind = peaks()
     cfg = dict(CONFIG, num_hidden_layers=args.layers)
+    if args.kv_heads is not None:
+        if args.only is None:
+            print("bench.py: --kv-heads changes the model's shape; it goes with --only (no bench line)")
+            return 2
+        cfg["num_key_value_heads"] = args.kv_heads
     t0 = time.time()
     model = L.random_model(cfg, seed=0, dtype="bfloat16", on_device=True)
     weight_bytes = model.weight_bytes()
@@ -224,7 +231,7 @@ def main():
     if args.only == "decode":
         ms, launches, *_ = decode_run(model, args.batch, args.context, steps, warmup)
         print(json.dumps({"only": "decode", "ms_per_step": round(ms, 4), "batch": args.batch, "layers": args.layers,
-                          "gpu_launches": launches}))
+                          "kv_heads": cfg["num_key_value_heads"], "gpu_launches": launches}))
         return 0
 
     clocks = ClockSampler()
