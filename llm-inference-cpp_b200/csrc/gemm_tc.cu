@@ -318,14 +318,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 //   full[s]      in the leader; 64 KB expected per stage (both SMs' A and B halves)
 //   empty[s]     in each SM; signalled by the leader's tcgen05.commit, multicast to the pair
 //   acc_full[b]  in each SM (multicast commit);  acc_empty[b] in the leader, 8 arrivals (4 warps x 2 SMs)
-constexpr int TP_BN = 256;
+constexpr int TP_BN = 256;              // widest token tile; an accumulator's columns in TMEM
 constexpr int TP_STAGES = 6;
 constexpr int TP_STAGE_BYTES = 2 * TC_BM * TC_BK * 2;   // A half-tile + B half-tile, 16 KB each
 constexpr int TP_SMEM = TP_STAGES * TP_STAGE_BYTES + 1024 + 8 * (2 * TP_STAGES + 4) + 16;
 
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p,
-                    int m_tiles, int n_tiles) {   // tiles of 256 weight rows x 256 tokens
+                    int m_tiles, int n_tiles, int bn) {   // tiles of 256 weight rows x bn tokens (bn % 16 == 0, <= 256)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bars = base + TP_STAGES * TP_STAGE_BYTES;
@@ -379,17 +379,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           const int s = it % TP_STAGES;
           if (it >= TP_STAGES && !mbar_wait(empty_bar(s), ((it / TP_STAGES) - 1) & 1, p.error_flag, 5)) { ok = false; break; }
           const uint32_t leader_full = map_to_rank(full_bar(s), 0);
-          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * TP_STAGE_BYTES);
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * (TC_BM * TC_BK * 2 + (bn >> 1) * TC_BK * 2));
           const uint32_t dst = base + s * TP_STAGE_BYTES;
           tma_load_2d_pair(dst, &map_w, i * TC_BK, mt * 256 + (int)rank * TC_BM, leader_full);
-          tma_load_2d_pair(dst + TC_BM * TC_BK * 2, &map_x, i * TC_BK, nt * TP_BN + (int)rank * 128, leader_full);
+          tma_load_2d_pair(dst + TC_BM * TC_BK * 2, &map_x, i * TC_BK, nt * bn + (int)rank * (bn >> 1), leader_full);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
-      // ---- MMA issuer (leader only): D fp32, A and B bf16 K-major, M = 256 over the pair, N = 256 ----
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TP_BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+      // ---- MMA issuer (leader only): D fp32, A and B bf16 K-major, M = 256 over the pair, N = bn ----
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
       int it = 0, j = 0;
       bool ok = true;
       for (int u = pair; u < n_units && ok; u += n_pairs, ++j) {
@@ -421,12 +421,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const int mt = u % m_tiles, nt = u / m_tiles;
       const int b = j & 1;
       const int m = mt * 256 + (int)rank * TC_BM + quad * 32 + lane;
-      const int n0 = nt * TP_BN;
+      const int n0 = nt * bn;
       const uint32_t t_base = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(b * TP_BN);
       const uint32_t leader_empty = map_to_rank(acc_empty(b), 0);
       if (!mbar_wait(acc_full(b), (j >> 1) & 1, p.error_flag, 8)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int nch = (min(TP_BN, p.n_tok - n0) + 15) / 16;
+      const int nch = (min(bn, p.n_tok - n0) + 15) / 16;
       if (p.mode == OUT_ADD_F32) {
         const bool row_ok = m < p.m_out;
         const float bias = (p.bias && row_ok) ? p.bias[m] : 0.f;
@@ -476,7 +476,35 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   }
 }
 
-static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int m_tiles, int n_tiles,
+// Width of the token tile for a product on pairs of SMs.  The 74 pairs take the (256 rows x bn tokens) tiles in
+// rounds, and a last round that is nearly empty costs as much as a full one: 2,048 tokens x 6,144 rows are 192
+// tiles of 256 tokens (2.6 rounds, paid as 3), but 216 tiles of 240 tokens (2.9 rounds of 240/256 the length).
+// A narrower tile also needs more bytes from L2 per flop (128 weight rows + bn/2 token rows a stage and SM), which
+// bounds the tile's time from below.
+static int pair_token_tile(int n_tok, int m_out) {
+  static int fixed = -1;
+  if (fixed < 0) {
+    const char* e = getenv("LLMI_TC_PAIR_BN");
+    fixed = e ? atoi(e) : 0;
+  }
+  if (fixed >= 128 && fixed <= 256 && fixed % 16 == 0) return fixed;
+  const long m_tiles = (m_out + 255) / 256;
+  int best = TP_BN;
+  double best_cost = 0;
+  for (int bn = TP_BN; bn >= 128; bn -= 16) {
+    const long units = m_tiles * ((n_tok + bn - 1) / bn);
+    const long rounds = (units + 73) / 74;
+    const double by_loads = 0.93 * (256 + bn) / 2;
+    const double cost = rounds * (bn > by_loads ? bn : by_loads);
+    if (bn == TP_BN || cost < best_cost * 0.97) {
+      best = bn;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
+
+static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int m_tiles, int n_tiles, int bn,
                           cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
@@ -500,7 +528,7 @@ static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, TcParams
   attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled(PDL_GEMM) ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mw, mx, p, m_tiles, n_tiles) == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH;
+  return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mw, mx, p, m_tiles, n_tiles, bn) == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -870,10 +898,11 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
     pair_ok = (e && e[0] == '0') ? 0 : 1;
   }
   if (pair_ok && n_tok >= 512 && splits == 1) {
-    rc = make_map(&mx, x, n_tok, k, ldx, 128);
+    const int pbn = pair_token_tile(n_tok, m_out);
+    rc = make_map(&mx, x, n_tok, k, ldx, pbn / 2);
     if (rc != LLMI_OK) return rc;
     TcParams pp{m_out, n_tok, k, y, ldy, bias, mode, 1, workspace, tickets, error_flag};
-    return launch_tc_pair(mw, mx, pp, (m_out + 255) / 256, (n_tok + 255) / 256, stream);
+    return launch_tc_pair(mw, mx, pp, (m_out + 255) / 256, (n_tok + pbn - 1) / pbn, pbn, stream);
   }
   rc = make_map(&mx, x, n_tok, k, ldx, bn);
   if (rc != LLMI_OK) return rc;
