@@ -76,8 +76,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   auto full_bar = [&](int s) { return bars + 8u * s; };
 
   pdl_launch_dependents();
-  // which sequence and which block of 128 queries (late blocks, which see more keys, come first)
-  int mb = gridDim.x - 1 - blockIdx.x;
+  // which sequence and which block of 128 queries: late blocks, which see more keys, come first, for ALL heads (the
+  // head is the fast grid index: a long block that starts late is the kernel's tail)
+  int mb = gridDim.y - 1 - blockIdx.y;
   int seq = 0, q_start = 0, q_len = 0;
   for (; seq < p.n_seqs; ++seq) {
     q_start = p.seq_q_start[seq];
@@ -87,7 +88,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     mb -= nb;
   }
   if (seq >= p.n_seqs) return;
-  const int head = blockIdx.y;
+  const int head = blockIdx.x;
   const int kvh = head / (p.n_heads / p.n_kv_heads);
   const int kv_len = p.seq_kv_len[seq];
   const int pos0 = kv_len - q_len;              // position of the sequence's first query in this step
@@ -312,7 +313,8 @@ static int launch_prefill(const CUtensorMap& mk, const CUtensorMap& mv, const Pr
       return LLMI_ERR_LAUNCH;
     configured = true;
   }
-  dim3 grid(n_blocks, p.n_heads);
+  if (n_blocks > 65535) return LLMI_ERR_BAD_SIZE;
+  dim3 grid(p.n_heads, n_blocks);
   attention_prefill_kernel<HD><<<grid, PF_THREADS, SMEM, stream>>>(mk, mv, p);
   return launch_status();
 }

@@ -6,26 +6,29 @@
 //
 //   S_j = Q · K_jᵀ        tcgen05.mma, M = 128 queries on TMEM lanes, N = 64 keys on TMEM columns
 //   softmax               four warps, ONE QUERY ROW PER THREAD: tcgen05.ld of the row, mask, maximum, exp2,
-//                         sum — no shuffles; P_j goes to shared memory as bf16 in the swizzled layout an MMA
-//                         A-operand wants
-//   O += P_j · V_j        tcgen05.mma again (V is the MN-major B operand, straight from the cache page),
-//                         ACCUMULATING in TMEM over the pages
+//                         sum — no shuffles; P_j goes back to TENSOR MEMORY as bf16 pairs, over the first
+//                         half of the S row the thread has just read (tcgen05.st)
+//   O += P_j · V_j        tcgen05.mma with the A operand in TMEM (V is the MN-major B operand, straight from
+//                         the cache page), ACCUMULATING in TMEM over the pages
+//
+// S_j lies in buffer j & 1, so S_{j+1} is computed while the softmax of S_j runs, and the softmax warps wait
+// for nothing else: MMAs of one thread run in issue order, which is what lets S_{j+1} overwrite the buffer of
+// P_{j-1} right after O += P_{j-1} V_{j-1} was issued.  No P tile in shared memory, no async-proxy fence, no
+// hand-back of S.
 //
 // The accumulator is scaled lazily: P_j and O are kept relative to a reference maximum that follows the
 // row's running maximum only when that has grown by more than 8 (in base 2), so P stays below 256 and the
-// read-multiply-write of O in TMEM happens a few times per row instead of once per page; the final division
-// by the row sum makes the result the same.
+// read-multiply-write of O in TMEM happens a few times per row instead of once per page (only then is
+// O += P_{j-1} V_{j-1} waited for); the final division by the row sum makes the result the same.
 //
 // A causal prompt's query blocks differ 16-fold in the keys they see, and the kernel is as long as its longest
 // block: with `split_pages` > 0 a block's key range is cut into parts of that many pages, each part a block of
 // its own that leaves (reference maximum, sum, unnormalised output) per row in a workspace; the part that takes
 // a (query block, head)'s last ticket adds the parts in key order and writes the output.
 //
-// A block is small on purpose (64 KB of shared memory, 128 TMEM columns, 192 threads): three are resident
-// per SM and hide one another's chain S -> softmax -> PV.  Roles: warp 0 = TMA producer (Q once, then
-// K_j / V_j pages into a ring of two), warp 1 = TMEM allocation and MMA issue, warps 2..5 = softmax and
-// output.  S_{j+1} is computed while the softmax of S_j runs (the softmax frees S as soon as it has read
-// it).  Every wait is bounded (see sm100.cuh).
+// A block has 64 KB of shared memory (Q, three K/V stages), 256 TMEM columns (S0, S1, O) and 192 threads: two
+// are resident per SM.  Roles: warp 0 = TMA producer (Q once, then K_j / V_j pages into the ring), warp 1 =
+// TMEM allocation and MMA issue, warps 2..5 = softmax and output.  Every wait is bounded (see sm100.cuh).
 #include <cuda.h>
 #include <math.h>
 
@@ -35,13 +38,13 @@
 namespace llmi {
 
 constexpr int FT_BM = 128, FT_PAGE = 64, FT_HD = 64;
-constexpr int FT_STAGES = 2;
-constexpr int FT_THREADS = 192;
+constexpr int FT_STAGES = 3;
+constexpr int FT_THREADS = 320;                     // producer warp, MMA warp, 8 softmax warps
+constexpr int FT_HALF = FT_PAGE / 2;                  // keys of a page per softmax thread
 constexpr int FT_TILE = FT_PAGE * FT_HD * 2;          // 8 KB: one K or V page tile
 constexpr int FT_QBYTES = FT_BM * FT_HD * 2;          // 16 KB
-constexpr int FT_PBYTES = FT_BM * FT_PAGE * 2;        // 16 KB
-constexpr int FT_SMEM = FT_QBYTES + FT_STAGES * 2 * FT_TILE + FT_PBYTES + 1024 + 128;
-constexpr int FT_TMEM_COLS = 128;                     // S at columns 0..63, O at 64..127
+constexpr int FT_SMEM = FT_QBYTES + FT_STAGES * 2 * FT_TILE + 1024 + 128;
+constexpr int FT_TMEM_COLS = 256;                     // S_j (then P_j) at columns 64 * (j & 1); O of key half h at 128 + 64 * h
 constexpr float FT_LAZY = 8.0f;                       // the reference maximum follows the running one in steps of 2^8
 
 struct PrefillTcParams {
@@ -58,7 +61,7 @@ struct PrefillTcParams {
   int* error_flag;
   int n_tiles;              // blocks of 128 queries over all sequences
   int split_pages;          // 0: a query block's keys are one job; else jobs of at most this many pages
-  float* partials;          // [job (gridDim.x)][head][66][128]: per row m_ref, l, O[64], when split
+  float* partials;          // [job (gridDim.y)][head][66][128]: per row m_ref, l, O[64], when split
   int* tickets;             // [n_tiles * n_heads], zero before and after the launch
 };
 
@@ -107,30 +110,51 @@ __device__ __forceinline__ void ft_st16(uint32_t taddr, const float* v) {
 }
 __device__ __forceinline__ void ft_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-__global__ void __launch_bounds__(FT_THREADS, 3)
+
+__device__ __forceinline__ void ft_mma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's TMEM lane, written; no wait
+__device__ __forceinline__ void ft_st16u(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+
+__global__ void __launch_bounds__(FT_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, PrefillTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem = base;
   const uint32_t kv_smem = base + FT_QBYTES;                        // stage s: K at +s*16K, V at +s*16K+8K
-  const uint32_t p_smem = kv_smem + FT_STAGES * 2 * FT_TILE;
-  const uint32_t bars = p_smem + FT_PBYTES;
-  // barriers: q_full, kv_full[2], kv_empty[2], s_full, s_free, p_ready, o_done, tmem slot
+  const uint32_t bars = kv_smem + FT_STAGES * 2 * FT_TILE;
+  // barriers: q_full, kv_full[stages], kv_empty[stages], s_full[2], p_ready[2], o_done, tmem slot
   const uint32_t q_full = bars;
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bars + 8u * (1 + FT_STAGES + s); };
-  const uint32_t s_full = bars + 8u * (1 + 2 * FT_STAGES);
-  const uint32_t s_free = s_full + 8u, p_ready = s_full + 16u, o_done = s_full + 24u;
-  const uint32_t tmem_slot = s_full + 32u;
+  auto s_full = [&](int b) { return bars + 8u * (1 + 2 * FT_STAGES + b); };
+  auto p_ready = [&](int b) { return bars + 8u * (3 + 2 * FT_STAGES + b); };
+  const uint32_t o_done = bars + 8u * (5 + 2 * FT_STAGES);
+  const uint32_t tmem_slot = o_done + 8u;
 
   pdl_launch_dependents();
-  // which sequence, which block of 128 queries and which part of its keys: jobs are counted from the last
+  // The head is the FAST grid index and the job the slow one: blocks start in the order of their linear index, and a
+  // long job that starts late is the kernel's tail (with the head as the slow index the longest job of the last head
+  // started when the kernel was half over: 51 us for 2,048 tokens x 32 heads against 33 us this way).
+  // Which sequence, which block of 128 queries and which part of its keys: jobs are counted from the last
   // block of the last sequence backwards (late blocks, which see more keys, come first), a block's parts in key order
+  const int job = blockIdx.y;
   int seq = p.n_seqs - 1, mb = 0, part = 0, n_parts = 1, tile_id = p.n_tiles;
   int q_start = 0, q_len = 0, kv_len = 0, pos0 = 0, m0 = 0, rows_here = 0, first_q = 0, last_q = 0, pg_first = 0, n_pg = 0;
   {
-    int x = blockIdx.x;
+    int x = job;
     bool found = false;
     for (; seq >= 0 && !found; --seq) {
       q_start = p.seq_q_start[seq];
@@ -162,10 +186,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     pg_first += part * p.split_pages;
     n_pg = min(p.split_pages, n_pg - part * p.split_pages);
   }
-  const int head = blockIdx.y;
+  const int head = blockIdx.x;
   const int kvh = head / (p.n_heads / p.n_kv_heads);
   const int32_t* pages = p.seq_pages + (size_t)seq * p.pages_stride;
   __shared__ int s_last;
+  __shared__ float s_ml[2][FT_BM][2];      // (reference maximum, sum) of a row's two key halves
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -177,9 +202,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(s_free, 4);
-    mbar_init(p_ready, 4);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(s_full(b), 1);
+      mbar_init(p_ready(b), 8);
+    }
     mbar_init(o_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -192,7 +218,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   uint32_t tmem;
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem) : "r"(tmem_slot));
-  const uint32_t tmem_s = tmem, tmem_o = tmem + 64;
+  const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -212,14 +238,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   } else if (warp == 1) {
     if (lane == 0) {
       // ---- MMA issuer ----
-      // S: A = Q (K-major), B = K page (K-major), N = 64.  O: A = P (K-major), B = V page (MN-major), N = 64.
+      // S: A = Q (shared, K-major), B = K page (K-major), N = 64.  O: A = P (TMEM: 128 lanes x 32 columns of bf16
+      // pairs, over the first half of the S buffer it came from), B = V page (MN-major), N = 64.  MMAs of one thread
+      // run in issue order: S_{j+1} may be issued into the buffer that P_{j-1} lies in right after O += P_{j-1} V_{j-1}.
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
       const uint32_t idesc_o = idesc_s | (1u << 16);
       auto issue_s = [&](int j) {
         const uint64_t a = ft_desc(q_smem), b = ft_desc(kv_smem + (j % FT_STAGES) * 2 * FT_TILE);
+        const uint32_t d = tmem_s + (uint32_t)(64 * (j & 1));
 #pragma unroll
-        for (int k4 = 0; k4 < FT_HD / 16; ++k4) ft_mma(tmem_s, a + 2 * k4, b + 2 * k4, idesc_s, k4 > 0);
-        ft_commit(s_full);
+        for (int k4 = 0; k4 < FT_HD / 16; ++k4) ft_mma(d, a + 2 * k4, b + 2 * k4, idesc_s, k4 > 0);
+        ft_commit(s_full(j & 1));
       };
       bool ok = mbar_wait(q_full, 0, p.error_flag, 42) && mbar_wait(kv_full(0), 0, p.error_flag, 43);
       if (ok) {
@@ -228,58 +257,64 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       for (int j = 0; j < n_pg && ok; ++j) {
         if (j + 1 < n_pg) {
-          // S_{j+1} as soon as its page is here and the softmax has read S_j
-          ok = mbar_wait(kv_full((j + 1) % FT_STAGES), ((j + 1) / FT_STAGES) & 1, p.error_flag, 44) &&
-               mbar_wait(s_free, j & 1, p.error_flag, 45);
+          // S_{j+1} as soon as its page is here: the softmax of S_j runs meanwhile
+          ok = mbar_wait(kv_full((j + 1) % FT_STAGES), ((j + 1) / FT_STAGES) & 1, p.error_flag, 44);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           issue_s(j + 1);
         }
-        ok = mbar_wait(p_ready, j & 1, p.error_flag, 46);
+        ok = mbar_wait(p_ready(j & 1), (j >> 1) & 1, p.error_flag, 46);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t a = ft_desc(p_smem);
+        const uint32_t a = tmem_s + (uint32_t)(64 * (j & 1));
         const uint64_t b = ft_desc(kv_smem + (j % FT_STAGES) * 2 * FT_TILE + FT_TILE);
+        // keys 32h .. 32h+31 accumulate into their own O (their softmax threads keep their own reference maximum):
+        // P of half h lies at columns 32h .. 32h+15 of the S buffer; 16 keys further: 8 columns of P, 16 rows of V
 #pragma unroll
-        for (int k4 = 0; k4 < FT_PAGE / 16; ++k4)   // 16 keys further: +32 bytes in a P row, +16 rows of 128 bytes in V
-          ft_mma(tmem_o, a + 2 * k4, b + (uint64_t)(k4 * ((16 * 128) >> 4)), idesc_o, (j > 0 || k4 > 0) ? 1u : 0u);
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int k4 = 0; k4 < FT_HALF / 16; ++k4)
+            ft_mma_ts(tmem_o + (uint32_t)(64 * h), a + (uint32_t)(32 * h + 8 * k4),
+                      b + (uint64_t)((2 * h + k4) * ((16 * 128) >> 4)), idesc_o, (j > 0 || k4 > 0) ? 1u : 0u);
         ft_commit(o_done);
         ft_commit(kv_empty(j % FT_STAGES));
       }
     }
   } else {
-    // ---- softmax and output: one query row per thread ----
+    // ---- softmax and output: two threads per query row, each with one half of a page's keys ----
+    // The two halves are independent streams (own running maximum, reference maximum, sum and O) that meet only
+    // at the end: no exchange inside the page loop, and twice the warps to hide one another's latencies.
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;                 // keys 32*half .. 32*half+31 of every page
     const int row = quad * 32 + lane;                 // row of the 128-query block = TMEM lane
     const int qrow = m0 + row;
     const bool row_ok = qrow < q_len;
     const int qpos = pos0 + qrow;
     const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
+    const uint32_t t_o = tmem_o + t_lane + (uint32_t)(64 * half);
     float m_run = -INFINITY, m_ref = -INFINITY, l_run = 0.f;   // maxima in base 2, scaled
     bool ok = true;
     for (int j = 0; j < n_pg && ok; ++j) {
-      ok = mbar_wait(s_full, j & 1, p.error_flag, 48);
+      ok = mbar_wait(s_full(j & 1), (j >> 1) & 1, p.error_flag, 48);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      float sc[FT_PAGE];
+      const uint32_t t_s = tmem_s + t_lane + (uint32_t)(64 * (j & 1) + FT_HALF * half);
+      float sc[FT_HALF];
 #pragma unroll
-      for (int c = 0; c < FT_PAGE; c += 16) ft_ld16(tmem_s + t_lane + (uint32_t)c, sc + c);
+      for (int c = 0; c < FT_HALF; c += 16) ft_ld16(t_s + (uint32_t)c, sc + c);
       ft_ld_wait();
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_free);
-      const int key0 = (pg_first + j) * FT_PAGE;
-      const bool need_mask = (key0 + FT_PAGE - 1 > first_q) || (p.window > 0);
+      const int key0 = (pg_first + j) * FT_PAGE + FT_HALF * half;
+      const bool need_mask = (key0 + FT_HALF - 1 > first_q) || (p.window > 0);
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < FT_PAGE; ++c) {
+        for (int c = 0; c < FT_HALF; ++c) {
           const int key = key0 + c;
           if (key > qpos || (p.window > 0 && key < qpos - p.window + 1)) sc[c] = -INFINITY;
         }
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one long one
 #pragma unroll
-      for (int c = 0; c < FT_PAGE; c += 8) {
+      for (int c = 0; c < FT_HALF; c += 8) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], fmaxf(sc[c + 2 * u], sc[c + 2 * u + 1]));
       }
@@ -295,9 +330,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // two keys per instruction where the hardware has it (fma.rn.f32x2, add.rn.f32x2)
       float2 sum2[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
       const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg2 = make_float2(neg_ref, neg_ref);
-      uint32_t packed[FT_PAGE / 2];
+      uint32_t packed[FT_HALF / 2];
 #pragma unroll
-      for (int c = 0; c < FT_PAGE; c += 2) {
+      for (int c = 0; c < FT_HALF; c += 2) {
         const float2 x = __ffma2_rn(make_float2(sc[c], sc[c + 1]), scale2, neg2);
         const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));          // 2^(-inf) = 0 for masked keys
         sum2[(c >> 1) & 3] = __fadd2_rn(sum2[(c >> 1) & 3], e);
@@ -309,95 +344,107 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const float2 t = __fadd2_rn(a, b);
         l_run += t.x + t.y;
       }
-      if (j >= 1) {
-        // O += P_{j-1} V_{j-1} has to be finished: P's buffer is written below, and O may be rescaled
+      if (j >= 1 && __any_sync(0xffffffffu, corr != 1.f)) {
+        // this half's O is rescaled in place: O += P_{j-1} V_{j-1} has to be finished (it may still run beside this softmax)
         ok = mbar_wait(o_done, (j - 1) & 1, p.error_flag, 49);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll
-          for (int c = 0; c < FT_HD; c += 16) {
-            float t[16];
-            ft_ld16(tmem_o + t_lane + (uint32_t)c, t);
-            ft_ld_wait();
+        for (int c = 0; c < FT_HD; c += 16) {
+          float t[16];
+          ft_ld16(t_o + (uint32_t)c, t);
+          ft_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 16; ++e) t[e] *= corr;
-            ft_st16(tmem_o + t_lane + (uint32_t)c, t);
-          }
-          ft_st_wait();
+          for (int e = 0; e < 16; ++e) t[e] *= corr;
+          ft_st16(t_o + (uint32_t)c, t);
         }
       }
-      // P row -> shared memory, swizzled as an MMA operand (chunk c of row r at r*128 + ((c ^ (r & 7)) << 4))
-      const uint32_t prow = p_smem + (uint32_t)row * 128;
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(prow + (uint32_t)(((c ^ (row & 7)) << 4))),
-                     "r"(packed[4 * c]), "r"(packed[4 * c + 1]), "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3])
-                     : "memory");
-      if (key0 + FT_PAGE > kv_len) {
+      // P half-row -> TMEM, over the first half of the S columns this thread has just read: 16 columns of bf16 pairs
+      ft_st16u(t_s, packed);
+      ft_st_wait();
+      if (key0 - FT_HALF * half + FT_PAGE > kv_len) {
         // The sequence ends inside this page: value rows behind its end are cleared so that their zero
         // probabilities cannot meet a NaN.  (The page is in shared memory: S_j was computed from it.)
         const uint32_t v_tile = kv_smem + (j % FT_STAGES) * 2 * FT_TILE + FT_TILE;
-        const int first_bad = kv_len - key0;
-        for (int idx = (warp - 2) * 32 + lane; idx < (FT_PAGE - first_bad) * 8; idx += 128) {
+        const int first_bad = kv_len - (key0 - FT_HALF * half);
+        for (int idx = (warp - 2) * 32 + lane; idx < (FT_PAGE - first_bad) * 8; idx += 256) {
           const int r = first_bad + (idx >> 3), ch = idx & 7;
           asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(v_tile + (uint32_t)(r * 128 + (ch << 4))), "r"(0u) : "memory");
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA's reads
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA's reads
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_ready);
+      if (lane == 0) mbar_arrive(p_ready(j & 1));
     }
     {
       // (a warp whose wait gave up still goes through the barriers below: nobody is left waiting for it)
       const bool fine = ok && mbar_wait(o_done, (n_pg - 1) & 1, p.error_flag, 50);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      float o[FT_HD];
+      // the row's two halves meet: (reference maximum, sum) through shared memory, the two O's straight from TMEM;
+      // each of the row's two threads finishes 32 of the 64 output dims
+      s_ml[half][row][0] = m_ref;
+      s_ml[half][row][1] = l_run;
+      asm volatile("bar.sync 1, 256;" ::: "memory");          // the eight softmax warps
+      const float m_a = s_ml[0][row][0], m_b = s_ml[1][row][0];
+      float M = fmaxf(m_a, m_b);
+      const float w_a = (m_a == -INFINITY) ? 0.f : fast_exp2(m_a - M), w_b = (m_b == -INFINITY) ? 0.f : fast_exp2(m_b - M);
+      float L = s_ml[0][row][1] * w_a + s_ml[1][row][1] * w_b;
+      constexpr int DH = FT_HD / 2;                             // output dims of this thread: DH*half ..
+      float o[DH];
+      {
+        float oa[DH], ob[DH];
 #pragma unroll
-      for (int c = 0; c < FT_HD; c += 16) ft_ld16(tmem_o + t_lane + (uint32_t)c, o + c);
-      ft_ld_wait();
+        for (int c = 0; c < DH; c += 16) {
+          ft_ld16(tmem_o + t_lane + (uint32_t)(DH * half + c), oa + c);
+          ft_ld16(tmem_o + t_lane + (uint32_t)(64 + DH * half + c), ob + c);
+        }
+        ft_ld_wait();
+#pragma unroll
+        for (int c = 0; c < DH; ++c) o[c] = w_a * oa[c] + w_b * ob[c];
+      }
       bool write_out = fine;
       if (n_parts > 1) {
-        // this part's (m_ref, l, O) to the workspace; the part that comes last adds them all in key order
+        // this part's (maximum, sum, O) to the workspace; the part that comes last adds them all in key order
         const size_t slot_floats = (size_t)(FT_HD + 2) * FT_BM;
-        float* mine = p.partials + ((size_t)blockIdx.x * p.n_heads + head) * slot_floats + row;
-        mine[0] = m_ref;
-        mine[FT_BM] = l_run;
+        float* mine = p.partials + ((size_t)job * p.n_heads + head) * slot_floats + row;
+        if (half == 0) {
+          mine[0] = M;
+          mine[FT_BM] = L;
+        }
 #pragma unroll
-        for (int c = 0; c < FT_HD; ++c) mine[(size_t)(2 + c) * FT_BM] = o[c];
+        for (int c = 0; c < DH; ++c) mine[(size_t)(2 + DH * half + c) * FT_BM] = o[c];
         __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");          // the four softmax warps
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         int* ticket = p.tickets + tile_id * p.n_heads + head;
         if (threadIdx.x == 64) s_last = (atomicAdd(ticket, 1) == n_parts - 1);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         write_out = fine && s_last != 0;
         if (s_last != 0) {
           __threadfence();
-          const float* first = p.partials + ((size_t)(blockIdx.x - part) * p.n_heads + head) * slot_floats + row;
+          const float* first = p.partials + ((size_t)(job - part) * p.n_heads + head) * slot_floats + row;
           const size_t part_stride = (size_t)p.n_heads * slot_floats;
-          float M = -INFINITY;
+          M = -INFINITY;
           for (int z = 0; z < n_parts; ++z) M = fmaxf(M, __ldcg(first + z * part_stride));
-          float L = 0.f;
+          L = 0.f;
 #pragma unroll
-          for (int c = 0; c < FT_HD; ++c) o[c] = 0.f;
+          for (int c = 0; c < DH; ++c) o[c] = 0.f;
           for (int z = 0; z < n_parts; ++z) {
             const float* pz = first + z * part_stride;
             const float mz = __ldcg(pz);
             const float w = (mz == -INFINITY) ? 0.f : fast_exp2(mz - M);
             L = fmaf(__ldcg(pz + FT_BM), w, L);
 #pragma unroll
-            for (int c = 0; c < FT_HD; ++c) o[c] = fmaf(w, __ldcg(pz + (size_t)(2 + c) * FT_BM), o[c]);
+            for (int c = 0; c < DH; ++c) o[c] = fmaf(w, __ldcg(pz + (size_t)(2 + DH * half + c) * FT_BM), o[c]);
           }
-          l_run = L;
           if (threadIdx.x == 64) *ticket = 0;
         }
       }
       if (write_out && row_ok) {
-        const float inv = 1.f / l_run;
-        __nv_bfloat16* dst = p.out + (size_t)(q_start + qrow) * p.ldo + (size_t)head * FT_HD;
+        const float inv = 1.f / L;
+        __nv_bfloat16* dst = p.out + (size_t)(q_start + qrow) * p.ldo + (size_t)head * FT_HD + DH * half;
 #pragma unroll
-        for (int c = 0; c < FT_HD; c += 8) {
+        for (int c = 0; c < DH; c += 8) {
           uint4 v;
           __nv_bfloat162 h0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv), h1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
           __nv_bfloat162 h2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv), h3 = __floats2bfloat162_rn(o[c + 6] * inv, o[c + 7] * inv);
@@ -455,7 +502,7 @@ LLMI_EXPORT int llmi_attention_prefill_tc(const void* q, long ldq, long n_tokens
                                           int window, int n_jobs, int split_pages, float* partials, long partials_floats,
                                           int* tickets, int n_tickets, int* error_flag, cudaStream_t stream) {
   if (n_seqs <= 0 || n_blocks <= 0 || n_heads <= 0 || n_kv_heads <= 0 || n_cache_pages <= 0 || n_tokens <= 0) return LLMI_ERR_BAD_SIZE;
-  if (n_heads % n_kv_heads || n_heads > 65535) return LLMI_ERR_BAD_SIZE;
+  if (n_heads % n_kv_heads) return LLMI_ERR_BAD_SIZE;
   if (head_dim != FT_HD) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)q & 15) || (ldq & 7) || ((uintptr_t)out & 15) || (ldo & 7) || ((uintptr_t)k_cache & 15) ||
       ((uintptr_t)v_cache & 15))
@@ -486,7 +533,8 @@ LLMI_EXPORT int llmi_attention_prefill_tc(const void* q, long ldq, long n_tokens
   }
   PrefillTcParams p{(__nv_bfloat16*)out, ldo, seq_pages, seq_q_start, seq_kv_len, pages_stride, n_seqs, n_heads,
                     n_kv_heads, scale * 1.4426950408889634f, window, error_flag, n_blocks, split_pages, partials, tickets};
-  dim3 grid(n_jobs, n_heads);
+  if (n_jobs > 65535) return LLMI_ERR_BAD_SIZE;
+  dim3 grid(n_heads, n_jobs);
   attention_prefill_tc_kernel<<<grid, FT_THREADS, FT_SMEM, stream>>>(mq, mk, mv, p);
   return launch_status();
 }
