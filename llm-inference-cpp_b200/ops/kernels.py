@@ -525,7 +525,7 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, s
         c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), _stream()))
 
 
-# Which prompt-attention kernel runs for head size 64: "tc" (tcgen05: about 55 us for a 2,048-token prompt of 32
+# Which prompt-attention kernel runs for head size 64: "tc" (tcgen05: about 43 us for a 2,048-token prompt of 32
 # heads) or "mma" (mma.sync: 95 us; the kernel for head size 128).
 _PREFILL_ATTENTION = os.environ.get("LLMI_PREFILL_ATTENTION", "tc")     # "mma": the mma.sync kernel for every head size
 _FORCE_GENERIC_ATTENTION = os.environ.get("LLMI_ATTENTION", "") == "generic"
@@ -595,12 +595,13 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
     if (not ctx.decode and qkv.dtype == torch.bfloat16 and page_size == 64 and not _FORCE_GENERIC_ATTENTION
             and attention_prefill_supported(head_dim)):
         if head_dim == 64 and _PREFILL_ATTENTION == "tc" and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
-            # A step with fewer (query block, head) jobs than the device holds blocks (3 per SM) leaves SMs idle and
-            # is as long as its longest job: then the key ranges are cut (see the kernel's head).  With more jobs
-            # the cut gains nothing (measured: 2,048 tokens x 32 heads, 8.43 ms a prefill with it, 8.37 without).
+            # A step with fewer (query block, head) jobs than the device has SMs leaves SMs idle and is as long as its
+            # longest job: then the key ranges are cut (see the kernel's head).  Measured: 2,048 tokens x 8 heads 28.0 ->
+            # 22.2 us, x 4 heads 27.5 -> 21.0 us; with 256 jobs and more the cut gains nothing or costs (4,096 x 8:
+            # 49.3 -> 50.5 us; 2,048 x 32: 42.1 -> 49.6 us).
             split = None
             q_lens, kv_lens = getattr(ctx, "host_q_lens", None), getattr(ctx, "host_kv_lens", None)
-            if _PREFILL_SPLIT and rt is not None and q_lens is not None and ctx.n_q_blocks * n_heads < 3 * 148:
+            if _PREFILL_SPLIT and rt is not None and q_lens is not None and ctx.n_q_blocks * n_heads < 148:
                 jobs = prefill_split_jobs(q_lens, kv_lens, window, PREFILL_SPLIT_PAGES)
                 if jobs > ctx.n_q_blocks:
                     ws = rt.scratch("attn_prefill_partials", (jobs * n_heads * 66 * 128,), torch.float32)
