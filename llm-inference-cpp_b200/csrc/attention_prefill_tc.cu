@@ -1,13 +1,15 @@
-// Prefill attention on the 5th-generation tensor cores (tcgen05), bf16, head size 64.
+// Prefill attention on the 5th-generation tensor cores (tcgen05), bf16, head size 64 or 128.
 //
 // Same operation as attention_prefill.cu (reference loop: src/model/transformer.cpp:263-282): causal
 // grouped-query attention of the prompts of a step over their cache pages.  A block takes 128 queries of
 // one sequence and one query head and walks the pages (64 keys) the queries can see:
 //
 //   S_j = Q · K_jᵀ        tcgen05.mma, M = 128 queries on TMEM lanes, N = 64 keys on TMEM columns
-//   softmax               four warps, ONE QUERY ROW PER THREAD: tcgen05.ld of the row, mask, maximum, exp2,
-//                         sum — no shuffles; P_j goes back to TENSOR MEMORY as bf16 pairs, over the first
-//                         half of the S row the thread has just read (tcgen05.st)
+//   softmax               a thread owns a query row's share of the page (all 64 keys at head size 128; 32 keys
+//                         at head size 64, where two threads share a row, each with its own running maximum,
+//                         sum and O that meet only at the end): tcgen05.ld, mask, maximum, exp2, sum — no
+//                         shuffles; P_j goes back to TENSOR MEMORY as bf16 pairs, over the first half of the
+//                         S columns the thread has just read (tcgen05.st)
 //   O += P_j · V_j        tcgen05.mma with the A operand in TMEM (V is the MN-major B operand, straight from
 //                         the cache page), ACCUMULATING in TMEM over the pages
 //
@@ -26,9 +28,11 @@
 // its own that leaves (reference maximum, sum, unnormalised output) per row in a workspace; the part that takes
 // a (query block, head)'s last ticket adds the parts in key order and writes the output.
 //
-// A block has 64 KB of shared memory (Q, three K/V stages), 256 TMEM columns (S0, S1, O) and 192 threads: two
-// are resident per SM.  Roles: warp 0 = TMA producer (Q once, then K_j / V_j pages into the ring), warp 1 =
-// TMEM allocation and MMA issue, warps 2..5 = softmax and output.  Every wait is bounded (see sm100.cuh).
+// A block has 64 KB (head size 128: 96 KB) of shared memory (Q, three (two) K/V stages) and 256 TMEM columns
+// (S0, S1, O): two are resident per SM.  Roles: warp 0 = TMA producer (Q once, then K_j / V_j pages into the
+// ring), warp 1 = TMEM allocation and MMA issue, warps 2.. = softmax and output (eight at head size 64, four at
+// 128).  tcgen05.ld and .st are warp-wide instructions: no lane may skip them (rows past a sequence's end are
+// computed and not stored).  Every wait is bounded (see sm100.cuh).
 #include <cuda.h>
 #include <math.h>
 
@@ -37,15 +41,25 @@
 
 namespace llmi {
 
-constexpr int FT_BM = 128, FT_PAGE = 64, FT_HD = 64;
-constexpr int FT_STAGES = 3;
-constexpr int FT_THREADS = 320;                     // producer warp, MMA warp, 8 softmax warps
-constexpr int FT_HALF = FT_PAGE / 2;                  // keys of a page per softmax thread
-constexpr int FT_TILE = FT_PAGE * FT_HD * 2;          // 8 KB: one K or V page tile
-constexpr int FT_QBYTES = FT_BM * FT_HD * 2;          // 16 KB
-constexpr int FT_SMEM = FT_QBYTES + FT_STAGES * 2 * FT_TILE + 1024 + 128;
-constexpr int FT_TMEM_COLS = 256;                     // S_j (then P_j) at columns 64 * (j & 1); O of key half h at 128 + 64 * h
+constexpr int FT_BM = 128, FT_PAGE = 64;
+constexpr int FT_SUB = FT_PAGE * 64 * 2;              // 8 KB: 64 rows x 64 columns of bf16, one swizzled sub-tile
+constexpr int FT_TMEM_COLS = 256;                     // S_j (then P_j) at columns 64 * (j & 1); O of key half h at 128 + HD * h
 constexpr float FT_LAZY = 8.0f;                       // the reference maximum follows the running one in steps of 2^8
+
+// Head size 64: two softmax threads per query row (HALVES = 2), each with 32 keys of a page and an O of 64 columns.
+// Head size 128: one thread per row with all 64 keys and an O of 128 columns.  Either way S0, S1 and O fill 256
+// TMEM columns and two blocks are resident per SM.
+template <int HD>
+struct FtCfg {
+  static constexpr int NSUB = HD / 64;                        // 64-column sub-tiles of a Q, K or V tile
+  static constexpr int HALVES = 128 / HD;
+  static constexpr int KEYS = FT_PAGE / HALVES;               // keys of a page per softmax thread
+  static constexpr int THREADS = 64 + 128 * HALVES;           // producer warp, MMA warp, 4 * HALVES softmax warps
+  static constexpr int STAGES = HD == 64 ? 3 : 2;
+  static constexpr int TILE = NSUB * FT_SUB;                  // one K or V page
+  static constexpr int QBYTES = 2 * NSUB * FT_SUB;            // 128 query rows
+  static constexpr int SMEM = QBYTES + STAGES * 2 * TILE + 1024 + 128;
+};
 
 struct PrefillTcParams {
   __nv_bfloat16* out;
@@ -61,7 +75,7 @@ struct PrefillTcParams {
   int* error_flag;
   int n_tiles;              // blocks of 128 queries over all sequences
   int split_pages;          // 0: a query block's keys are one job; else jobs of at most this many pages
-  float* partials;          // [job (gridDim.y)][head][66][128]: per row m_ref, l, O[64], when split
+  float* partials;          // [job (gridDim.y)][head][HD + 2][128]: per row m_ref, l, O[HD], when split
   int* tickets;             // [n_tiles * n_heads], zero before and after the launch
 };
 
@@ -127,21 +141,24 @@ __device__ __forceinline__ void ft_st16u(uint32_t taddr, const uint32_t* v) {
       : "memory");
 }
 
-__global__ void __launch_bounds__(FT_THREADS, 2)
+template <int HD>
+__global__ void __launch_bounds__(FtCfg<HD>::THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, PrefillTcParams p) {
+  using C = FtCfg<HD>;
+  constexpr int STAGES = C::STAGES, NSUB = C::NSUB, HALVES = C::HALVES, KEYS = C::KEYS;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t q_smem = base;
-  const uint32_t kv_smem = base + FT_QBYTES;                        // stage s: K at +s*16K, V at +s*16K+8K
-  const uint32_t bars = kv_smem + FT_STAGES * 2 * FT_TILE;
+  const uint32_t q_smem = base;                                      // sub-tile u (dims 64u..): + u * 16 KB
+  const uint32_t kv_smem = base + C::QBYTES;                         // stage s: K at + s * 2 * TILE, V a TILE further
+  const uint32_t bars = kv_smem + STAGES * 2 * C::TILE;
   // barriers: q_full, kv_full[stages], kv_empty[stages], s_full[2], p_ready[2], o_done, tmem slot
   const uint32_t q_full = bars;
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto kv_empty = [&](int s) { return bars + 8u * (1 + FT_STAGES + s); };
-  auto s_full = [&](int b) { return bars + 8u * (1 + 2 * FT_STAGES + b); };
-  auto p_ready = [&](int b) { return bars + 8u * (3 + 2 * FT_STAGES + b); };
-  const uint32_t o_done = bars + 8u * (5 + 2 * FT_STAGES);
+  auto kv_empty = [&](int s) { return bars + 8u * (1 + STAGES + s); };
+  auto s_full = [&](int b) { return bars + 8u * (1 + 2 * STAGES + b); };
+  auto p_ready = [&](int b) { return bars + 8u * (3 + 2 * STAGES + b); };
+  const uint32_t o_done = bars + 8u * (5 + 2 * STAGES);
   const uint32_t tmem_slot = o_done + 8u;
 
   pdl_launch_dependents();
@@ -198,13 +215,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
     mbar_init(q_full, 1);
-    for (int s = 0; s < FT_STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(s_full(b), 1);
-      mbar_init(p_ready(b), 8);
+      mbar_init(p_ready(b), 4 * HALVES);
     }
     mbar_init(o_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -224,30 +241,37 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (lane == 0) {
       // ---- producer ----
       pdl_wait();   // q and the cache pages of this step come from the kernels before
-      mbar_expect_tx(q_full, FT_QBYTES);
-      ft_tma(q_smem, &map_q, head * FT_HD, q_start + m0, q_full);
+      mbar_expect_tx(q_full, C::QBYTES);
+#pragma unroll
+      for (int u = 0; u < NSUB; ++u) ft_tma(q_smem + u * 2 * FT_SUB, &map_q, head * HD + 64 * u, q_start + m0, q_full);
       for (int j = 0; j < n_pg; ++j) {
-        const int s = j % FT_STAGES;
-        if (j >= FT_STAGES && !mbar_wait(kv_empty(s), ((j / FT_STAGES) - 1) & 1, p.error_flag, 41)) break;
+        const int s = j % STAGES;
+        if (j >= STAGES && !mbar_wait(kv_empty(s), ((j / STAGES) - 1) & 1, p.error_flag, 41)) break;
         const int row = (pages[pg_first + j] * p.n_kv_heads + kvh) * FT_PAGE;
-        mbar_expect_tx(kv_full(s), 2 * FT_TILE);
-        ft_tma(kv_smem + s * 2 * FT_TILE, &map_k, 0, row, kv_full(s));
-        ft_tma(kv_smem + s * 2 * FT_TILE + FT_TILE, &map_v, 0, row, kv_full(s));
+        mbar_expect_tx(kv_full(s), 2 * C::TILE);
+#pragma unroll
+        for (int u = 0; u < NSUB; ++u) {
+          ft_tma(kv_smem + s * 2 * C::TILE + u * FT_SUB, &map_k, 64 * u, row, kv_full(s));
+          ft_tma(kv_smem + s * 2 * C::TILE + C::TILE + u * FT_SUB, &map_v, 64 * u, row, kv_full(s));
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // ---- MMA issuer ----
-      // S: A = Q (shared, K-major), B = K page (K-major), N = 64.  O: A = P (TMEM: 128 lanes x 32 columns of bf16
-      // pairs, over the first half of the S buffer it came from), B = V page (MN-major), N = 64.  MMAs of one thread
-      // run in issue order: S_{j+1} may be issued into the buffer that P_{j-1} lies in right after O += P_{j-1} V_{j-1}.
+      // S: A = Q (shared, K-major), B = K page (K-major), N = 64 keys, k over the head's dims (sub-tiles of 64).
+      // O: A = P (TMEM: 128 lanes x 32 columns of bf16 pairs, over the first half of the S buffer it came from),
+      // B = V page (MN-major), N = 64 dims per MMA (one per 64-column sub-tile of V).  MMAs of one thread run in
+      // issue order: S_{j+1} may be issued into the buffer that P_{j-1} lies in right after O += P_{j-1} V_{j-1}.
       const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
       const uint32_t idesc_o = idesc_s | (1u << 16);
       auto issue_s = [&](int j) {
-        const uint64_t a = ft_desc(q_smem), b = ft_desc(kv_smem + (j % FT_STAGES) * 2 * FT_TILE);
         const uint32_t d = tmem_s + (uint32_t)(64 * (j & 1));
 #pragma unroll
-        for (int k4 = 0; k4 < FT_HD / 16; ++k4) ft_mma(d, a + 2 * k4, b + 2 * k4, idesc_s, k4 > 0);
+        for (int k4 = 0; k4 < HD / 16; ++k4) {
+          const uint64_t a = ft_desc(q_smem + (k4 / 4) * 2 * FT_SUB), b = ft_desc(kv_smem + (j % STAGES) * 2 * C::TILE + (k4 / 4) * FT_SUB);
+          ft_mma(d, a + 2 * (k4 % 4), b + 2 * (k4 % 4), idesc_s, k4 > 0);
+        }
         ft_commit(s_full(j & 1));
       };
       bool ok = mbar_wait(q_full, 0, p.error_flag, 42) && mbar_wait(kv_full(0), 0, p.error_flag, 43);
@@ -258,7 +282,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int j = 0; j < n_pg && ok; ++j) {
         if (j + 1 < n_pg) {
           // S_{j+1} as soon as its page is here: the softmax of S_j runs meanwhile
-          ok = mbar_wait(kv_full((j + 1) % FT_STAGES), ((j + 1) / FT_STAGES) & 1, p.error_flag, 44);
+          ok = mbar_wait(kv_full((j + 1) % STAGES), ((j + 1) / STAGES) & 1, p.error_flag, 44);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           issue_s(j + 1);
@@ -267,54 +291,58 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a = tmem_s + (uint32_t)(64 * (j & 1));
-        const uint64_t b = ft_desc(kv_smem + (j % FT_STAGES) * 2 * FT_TILE + FT_TILE);
-        // keys 32h .. 32h+31 accumulate into their own O (their softmax threads keep their own reference maximum):
-        // P of half h lies at columns 32h .. 32h+15 of the S buffer; 16 keys further: 8 columns of P, 16 rows of V
+        const uint32_t v_tile = kv_smem + (j % STAGES) * 2 * C::TILE + C::TILE;
+        // the keys of half h accumulate into their own O (their softmax threads keep their own reference maximum):
+        // P of half h lies at columns 32h.. of the S buffer; 16 keys further: 8 columns of P, 16 rows of 128 bytes of V
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+        for (int h = 0; h < HALVES; ++h)
 #pragma unroll
-          for (int k4 = 0; k4 < FT_HALF / 16; ++k4)
-            ft_mma_ts(tmem_o + (uint32_t)(64 * h), a + (uint32_t)(32 * h + 8 * k4),
-                      b + (uint64_t)((2 * h + k4) * ((16 * 128) >> 4)), idesc_o, (j > 0 || k4 > 0) ? 1u : 0u);
+          for (int k4 = 0; k4 < KEYS / 16; ++k4)
+#pragma unroll
+            for (int u = 0; u < NSUB; ++u)
+              ft_mma_ts(tmem_o + (uint32_t)(HD * h + 64 * u), a + (uint32_t)(32 * h + 8 * k4),
+                        ft_desc(v_tile + u * FT_SUB) + (uint64_t)(((KEYS / 16) * h + k4) * ((16 * 128) >> 4)), idesc_o,
+                        (j > 0 || k4 > 0) ? 1u : 0u);
         ft_commit(o_done);
-        ft_commit(kv_empty(j % FT_STAGES));
+        ft_commit(kv_empty(j % STAGES));
       }
     }
   } else {
-    // ---- softmax and output: two threads per query row, each with one half of a page's keys ----
-    // The two halves are independent streams (own running maximum, reference maximum, sum and O) that meet only
-    // at the end: no exchange inside the page loop, and twice the warps to hide one another's latencies.
+    // ---- softmax and output: HALVES threads per query row, each with its share of a page's keys ----
+    // The halves are independent streams (own running maximum, reference maximum, sum and O) that meet only at the
+    // end: no exchange inside the page loop.
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;                 // keys 32*half .. 32*half+31 of every page
+    const int half = (warp - 2) >> 2;                 // keys KEYS*half .. of every page
     const int row = quad * 32 + lane;                 // row of the 128-query block = TMEM lane
     const int qrow = m0 + row;
     const bool row_ok = qrow < q_len;
     const int qpos = pos0 + qrow;
     const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
-    const uint32_t t_o = tmem_o + t_lane + (uint32_t)(64 * half);
+    const uint32_t t_o = tmem_o + t_lane + (uint32_t)(HD * half);
     float m_run = -INFINITY, m_ref = -INFINITY, l_run = 0.f;   // maxima in base 2, scaled
     bool ok = true;
     for (int j = 0; j < n_pg && ok; ++j) {
       ok = mbar_wait(s_full(j & 1), (j >> 1) & 1, p.error_flag, 48);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t t_s = tmem_s + t_lane + (uint32_t)(64 * (j & 1) + FT_HALF * half);
-      float sc[FT_HALF];
+      const uint32_t t_s = tmem_s + t_lane + (uint32_t)(64 * (j & 1) + KEYS * half);
+      float sc[KEYS];
 #pragma unroll
-      for (int c = 0; c < FT_HALF; c += 16) ft_ld16(t_s + (uint32_t)c, sc + c);
+      for (int c = 0; c < KEYS; c += 16) ft_ld16(t_s + (uint32_t)c, sc + c);
       ft_ld_wait();
-      const int key0 = (pg_first + j) * FT_PAGE + FT_HALF * half;
-      const bool need_mask = (key0 + FT_HALF - 1 > first_q) || (p.window > 0);
+      const int page_key0 = (pg_first + j) * FT_PAGE;
+      const int key0 = page_key0 + KEYS * half;
+      const bool need_mask = (key0 + KEYS - 1 > first_q) || (p.window > 0);
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < FT_HALF; ++c) {
+        for (int c = 0; c < KEYS; ++c) {
           const int key = key0 + c;
           if (key > qpos || (p.window > 0 && key < qpos - p.window + 1)) sc[c] = -INFINITY;
         }
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains instead of one long one
 #pragma unroll
-      for (int c = 0; c < FT_HALF; c += 8) {
+      for (int c = 0; c < KEYS; c += 8) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], fmaxf(sc[c + 2 * u], sc[c + 2 * u + 1]));
       }
@@ -330,9 +358,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // two keys per instruction where the hardware has it (fma.rn.f32x2, add.rn.f32x2)
       float2 sum2[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
       const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg2 = make_float2(neg_ref, neg_ref);
-      uint32_t packed[FT_HALF / 2];
+      uint32_t packed[KEYS / 2];
 #pragma unroll
-      for (int c = 0; c < FT_HALF; c += 2) {
+      for (int c = 0; c < KEYS; c += 2) {
         const float2 x = __ffma2_rn(make_float2(sc[c], sc[c + 1]), scale2, neg2);
         const float2 e = make_float2(fast_exp2(x.x), fast_exp2(x.y));          // 2^(-inf) = 0 for masked keys
         sum2[(c >> 1) & 3] = __fadd2_rn(sum2[(c >> 1) & 3], e);
@@ -350,7 +378,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int c = 0; c < FT_HD; c += 16) {
+        for (int c = 0; c < HD; c += 16) {
           float t[16];
           ft_ld16(t_o + (uint32_t)c, t);
           ft_ld_wait();
@@ -359,17 +387,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           ft_st16(t_o + (uint32_t)c, t);
         }
       }
-      // P half-row -> TMEM, over the first half of the S columns this thread has just read: 16 columns of bf16 pairs
-      ft_st16u(t_s, packed);
+      // P -> TMEM, over the first half of the S columns this thread has just read: bf16 pairs, 16 columns at a time
+#pragma unroll
+      for (int c = 0; c < KEYS / 2; c += 16) ft_st16u(t_s + (uint32_t)c, packed + c);
       ft_st_wait();
-      if (key0 - FT_HALF * half + FT_PAGE > kv_len) {
+      if (page_key0 + FT_PAGE > kv_len) {
         // The sequence ends inside this page: value rows behind its end are cleared so that their zero
         // probabilities cannot meet a NaN.  (The page is in shared memory: S_j was computed from it.)
-        const uint32_t v_tile = kv_smem + (j % FT_STAGES) * 2 * FT_TILE + FT_TILE;
-        const int first_bad = kv_len - (key0 - FT_HALF * half);
-        for (int idx = (warp - 2) * 32 + lane; idx < (FT_PAGE - first_bad) * 8; idx += 256) {
-          const int r = first_bad + (idx >> 3), ch = idx & 7;
-          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(v_tile + (uint32_t)(r * 128 + (ch << 4))), "r"(0u) : "memory");
+        const uint32_t v_tile = kv_smem + (j % STAGES) * 2 * C::TILE + C::TILE;
+        const int first_bad = kv_len - page_key0;
+        for (int idx = (warp - 2) * 32 + lane; idx < (FT_PAGE - first_bad) * 8 * NSUB; idx += 128 * HALVES) {
+          const int r = first_bad + (idx >> 3) / NSUB, u = (idx >> 3) % NSUB, ch = idx & 7;
+          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(v_tile + (uint32_t)(u * FT_SUB + r * 128 + (ch << 4))), "r"(0u) : "memory");
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA's reads
       }
@@ -379,80 +408,110 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     {
       // (a warp whose wait gave up still goes through the barriers below: nobody is left waiting for it)
-      const bool fine = ok && mbar_wait(o_done, (n_pg - 1) & 1, p.error_flag, 50);
+      // (`fine` is the same in all lanes of a warp: the TMEM loads below are warp-wide instructions)
+      const bool fine = __all_sync(0xffffffffu, ok && mbar_wait(o_done, (n_pg - 1) & 1, p.error_flag, 50));
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // the row's two halves meet: (reference maximum, sum) through shared memory, the two O's straight from TMEM;
-      // each of the row's two threads finishes 32 of the 64 output dims
-      s_ml[half][row][0] = m_ref;
-      s_ml[half][row][1] = l_run;
-      asm volatile("bar.sync 1, 256;" ::: "memory");          // the eight softmax warps
-      const float m_a = s_ml[0][row][0], m_b = s_ml[1][row][0];
-      float M = fmaxf(m_a, m_b);
-      const float w_a = (m_a == -INFINITY) ? 0.f : fast_exp2(m_a - M), w_b = (m_b == -INFINITY) ? 0.f : fast_exp2(m_b - M);
-      float L = s_ml[0][row][1] * w_a + s_ml[1][row][1] * w_b;
-      constexpr int DH = FT_HD / 2;                             // output dims of this thread: DH*half ..
-      float o[DH];
-      {
-        float oa[DH], ob[DH];
-#pragma unroll
-        for (int c = 0; c < DH; c += 16) {
-          ft_ld16(tmem_o + t_lane + (uint32_t)(DH * half + c), oa + c);
-          ft_ld16(tmem_o + t_lane + (uint32_t)(64 + DH * half + c), ob + c);
-        }
-        ft_ld_wait();
-#pragma unroll
-        for (int c = 0; c < DH; ++c) o[c] = w_a * oa[c] + w_b * ob[c];
+      // A row's halves meet: (reference maximum, sum) through shared memory, the O's straight from TMEM; each of the
+      // row's threads finishes DH of the output dims, 32 at a time.
+      constexpr int DH = HD / HALVES;
+      float M = m_ref, L = l_run, w_a = 1.f, w_b = 0.f;
+      if (HALVES == 2) {
+        s_ml[half][row][0] = m_ref;
+        s_ml[half][row][1] = l_run;
+        asm volatile("bar.sync 1, %0;" ::"n"(128 * HALVES) : "memory");          // the softmax warps
+        const float m_a = s_ml[0][row][0], m_b = s_ml[1][row][0];
+        M = fmaxf(m_a, m_b);
+        w_a = (m_a == -INFINITY) ? 0.f : fast_exp2(m_a - M);
+        w_b = (m_b == -INFINITY) ? 0.f : fast_exp2(m_b - M);
+        L = s_ml[0][row][1] * w_a + s_ml[1][row][1] * w_b;
       }
-      bool write_out = fine;
+      const uint32_t t_mine = tmem_o + t_lane + (uint32_t)(DH * half);          // this thread's dims in the first O
+      const size_t slot_floats = (size_t)(HD + 2) * FT_BM;
+      const size_t part_stride = (size_t)p.n_heads * slot_floats;
+      bool write_out = fine, merge = false;
       if (n_parts > 1) {
         // this part's (maximum, sum, O) to the workspace; the part that comes last adds them all in key order
-        const size_t slot_floats = (size_t)(FT_HD + 2) * FT_BM;
         float* mine = p.partials + ((size_t)job * p.n_heads + head) * slot_floats + row;
         if (half == 0) {
           mine[0] = M;
           mine[FT_BM] = L;
         }
+#pragma unroll 1
+        for (int c0 = 0; c0 < DH; c0 += 32) {
+          float oa[32], ob[32];
+          ft_ld16(t_mine + (uint32_t)c0, oa);
+          ft_ld16(t_mine + (uint32_t)(c0 + 16), oa + 16);
+          if (HALVES == 2) {
+            ft_ld16(t_mine + (uint32_t)(HD + c0), ob);
+            ft_ld16(t_mine + (uint32_t)(HD + c0 + 16), ob + 16);
+          }
+          ft_ld_wait();
 #pragma unroll
-        for (int c = 0; c < DH; ++c) mine[(size_t)(2 + DH * half + c) * FT_BM] = o[c];
+          for (int c = 0; c < 32; ++c)
+            mine[(size_t)(2 + DH * half + c0 + c) * FT_BM] = HALVES == 2 ? w_a * oa[c] + w_b * ob[c] : oa[c];
+        }
         __threadfence();
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(128 * HALVES) : "memory");
         int* ticket = p.tickets + tile_id * p.n_heads + head;
         if (threadIdx.x == 64) s_last = (atomicAdd(ticket, 1) == n_parts - 1);
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        write_out = fine && s_last != 0;
-        if (s_last != 0) {
+        asm volatile("bar.sync 1, %0;" ::"n"(128 * HALVES) : "memory");
+        merge = s_last != 0;
+        write_out = fine && merge;
+        if (merge) {
           __threadfence();
           const float* first = p.partials + ((size_t)(job - part) * p.n_heads + head) * slot_floats + row;
-          const size_t part_stride = (size_t)p.n_heads * slot_floats;
           M = -INFINITY;
           for (int z = 0; z < n_parts; ++z) M = fmaxf(M, __ldcg(first + z * part_stride));
           L = 0.f;
-#pragma unroll
-          for (int c = 0; c < DH; ++c) o[c] = 0.f;
           for (int z = 0; z < n_parts; ++z) {
-            const float* pz = first + z * part_stride;
-            const float mz = __ldcg(pz);
-            const float w = (mz == -INFINITY) ? 0.f : fast_exp2(mz - M);
-            L = fmaf(__ldcg(pz + FT_BM), w, L);
-#pragma unroll
-            for (int c = 0; c < DH; ++c) o[c] = fmaf(w, __ldcg(pz + (size_t)(2 + DH * half + c) * FT_BM), o[c]);
+            const float mz = __ldcg(first + z * part_stride);
+            L = fmaf(__ldcg(first + z * part_stride + FT_BM), (mz == -INFINITY) ? 0.f : fast_exp2(mz - M), L);
           }
           if (threadIdx.x == 64) *ticket = 0;
         }
       }
-      if (write_out && row_ok) {
+      if (write_out) {      // every lane takes part in the TMEM loads; only the rows that exist are stored
         const float inv = 1.f / L;
-        __nv_bfloat16* dst = p.out + (size_t)(q_start + qrow) * p.ldo + (size_t)head * FT_HD + DH * half;
+        __nv_bfloat16* dst = p.out + (size_t)(q_start + qrow) * p.ldo + (size_t)head * HD + DH * half;
+#pragma unroll 1
+        for (int c0 = 0; c0 < DH; c0 += 32) {
+          float o[32];
+          if (merge) {
+            const float* first = p.partials + ((size_t)(job - part) * p.n_heads + head) * slot_floats + row;
 #pragma unroll
-        for (int c = 0; c < DH; c += 8) {
-          uint4 v;
-          __nv_bfloat162 h0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv), h1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
-          __nv_bfloat162 h2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv), h3 = __floats2bfloat162_rn(o[c + 6] * inv, o[c + 7] * inv);
-          v.x = *reinterpret_cast<uint32_t*>(&h0);
-          v.y = *reinterpret_cast<uint32_t*>(&h1);
-          v.z = *reinterpret_cast<uint32_t*>(&h2);
-          v.w = *reinterpret_cast<uint32_t*>(&h3);
-          *reinterpret_cast<uint4*>(dst + c) = v;
+            for (int c = 0; c < 32; ++c) o[c] = 0.f;
+            for (int z = 0; z < n_parts; ++z) {
+              const float* pz = first + z * part_stride;
+              const float mz = __ldcg(pz);
+              const float w = (mz == -INFINITY) ? 0.f : fast_exp2(mz - M);
+#pragma unroll
+              for (int c = 0; c < 32; ++c) o[c] = fmaf(w, __ldcg(pz + (size_t)(2 + DH * half + c0 + c) * FT_BM), o[c]);
+            }
+          } else {
+            float ob[32];
+            ft_ld16(t_mine + (uint32_t)c0, o);
+            ft_ld16(t_mine + (uint32_t)(c0 + 16), o + 16);
+            if (HALVES == 2) {
+              ft_ld16(t_mine + (uint32_t)(HD + c0), ob);
+              ft_ld16(t_mine + (uint32_t)(HD + c0 + 16), ob + 16);
+            }
+            ft_ld_wait();
+            if (HALVES == 2) {
+#pragma unroll
+              for (int c = 0; c < 32; ++c) o[c] = w_a * o[c] + w_b * ob[c];
+            }
+          }
+#pragma unroll
+          for (int c = 0; c < 32 && row_ok; c += 8) {
+            uint4 v;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv), h1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv), h3 = __floats2bfloat162_rn(o[c + 6] * inv, o[c + 7] * inv);
+            v.x = *reinterpret_cast<uint32_t*>(&h0);
+            v.y = *reinterpret_cast<uint32_t*>(&h1);
+            v.z = *reinterpret_cast<uint32_t*>(&h2);
+            v.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(dst + c0 + c) = v;
+          }
         }
       }
     }
@@ -492,9 +551,26 @@ static int ft_make_map(CUtensorMap* map, const void* ptr, long rows, long cols, 
 
 using namespace llmi;
 
-LLMI_EXPORT int llmi_attention_prefill_tc_supported(int head_dim) { return head_dim == 64; }
+LLMI_EXPORT int llmi_attention_prefill_tc_supported(int head_dim) { return head_dim == 64 || head_dim == 128; }
 
-// q: [n_tokens, >= n_heads*64] rotated queries (row pitch ldq, 16-byte aligned rows); otherwise as llmi_attention_prefill.
+namespace llmi {
+template <int HD>
+static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillTcParams& p, dim3 grid,
+                     cudaStream_t stream) {
+  using C = FtCfg<HD>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
+      return LLMI_ERR_LAUNCH;
+    configured = true;
+  }
+  attention_prefill_tc_kernel<HD><<<grid, C::THREADS, C::SMEM, stream>>>(mq, mk, mv, p);
+  return launch_status();
+}
+}  // namespace llmi
+
+// q: [n_tokens, >= n_heads*head_dim] rotated queries (row pitch ldq, 16-byte aligned rows); otherwise as llmi_attention_prefill.
+// With split_pages > 0: partials holds n_jobs * n_heads * (head_dim + 2) * 128 floats.
 LLMI_EXPORT int llmi_attention_prefill_tc(const void* q, long ldq, long n_tokens, void* out, long ldo, const void* k_cache,
                                           const void* v_cache, long n_cache_pages, const int32_t* seq_pages,
                                           int pages_stride, const int32_t* seq_q_start, const int32_t* seq_kv_len,
@@ -503,29 +579,23 @@ LLMI_EXPORT int llmi_attention_prefill_tc(const void* q, long ldq, long n_tokens
                                           int* tickets, int n_tickets, int* error_flag, cudaStream_t stream) {
   if (n_seqs <= 0 || n_blocks <= 0 || n_heads <= 0 || n_kv_heads <= 0 || n_cache_pages <= 0 || n_tokens <= 0) return LLMI_ERR_BAD_SIZE;
   if (n_heads % n_kv_heads) return LLMI_ERR_BAD_SIZE;
-  if (head_dim != FT_HD) return LLMI_ERR_UNSUPPORTED;
+  if (!llmi_attention_prefill_tc_supported(head_dim)) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)q & 15) || (ldq & 7) || ((uintptr_t)out & 15) || (ldo & 7) || ((uintptr_t)k_cache & 15) ||
       ((uintptr_t)v_cache & 15))
     return LLMI_ERR_ALIGN;
   const long rows = n_cache_pages * n_kv_heads * FT_PAGE;
   if (rows > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
   CUtensorMap mq, mk, mv;
-  int rc = ft_make_map(&mq, q, n_tokens, (long)n_heads * FT_HD, ldq, FT_BM);
+  int rc = ft_make_map(&mq, q, n_tokens, (long)n_heads * head_dim, ldq, FT_BM);
   if (rc != LLMI_OK) return rc;
-  rc = ft_make_map(&mk, k_cache, rows, FT_HD, FT_HD, FT_PAGE);
+  rc = ft_make_map(&mk, k_cache, rows, head_dim, head_dim, FT_PAGE);
   if (rc != LLMI_OK) return rc;
-  rc = ft_make_map(&mv, v_cache, rows, FT_HD, FT_HD, FT_PAGE);
+  rc = ft_make_map(&mv, v_cache, rows, head_dim, head_dim, FT_PAGE);
   if (rc != LLMI_OK) return rc;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FT_SMEM) != cudaSuccess)
-      return LLMI_ERR_LAUNCH;
-    configured = true;
-  }
-  // n_jobs: blocks along x — n_blocks without a split, else the sum over the query blocks of their parts (the caller
+  // n_jobs: blocks along y — n_blocks without a split, else the sum over the query blocks of their parts (the caller
   // counts them with the same rule as the kernel); the workspace holds one slot per job and head
   if (split_pages > 0) {
-    if (n_jobs < n_blocks || !partials || !tickets || (long)n_jobs * n_heads * (FT_HD + 2) * FT_BM > partials_floats ||
+    if (n_jobs < n_blocks || !partials || !tickets || (long)n_jobs * n_heads * (head_dim + 2) * FT_BM > partials_floats ||
         (long)n_blocks * n_heads > n_tickets)
       return LLMI_ERR_BAD_SIZE;
   } else {
@@ -535,6 +605,5 @@ LLMI_EXPORT int llmi_attention_prefill_tc(const void* q, long ldq, long n_tokens
                     n_kv_heads, scale * 1.4426950408889634f, window, error_flag, n_blocks, split_pages, partials, tickets};
   if (n_jobs > 65535) return LLMI_ERR_BAD_SIZE;
   dim3 grid(n_heads, n_jobs);
-  attention_prefill_tc_kernel<<<grid, FT_THREADS, FT_SMEM, stream>>>(mq, mk, mv, p);
-  return launch_status();
+  return head_dim == 64 ? ft_launch<64>(mq, mk, mv, p, grid, stream) : ft_launch<128>(mq, mk, mv, p, grid, stream);
 }

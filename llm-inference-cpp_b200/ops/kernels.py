@@ -465,6 +465,10 @@ def attention_prefill_supported(head_dim: int) -> bool:
     return bool(lib().llmi_attention_prefill_supported(c_int(head_dim)))
 
 
+def attention_prefill_tc_supported(head_dim: int) -> bool:
+    return bool(lib().llmi_attention_prefill_tc_supported(c_int(head_dim)))
+
+
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_q_start, seq_kv_len,
                       n_blocks: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> None:
     """Causal attention of the prompts of a step over their cache pages (bf16, head size 64 or 128, page 64).
@@ -505,10 +509,10 @@ def prefill_split_jobs(q_lens, kv_lens, window: int, split_pages: int) -> int:
 def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_q_start, seq_kv_len,
                          n_blocks: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int = 0,
                          split=None) -> None:
-    """The same prompt attention on the tcgen05 tensor cores (head size 64); arguments as ``attention_prefill``.
+    """The same prompt attention on the tcgen05 tensor cores (head size 64 or 128); arguments as ``attention_prefill``.
     ``split = (n_jobs, split_pages, workspace)``: cut the key range of every query block into jobs of
     ``split_pages`` pages (``n_jobs`` from :func:`prefill_split_jobs`, ``workspace`` fp32 of
-    n_jobs * n_heads * 66 * 128 floats)."""
+    n_jobs * n_heads * (head_dim + 2) * 128 floats)."""
     _need_cuda(q, out, k_cache, v_cache, seq_pages, seq_q_start, seq_kv_len)
     S = seq_pages.shape[0]
     assert q.dtype == out.dtype == k_cache.dtype == torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
@@ -525,8 +529,8 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, s
         c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), _stream()))
 
 
-# Which prompt-attention kernel runs for head size 64: "tc" (tcgen05: about 43 us for a 2,048-token prompt of 32
-# heads) or "mma" (mma.sync: 95 us; the kernel for head size 128).
+# Which prompt-attention kernel runs: "tc" (tcgen05: about 43 us for a 2,048-token prompt of 32 heads of 64) or
+# "mma" (mma.sync: 95 us).
 _PREFILL_ATTENTION = os.environ.get("LLMI_PREFILL_ATTENTION", "tc")     # "mma": the mma.sync kernel for every head size
 _FORCE_GENERIC_ATTENTION = os.environ.get("LLMI_ATTENTION", "") == "generic"
 _PREFILL_SPLIT = os.environ.get("LLMI_PREFILL_SPLIT", "1") != "0"
@@ -594,7 +598,8 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
         raise RuntimeError("attention: rotation can only be fused into the decode kernel (ask attention_fuses_rotation)")
     if (not ctx.decode and qkv.dtype == torch.bfloat16 and page_size == 64 and not _FORCE_GENERIC_ATTENTION
             and attention_prefill_supported(head_dim)):
-        if head_dim == 64 and _PREFILL_ATTENTION == "tc" and qkv.stride(0) % 8 == 0 and out.stride(0) % 8 == 0:
+        if (_PREFILL_ATTENTION == "tc" and attention_prefill_tc_supported(head_dim) and qkv.stride(0) % 8 == 0
+                and out.stride(0) % 8 == 0):
             # A step with fewer (query block, head) jobs than the device has SMs leaves SMs idle and is as long as its
             # longest job: then the key ranges are cut (see the kernel's head).  Measured: 2,048 tokens x 8 heads 28.0 ->
             # 22.2 us, x 4 heads 27.5 -> 21.0 us; with 256 jobs and more the cut gains nothing or costs (4,096 x 8:
@@ -604,7 +609,7 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
             if _PREFILL_SPLIT and rt is not None and q_lens is not None and ctx.n_q_blocks * n_heads < 148:
                 jobs = prefill_split_jobs(q_lens, kv_lens, window, PREFILL_SPLIT_PAGES)
                 if jobs > ctx.n_q_blocks:
-                    ws = rt.scratch("attn_prefill_partials", (jobs * n_heads * 66 * 128,), torch.float32)
+                    ws = rt.scratch("attn_prefill_partials", (jobs * n_heads * (head_dim + 2) * 128,), torch.float32)
                     split = (jobs, PREFILL_SPLIT_PAGES, ws)
             attention_prefill_tc(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_q_start, ctx.seq_kv_len, ctx.n_q_blocks,
                                  n_heads, n_kv_heads, head_dim, scale, window, split)
