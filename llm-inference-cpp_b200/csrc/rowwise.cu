@@ -102,6 +102,47 @@ __global__ void rmsnorm_reg_kernel(const float* __restrict__ x, const float* __r
   }
 }
 
+// The same for MANY rows (a prompt): one warp per row, the row in registers (VPT 16-byte loads in flight per lane),
+// the sum of squares by shuffles — no block barrier between the read and the write of a row.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(256)
+rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ weight, T* __restrict__ out,
+                    const int32_t* __restrict__ rows, int n_rows, int width, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= n_rows) return;
+  const int src = rows ? rows[r] : r;
+  T* o = out + (size_t)r * width;
+  const int nvec = width >> 2;
+  float4 v[VPT];
+  float ss = 0.f;
+  if (src >= 0) {
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * width);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int i = lane + j * 32;
+      v[j] = i < nvec ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) ss = fmaf(v[j].x, v[j].x, fmaf(v[j].y, v[j].y, fmaf(v[j].z, v[j].z, fmaf(v[j].w, v[j].w, ss))));
+  } else {
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+  const float4* wv = reinterpret_cast<const float4*>(weight);
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int i = lane + j * 32;
+    if (i < nvec) {
+      const float4 w = wv[i];
+      store4(o + 4 * i, w.x * (v[j].x * scale), w.y * (v[j].y * scale), w.z * (v[j].z * scale), w.w * (v[j].w * scale));
+    }
+  }
+}
+
 // gate_up is [rows, 2*inner]: gate in the first half of a row, up in the second.
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inner, size_t total) {
@@ -141,6 +182,12 @@ LLMI_EXPORT int llmi_rmsnorm(int out_dtype, const float* x, const float* weight,
   const bool aligned = (width % 4 == 0) && !((uintptr_t)x & 15) && !((uintptr_t)weight & 15) && !((uintptr_t)out & 15);
   constexpr int VPT = 4;
   const int reg_threads = ((width / 4 + VPT - 1) / VPT + 31) / 32 * 32;    // four 16-byte loads per thread
+  // many rows, compute-type output: a warp per row (the 32-bit path keeps one kernel for every number of rows, so that
+  // a row's bits do not depend on how many rows are normalised with it)
+  constexpr int WVPT = 16;                                                  // width <= 2048
+  if (aligned && n_rows >= 512 && width <= 4 * 32 * WVPT && out_dtype == LLMI_DTYPE_BF16)
+    return launch_pdl(PDL_SMALL, rmsnorm_warp_kernel<__nv_bfloat16, WVPT>, (n_rows + 7) / 8, 256, 0, stream, x, weight,
+                      (__nv_bfloat16*)out, rows, n_rows, width, eps);
   if (aligned && reg_threads <= 1024) {
     if (out_dtype == LLMI_DTYPE_F32)
       return launch_pdl(PDL_SMALL, rmsnorm_reg_kernel<float, VPT>, n_rows, reg_threads, 0, stream, x, weight, (float*)out, rows, width, eps);

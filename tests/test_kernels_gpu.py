@@ -52,6 +52,22 @@ def test_rmsnorm(dtype, width, eps):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_rows,width", [(700, 2048), (513, 136), (2048, 960)])
+def test_rmsnorm_many_rows(dtype, n_rows, width):
+    """A prompt's worth of rows (the compute-type output has a kernel of its own from 512 rows on), with padding rows."""
+    x = torch.randn(n_rows, width, device="cuda") * 2
+    w = 1 + 0.1 * torch.randn(width, device="cuda")
+    rows = torch.arange(n_rows, dtype=torch.int32, device="cuda").flip(0).contiguous()
+    rows[5] = -1
+    out = torch.full((n_rows, width), 7.0, device="cuda", dtype=DT[dtype])
+    K().rmsnorm(x, w, out, 1e-5, rows)
+    xd = x.double()[rows.long().clamp(min=0)]
+    ref = w.double() * (xd / torch.sqrt((xd * xd).mean(-1, keepdim=True) + float(np.float32(1e-5))))
+    ref[5] = 0
+    assert rel(out, ref) < (1e-6 if dtype == "float32" else 5e-3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M,N,K_", [(1, 200, 72), (5, 64, 64), (70, 129, 1000), (130, 40, 17), (64, 384, 120)])
 def test_linear_simt_modes(dtype, M, N, K_):
     k = K()
