@@ -189,6 +189,7 @@ rope_store_rows_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ i
 #pragma unroll
   for (int e = 0; e < N; ++e) sincosf((float)pos * inv_freq[i0 + e], &sn[e], &cs[e]);
   T* row = qkv + (size_t)t * ld;
+#pragma unroll 4
   for (int j = hl; j < n_heads; j += ROWS_HEAD_LANES) {
     T* p = row + (size_t)j * hd + i0;
     float a[N], b[N], lo[N], hi[N];
@@ -203,6 +204,7 @@ rope_store_rows_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ i
     Chunk<T>::store(p + half, hi);
   }
   if (!write_kv) return;
+#pragma unroll 4
   for (int h = hl; h < kv.n_kv_heads; h += ROWS_HEAD_LANES) {
     const T* ksrc = row + (size_t)(n_heads + h) * hd + i0;
     const T* vsrc = row + (size_t)(n_heads + kv.n_kv_heads + h) * hd + i0;
