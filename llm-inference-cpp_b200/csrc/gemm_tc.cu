@@ -321,14 +321,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 constexpr int TP_BN = 256;              // widest token tile; an accumulator's columns in TMEM
 constexpr int TP_STAGES = 6;
 constexpr int TP_STAGE_BYTES = 2 * TC_BM * TC_BK * 2;   // A half-tile + B half-tile, 16 KB each
-constexpr int TP_SMEM = TP_STAGES * TP_STAGE_BYTES + 1024 + 8 * (2 * TP_STAGES + 4) + 16;
+constexpr int TP_OUT_BYTES = 16 * TC_BM * 4;             // residual-add epilogue: [16 tokens][128 rows] fp32 on its way out
+constexpr int TP_SMEM = TP_STAGES * TP_STAGE_BYTES + 2 * TP_OUT_BYTES + 1024 + 8 * (2 * TP_STAGES + 4) + 16;
 
 __global__ void __launch_bounds__(TC_THREADS)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p,
-                    int m_tiles, int n_tiles, int bn) {   // tiles of 256 weight rows x bn tokens (bn % 16 == 0, <= 256)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const __grid_constant__ CUtensorMap map_out, TcParams p, int m_tiles, int n_tiles, int bn) {   // tiles of 256 weight rows x bn tokens (bn % 16 == 0, <= 256)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bars = base + TP_STAGES * TP_STAGE_BYTES;
+  const uint32_t out_smem = base + TP_STAGES * TP_STAGE_BYTES;      // two buffers of TP_OUT_BYTES
+  const uint32_t bars = out_smem + 2 * TP_OUT_BYTES;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (TP_STAGES + s); };
   auto acc_full = [&](int b) { return bars + 8u * (2 * TP_STAGES + b); };
@@ -416,7 +418,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     // ---- epilogue warps (both CTAs): this CTA's 128 rows x 256 tokens ----
     const int quad = warp & 3;
     pdl_wait();
-    int j = 0;
+    int j = 0, n_out = 0;       // n_out: chunks this CTA has sent out through shared memory (residual-add epilogue)
     for (int u = pair; u < n_units; u += n_pairs, ++j) {
       const int mt = u % m_tiles, nt = u / m_tiles;
       const int b = j & 1;
@@ -428,30 +430,40 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int nch = (min(bn, p.n_tok - n0) + 15) / 16;
       if (p.mode == OUT_ADD_F32) {
-        const bool row_ok = m < p.m_out;
-        const float bias = (p.bias && row_ok) ? p.bias[m] : 0.f;
-        float* o = (float*)p.out + (size_t)n0 * p.ldo + m;
-        float nxt[16];
-#pragma unroll
-        for (int c = 0; c < 16; ++c) nxt[c] = (row_ok && n0 + c < p.n_tok) ? o[(size_t)c * p.ldo] : 0.f;
+        // out += tile: the tile goes through shared memory ([16 tokens][128 rows] fp32, two buffers) and is ADDED to
+        // the residual stream by TMA (cp.reduce.async.bulk.tensor .add): nothing of the old values comes to the SM, so
+        // the epilogue is a stream of stores instead of a chain of read-modify-write round trips (it is not hidden
+        // behind a next tile when a pair has one tile only: the o and down projections of a 2,048-token prompt).
+        // Rows and tokens past the ends of `out` are clipped by the copy.
+        const float bias = (p.bias && m < p.m_out) ? p.bias[m] : 0.f;
+        const int row_in_cta = quad * 32 + lane;
         for (int ci = 0; ci < nch; ++ci) {
-          float cur[16], v[16];
-#pragma unroll
-          for (int c = 0; c < 16; ++c) cur[c] = nxt[c];
-          if (ci + 1 < nch) {
-#pragma unroll
-            for (int c = 0; c < 16; ++c)
-              nxt[c] = (row_ok && n0 + (ci + 1) * 16 + c < p.n_tok) ? o[(size_t)((ci + 1) * 16 + c) * p.ldo] : 0.f;
-          }
+          float v[16];
           tmem_ld16(t_base + ci * 16, v);
           if (ci == nch - 1) {
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(leader_empty);
           }
+          const uint32_t buf = out_smem + (uint32_t)((n_out & 1) * TP_OUT_BYTES);
+          if (n_out >= 2) {
+            // the copy that read this buffer two chunks ago has to be done with it
+            if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+          }
 #pragma unroll
           for (int c = 0; c < 16; ++c)
-            if (row_ok && n0 + ci * 16 + c < p.n_tok) o[(size_t)(ci * 16 + c) * p.ldo] = cur[c] + (v[c] + bias);
+            asm volatile("st.shared.f32 [%0], %1;" ::"r"(buf + (uint32_t)((c * TC_BM + row_in_cta) * 4)), "f"(v[c] + bias) : "memory");
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (warp == 2 && lane == 0) {
+            asm volatile(
+                "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                ::"l"(&map_out), "r"(mt * 256 + (int)rank * TC_BM), "r"(n0 + ci * 16), "r"(buf)
+                : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          ++n_out;
         }
       } else {
         for (int ci = 0; ci < nch; ++ci) {
@@ -466,6 +478,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
       }
     }
+    // the additions still on their way read this CTA's shared memory: they are done before anybody leaves
+    if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
   // nobody leaves while its partner may still signal it or read its shared memory
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -504,8 +518,8 @@ static int pair_token_tile(int n_tok, int m_out) {
   return best;
 }
 
-static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int m_tiles, int n_tiles, int bn,
-                          cudaStream_t stream) {
+static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, TcParams p, int m_tiles,
+                          int n_tiles, int bn, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM) != cudaSuccess)
@@ -528,7 +542,7 @@ static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, TcParams
   attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled(PDL_GEMM) ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mw, mx, p, m_tiles, n_tiles, bn) == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH;
+  return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mw, mx, mo, p, m_tiles, n_tiles, bn) == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -802,6 +816,19 @@ static int make_map(CUtensorMap* map, const void* ptr, long rows, long k, long l
   return r == CUDA_SUCCESS ? LLMI_OK : LLMI_ERR_DRIVER;
 }
 
+// out [n_tok, m_out] fp32 with row pitch ldo, as [16 tokens][128 rows] boxes for the residual-add epilogue.
+static int make_out_map(CUtensorMap* map, void* out, long n_tok, long m_out, long ldo) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return LLMI_ERR_DRIVER;
+  const cuuint64_t dims[2] = {(cuuint64_t)m_out, (cuuint64_t)n_tok};
+  const cuuint64_t strides[1] = {(cuuint64_t)ldo * 4};
+  const cuuint32_t box[2] = {(cuuint32_t)TC_BM, 16};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LLMI_OK : LLMI_ERR_DRIVER;
+}
+
 template <int BN>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int m_tiles, int n_tiles,
                      cudaStream_t stream) {
@@ -897,12 +924,19 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
     const char* e = getenv("LLMI_TC_PAIR");
     pair_ok = (e && e[0] == '0') ? 0 : 1;
   }
-  if (pair_ok && n_tok >= 512 && splits == 1) {
+  // (the pair kernel adds into the residual stream by TMA: y must then be 16-byte aligned with a pitch of whole 16 bytes)
+  const bool pair_out_ok = mode != OUT_ADD_F32 || (!((uintptr_t)y & 15) && !(ldy & 3));
+  if (pair_ok && n_tok >= 512 && splits == 1 && pair_out_ok) {
     const int pbn = pair_token_tile(n_tok, m_out);
     rc = make_map(&mx, x, n_tok, k, ldx, pbn / 2);
     if (rc != LLMI_OK) return rc;
     TcParams pp{m_out, n_tok, k, y, ldy, bias, mode, 1, workspace, tickets, error_flag};
-    return launch_tc_pair(mw, mx, pp, (m_out + 255) / 256, (n_tok + pbn - 1) / pbn, pbn, stream);
+    CUtensorMap mo = mx;      // only the residual-add epilogue uses it
+    if (mode == OUT_ADD_F32) {
+      rc = make_out_map(&mo, y, n_tok, m_out, ldy);
+      if (rc != LLMI_OK) return rc;
+    }
+    return launch_tc_pair(mw, mx, mo, pp, (m_out + 255) / 256, (n_tok + pbn - 1) / pbn, pbn, stream);
   }
   rc = make_map(&mx, x, n_tok, k, ldx, bn);
   if (rc != LLMI_OK) return rc;
