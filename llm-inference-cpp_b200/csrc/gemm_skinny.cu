@@ -169,6 +169,20 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     for (int n = 0; n < NT; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
+    // residual add: the old values of this tile's outputs are asked for now and used after the k loop (nobody else
+    // writes them), so the tile does not end with a round trip to L2
+    constexpr int OLD = NPAD * SK_ROWS / (SK_CONSUMERS * 32);
+    float old[OLD], norm_w[OLD];
+    if (p.mode == SK_ADD_F32) {
+#pragma unroll
+      for (int r = 0; r < OLD; ++r) {
+        const int idx = threadIdx.x + r * SK_CONSUMERS * 32;
+        const int tok = idx >> 4, m = t * SK_ROWS + (idx & 15);
+        const bool live = tok < p.n_tok && m < p.m_out;
+        old[r] = live ? __ldcg((const float*)p.out + (size_t)tok * p.ldo + m) : 0.f;
+        norm_w[r] = (live && p.emit_w) ? p.emit_w[m] : 0.f;      // the weight of the norm behind this product, likewise
+      }
+    }
     for (int ks = 0; ks < kstages; ++ks, ++it) {
       const int s = it % SK_STAGES;
       ok = mbar_wait(full_bar(s), (it / SK_STAGES) & 1, p.error_flag, 32);
@@ -232,7 +246,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     } else {
       // NPAD * 16 is a multiple of the 128 consumer threads: every thread makes the same number of rounds, and
       // the 16 rows of one token sit in 16 neighbouring lanes (the sum of squares below relies on both)
-      for (int idx = threadIdx.x; idx < NPAD * SK_ROWS; idx += SK_CONSUMERS * 32) {
+#pragma unroll
+      for (int r = 0; r < OLD; ++r) {
+        const int idx = threadIdx.x + r * SK_CONSUMERS * 32;
         const int tok = idx >> 4, row = idx & 15;
         const int m = m0 + row;
         const bool live = tok < p.n_tok && m < p.m_out;
@@ -248,12 +264,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           if (p.mode == SK_STORE) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
           else if (p.mode == SK_STORE_F32) ((float*)p.out)[o] = v;
           else {
-            xn = ((float*)p.out)[o] + v;
+            xn = old[r] + v;
             ((float*)p.out)[o] = xn;
           }
         }
         if (p.emit_w) {      // only with SK_ADD_F32
-          if (live) p.emit_h[(size_t)tok * p.emit_ldh + m] = __float2bfloat16_rn(p.emit_w[m] * xn);
+          if (live) p.emit_h[(size_t)tok * p.emit_ldh + m] = __float2bfloat16_rn(norm_w[r] * xn);
           float sq = xn * xn;
 #pragma unroll
           for (int o = 8; o >= 1; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
