@@ -739,9 +739,11 @@ gemm_tc_ksplit_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 }
 
 // Cluster size for a product of `tiles` output tiles and `kblocks` 64-wide k blocks: the largest of 8, 4, 2
-// that leaves every CTA at least four k blocks and does not ask for more CTAs than are resident at once.
-static int ksplit_cluster(long tiles, int kblocks, long resident) {
-  for (int s = 8; s >= 2; s >>= 1)
+// that leaves every CTA at least four k blocks and does not ask for more CTAs than are resident at once.  Tiles
+// of 128 tokens stop at clusters of four: eight CTAs of 130 KB each have few places on the device (measured,
+// 2,048 x 2,048 at 128 tokens: 24.4 us in clusters of eight, 14.1 us in clusters of four; 2,048 x 8,192: 34.2 / 22.1).
+static int ksplit_cluster(long tiles, int kblocks, long resident, int bn) {
+  for (int s = bn >= 128 ? 4 : 8; s >= 2; s >>= 1)
     if (tiles * s <= resident && kblocks / s >= 4) return s;
   return 1;
 }
@@ -849,13 +851,22 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, i
 
 using namespace llmi;
 
-static int tc_bn(int n_tok) { return n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : n_tok <= 128 ? 128 : 256; }
+// Width of the token tile.  Up to 128 tokens: the tokens are one tile.  Beyond that, 128 while that makes no more
+// tiles than the device has SMs — few tiles want their k range cut over a cluster, which the cluster kernel does
+// for tiles up to 128 wide (the o projection of a 256-token prompt, 2,048 x 2,048: 16 tiles of 256 tokens cut 8
+// ways through a workspace took 53 us, of which the CTA that came last spent most adding eight partial tiles
+// alone) — else 256.
+static int tc_bn(int n_tok, int m_out) {
+  if (n_tok <= 128) return n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : 128;
+  const long tiles128 = (long)((m_out + TC_BM - 1) / TC_BM) * ((n_tok + 127) / 128);
+  return tiles128 <= 148 ? 128 : 256;
+}
 static int tc_ctas_per_sm(int bn) { return bn <= 32 ? LLMI_TC_SMALL_CTAS : (bn == 64 ? 2 : 1); }
 
 // How many k-splits a product of this shape gets (a function of the shape only): enough blocks to
 // fill every SM's resident slots once, each with at least four k-blocks to stream.
 LLMI_EXPORT int llmi_gemm_tc_splits(int n_tok, int m_out, int k) {
-  const int bn = tc_bn(n_tok);
+  const int bn = tc_bn(n_tok, m_out);
   const long tiles = (long)((m_out + TC_BM - 1) / TC_BM) * ((n_tok + bn - 1) / bn);
   const int kblocks = (k + TC_BK - 1) / TC_BK;
   const long slots = 148L * tc_ctas_per_sm(bn);
@@ -874,11 +885,11 @@ static int tc_cluster_size(int n_tok, int m_out, int k) {
     const char* e = getenv("LLMI_TC_KSPLIT");
     enabled = (e && e[0] == '0') ? 0 : 1;
   }
-  const int bn = tc_bn(n_tok);
+  const int bn = tc_bn(n_tok, m_out);
   if (!enabled || bn < 32 || bn > 128 || llmi_gemm_tc_splits(n_tok, m_out, k) <= 1) return 1;
   const long tiles = (long)((m_out + TC_BM - 1) / TC_BM) * ((n_tok + bn - 1) / bn);
   const int per_sm = bn == 32 ? ksplit_per_sm<32>() : (bn == 64 ? ksplit_per_sm<64>() : ksplit_per_sm<128>());
-  return ksplit_cluster(tiles, (k + TC_BK - 1) / TC_BK, 148L * per_sm);
+  return ksplit_cluster(tiles, (k + TC_BK - 1) / TC_BK, 148L * per_sm, bn);
 }
 
 // 64-wide k blocks that one CTA accumulates before partial sums are added across CTAs (the whole k range when
@@ -893,7 +904,7 @@ LLMI_EXPORT int llmi_gemm_tc_k_per_cta(int n_tok, int m_out, int k) {
 // Bytes of fp32 workspace and number of int tickets the product needs (both 0 without split-K).
 LLMI_EXPORT long llmi_gemm_tc_workspace(int n_tok, int m_out, int k, int* n_tickets) {
   const int s = llmi_gemm_tc_splits(n_tok, m_out, k);
-  const int bn = tc_bn(n_tok);
+  const int bn = tc_bn(n_tok, m_out);
   const long tiles = (long)((m_out + TC_BM - 1) / TC_BM) * ((n_tok + bn - 1) / bn);
   if (n_tickets) *n_tickets = s > 1 ? (int)tiles : 0;
   return s > 1 ? (long)s * tiles * bn * TC_BM * 4 : 0;
@@ -910,7 +921,7 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
   if (mode < 0 || mode > 3) return LLMI_ERR_UNSUPPORTED;
   if (mode == OUT_SWIGLU && ((m_out & 1) || bias)) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (ldw & 7)) return LLMI_ERR_ALIGN;
-  const int bn = tc_bn(n_tok);
+  const int bn = tc_bn(n_tok, m_out);
   int need_tickets = 0;
   const long need_ws = llmi_gemm_tc_workspace(n_tok, m_out, k, &need_tickets);
   int splits = llmi_gemm_tc_splits(n_tok, m_out, k);
@@ -926,7 +937,9 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
   }
   // (the pair kernel adds into the residual stream by TMA: y must then be 16-byte aligned with a pitch of whole 16 bytes)
   const bool pair_out_ok = mode != OUT_ADD_F32 || (!((uintptr_t)y & 15) && !(ldy & 3));
-  if (pair_ok && n_tok >= 512 && splits == 1 && pair_out_ok) {
+  // pairs of SMs: from 256 tokens on, where the shape has more 128-wide tiles than SMs (bn == 256) or nothing to cut
+  if (pair_ok && n_tok >= 256 && (bn == 256 || (n_tok >= 512 && tc_cluster_size(n_tok, m_out, k) == 1)) && splits == 1 &&
+      pair_out_ok) {
     const int pbn = pair_token_tile(n_tok, m_out);
     rc = make_map(&mx, x, n_tok, k, ldx, pbn / 2);
     if (rc != LLMI_OK) return rc;

@@ -364,7 +364,8 @@ def test_sample_distribution():
 @pytest.mark.parametrize("n_tok,m_out,k", [(1, 200, 72), (5, 64, 64), (16, 128, 64), (17, 384, 120), (70, 129, 1000),
                                            (300, 520, 136), (64, 2048, 8192), (8, 256, 4096), (1000, 136, 264),
                                            (33, 300, 2048), (100, 2048, 2048), (20, 640, 512), (128, 136, 1024),
-                                           (600, 1100, 320), (1500, 700, 1088), (512, 256, 64)])
+                                           (600, 1100, 320), (1500, 700, 1088), (512, 256, 64), (256, 2048, 2048),
+                                           (300, 2048, 1024), (511, 6144, 512), (256, 16384, 256), (384, 1024, 4096)])
 def test_gemm_tc_all_modes(n_tok, m_out, k):
     """The tcgen05 product against fp64 on ragged shapes, with and without split-K."""
     kk = K()
