@@ -77,6 +77,15 @@ def _stream() -> c_void_p:
     return c_void_p(_raw_stream(_device_index))
 
 
+def _stream_int() -> int:
+    """The same as a plain integer, for the functions whose argument types are declared (see ``lib``)."""
+    return _stream().value or 0
+
+
+def _addr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
 def _ptr(t) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
@@ -104,6 +113,13 @@ def lib():
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
         l.llmi_attention_decode_workspace.restype = c_long
+        # The launchers of a prompt's step are called a few hundred times per step from Python: with their argument
+        # types declared, plain integers go in without a ctypes object being made for each (a third of a call's cost).
+        P, L, I, F = c_void_p, c_long, c_int, c_float
+        l.llmi_gemm_tc.argtypes = [P, L, P, L, P, P, L, I, I, I, I, P, L, P, I, P, P]
+        l.llmi_rmsnorm.argtypes = [I, P, P, P, P, I, I, F, P]
+        l.llmi_rope_store.argtypes = [I, P, L, P, I, P, P, P, I, I, P, P, I, I, I, I, I, P]
+        l.llmi_attention_prefill_tc.argtypes = [P, L, L, P, L, P, P, L, P, I, P, P, I, I, I, I, I, F, I, I, I, P, L, P, I, P, P]
         _configured = True
     return l
 
@@ -125,8 +141,8 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
     assert x.dtype == torch.float32 and weight.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
     n, W = out.shape
     assert x.shape[1] == W and weight.numel() == W
-    _check("rmsnorm", lib().llmi_rmsnorm(c_int(_dtype_code(out)), _ptr(x), _ptr(weight), _ptr(out), _ptr(rows),
-                                         c_int(n), c_int(W), c_float(eps), _stream()))
+    _check("rmsnorm", lib().llmi_rmsnorm(_dtype_code(out), x.data_ptr(), weight.data_ptr(), out.data_ptr(), _addr(rows), n, W,
+                                         eps, _stream_int()))
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -208,9 +224,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Ten
         assert bias.dtype == torch.float32 and bias.numel() == N
     sc = tc_scratch(x.device)
     _check("gemm_tc", lib().llmi_gemm_tc(
-        _ptr(x), c_long(x.stride(0)), _ptr(w), c_long(w.stride(0)), _ptr(bias), _ptr(out), c_long(out.stride(0)),
-        c_int(M), c_int(N), c_int(K), c_int(mode), _ptr(sc.workspace), c_long(sc.WORKSPACE_BYTES), _ptr(sc.tickets),
-        c_int(sc.N_TICKETS), _ptr(sc.error), _stream()))
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _addr(bias), out.data_ptr(), out.stride(0), M, N, K, mode,
+        sc.workspace.data_ptr(), sc.WORKSPACE_BYTES, sc.tickets.data_ptr(), sc.N_TICKETS, sc.error.data_ptr(), _stream_int()))
 
 
 class DeferredNorm:
@@ -322,9 +337,9 @@ def rope_store(qkv: torch.Tensor, inv_freq: torch.Tensor | None, rotary_dim: int
     assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
     assert seq_pages.dtype == torch.int32 and seq_pages.dim() == 2
     _check("rope_store", lib().llmi_rope_store(
-        c_int(_dtype_code(qkv)), _ptr(qkv), c_long(qkv.stride(0)), _ptr(inv_freq), c_int(rotary_dim), _ptr(tok_seq),
-        _ptr(tok_pos), _ptr(seq_pages), c_int(seq_pages.stride(0)), c_int(page_size), _ptr(k_cache), _ptr(v_cache),
-        c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(1 if write_kv else 0), _stream()))
+        _dtype_code(qkv), qkv.data_ptr(), qkv.stride(0), _addr(inv_freq), rotary_dim, tok_seq.data_ptr(), tok_pos.data_ptr(),
+        seq_pages.data_ptr(), seq_pages.stride(0), page_size, k_cache.data_ptr(), v_cache.data_ptr(), T, n_heads, n_kv_heads,
+        head_dim, 1 if write_kv else 0, _stream_int()))
 
 
 def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, tok_seq, tok_pos, seq_pages,
@@ -534,11 +549,10 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, s
     if ws is not None:
         assert ws.dtype == torch.float32 and ws.is_cuda
     _check("attention_prefill_tc", lib().llmi_attention_prefill_tc(
-        _ptr(q), c_long(q.stride(0)), c_long(q.shape[0]), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
-        c_long(k_cache.shape[0]), _ptr(seq_pages), c_int(seq_pages.stride(0)), _ptr(seq_q_start), _ptr(seq_kv_len),
-        c_int(S), c_int(n_blocks), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_float(scale), c_int(window),
-        c_int(n_jobs), c_int(split_pages), _ptr(ws), c_long(ws.numel() if ws is not None else 0), _ptr(sc.attn_tickets),
-        c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), _stream()))
+        q.data_ptr(), q.stride(0), q.shape[0], out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+        k_cache.shape[0], seq_pages.data_ptr(), seq_pages.stride(0), seq_q_start.data_ptr(), seq_kv_len.data_ptr(), S,
+        n_blocks, n_heads, n_kv_heads, head_dim, scale, window, n_jobs, split_pages, _addr(ws),
+        ws.numel() if ws is not None else 0, sc.attn_tickets.data_ptr(), sc.N_ATTN_TICKETS, sc.error.data_ptr(), _stream_int()))
 
 
 # Which prompt-attention kernel runs: "tc" (tcgen05: about 43 us for a 2,048-token prompt of 32 heads of 64) or
