@@ -1,6 +1,8 @@
-"""The kernels that only large shapes reach — the product on pairs of SMs (512 tokens and more), the cluster
-k-split (17 to 128 tokens), the tcgen05 prompt attention (head size 64) — inside the model: two layers at
-SmolLM2-1.7B width, the bf16 path against the 32-bit path of the same seeded weights (GPU)."""
+"""The kernels that only large shapes reach — the product on pairs of SMs (256 tokens and more), the cluster
+k-split (17 to about 1,000 tokens), the tcgen05 prompt attention (head sizes 64 and 128), the tensor-core decode
+attention for grouped queries — inside the model: two layers at SmolLM2-1.7B width, and two at the width of an
+8B Llama (4,096 wide, 32 heads of 128 over 8 kv heads, feed-forward 14,336), the bf16 path against the 32-bit
+path of the same seeded weights (GPU)."""
 import numpy as np
 import pytest
 
@@ -11,10 +13,13 @@ CONFIG = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden
           "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 8192, "hidden_act": "silu"}
 
 
-def run(model, prompts, n_decode, seed):
+WIDE = dict(CONFIG, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336,
+            vocab_size=32000, rope_theta=500000.0, tie_word_embeddings=False)
+
+
+def run(model, prompts, n_decode, seed, V=CONFIG["vocab_size"]):
     import llmi_b200 as L
     rng = np.random.default_rng(seed)
-    V = CONFIG["vocab_size"]
     cache = model.new_cache(sum((len(p) + n_decode + 63) // 64 * 64 for p in prompts), n_slots=len(prompts))
     slots = [cache.alloc_slot() for _ in prompts]
     out = [model.step(cache, [L.SequenceStep(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)]).float().cpu().numpy().copy()]
@@ -37,4 +42,18 @@ def test_bf16_path_follows_the_32_bit_path_at_full_width(lens, n_decode):
     for a, b in zip(fast, exact):
         assert np.isfinite(a).all()
         # the bf16 model's weights are the rounded 32-bit ones: about 1.3 % of the largest logit in practice
+        assert float(np.abs(a - b).max() / np.abs(b).max()) < 3e-2
+
+
+def test_bf16_path_follows_the_32_bit_path_at_8b_width():
+    import llmi_b200 as L
+    from llmi_b200.ops import kernels
+    rng = np.random.default_rng(2)
+    V = WIDE["vocab_size"]
+    prompts = [rng.integers(0, V, n).tolist() for n in (1, 70, 129, 300, 700)]
+    fast = run(L.random_model(WIDE, seed=4, dtype="bfloat16", on_device=True), prompts, 3, 6, V)
+    exact = run(L.random_model(WIDE, seed=4, dtype="float32", on_device=True), prompts, 3, 6, V)
+    kernels.check_device_errors("cuda:0")
+    for a, b in zip(fast, exact):
+        assert np.isfinite(a).all()
         assert float(np.abs(a - b).max() / np.abs(b).max()) < 3e-2
