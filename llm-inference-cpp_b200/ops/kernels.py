@@ -288,10 +288,16 @@ _NO_SKINNY = os.environ.get("LLMI_LINEAR", "") == "tc"
 _FUSE_NORM = os.environ.get("LLMI_FUSE_NORM", "1") != "0"
 
 
+SKINNY_SMALL_WEIGHT = 8 << 20     # elements: up to here the weight-streaming kernel also takes 17 to 32 tokens
+
+
 def skinny_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether the product x·wᵀ goes to the weight-streaming kernel."""
-    return bool(not _FORCE_SIMT and not _NO_SKINNY and gemm_tc_eligible(x, w) and x.shape[0] <= SKINNY_MAX_TOKENS
-                and x.shape[1] % 64 == 0)
+    """Whether the product x·wᵀ goes to the weight-streaming kernel: up to 16 tokens, and up to 32 for a small
+    weight matrix, where the tcgen05 kernel's fixed cost (cluster, TMEM, reduction: 6 to 7 us) is most of its time
+    (576 x 576 at 32 tokens: 2.8 against 5.9 us; 2,048 x 2,048: 6.3 against 7.4; 16,384 x 2,048: 23.3 against 17.1)."""
+    n = x.shape[0]
+    return bool(not _FORCE_SIMT and not _NO_SKINNY and gemm_tc_eligible(x, w) and x.shape[1] % 64 == 0
+                and (n <= SKINNY_MAX_TOKENS or (n <= 32 and w.numel() <= SKINNY_SMALL_WEIGHT)))
 
 
 def norm_deferrable(n_tokens: int, width: int, dtype) -> bool:
