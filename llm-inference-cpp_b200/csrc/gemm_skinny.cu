@@ -1,7 +1,8 @@
 // y = x · Wᵀ for a handful of tokens (decode at small batch): a weight-streaming product.
 //
 // Same operation as the reference's matmul (src/model/kernels.cpp:97-113; W is [out, in]) and as gemm_tc.cu,
-// for the case where it is nothing but a read of W from HBM: 1..32 tokens.  The big kernel's 128-row weight
+// for the case where it is nothing but a read of W from HBM: 1..32 tokens (up to 64 for small matrices).
+// The big kernel's 128-row weight
 // tiles leave too few blocks for such products unless k is split across blocks, and the cross-block reduce,
 // the TMEM allocation and the ticket cost more than the product itself (a 8 MB weight matrix is 1.2 us of
 // HBM time).  Here a block owns 16 output rows over the WHOLE k range, so nothing crosses blocks:
@@ -35,7 +36,8 @@ namespace llmi {
 
 constexpr int SK_ROWS = 16;          // output rows per tile
 constexpr int SK_BK = 256;           // k per stage: four 64-wide slices, one per consumer warp
-constexpr int SK_STAGES = 6;
+// stages of the ring: six, three for the widest token tile (64 tokens: 40 KB a stage)
+template <int NT> struct SkStages { static constexpr int value = NT >= 8 ? 3 : 6; };
 constexpr int SK_CONSUMERS = 4;
 constexpr int SK_THREADS = (SK_CONSUMERS + 1) * 32;
 
@@ -82,6 +84,7 @@ __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, SkinnyParams p,
                    int m_tiles) {
   constexpr int NPAD = NT * 8;
+  constexpr int SK_STAGES = SkStages<NT>::value;
   constexpr int W_SLICE = SK_ROWS * 128;          // 16 rows x 64 k of bf16
   constexpr int X_SLICE = NPAD * 128;
   constexpr int W_BYTES = 4 * W_SLICE, X_BYTES = 4 * X_SLICE;
@@ -310,6 +313,7 @@ static int sk_make_map(CUtensorMap* map, const void* ptr, long rows, long k, lon
 template <int NT>
 static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& mx, const SkinnyParams& p, int m_tiles,
                          cudaStream_t stream) {
+  constexpr int SK_STAGES = SkStages<NT>::value;
   constexpr int SMEM = SK_STAGES * (4 * SK_ROWS * 128 + 4 * NT * 8 * 128) + 1024 + 8 * 2 * SK_STAGES + 16;
   static int resident = 0;
   if (!resident) {
@@ -332,9 +336,9 @@ static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& mx, const Ski
 using namespace llmi;
 
 // Most tokens the weight-streaming product takes.
-LLMI_EXPORT int llmi_gemm_skinny_max_tokens() { return 32; }
+LLMI_EXPORT int llmi_gemm_skinny_max_tokens() { return 64; }
 
-// y[n_tok, m_out] (mode) = x[n_tok, k] · w[m_out, k]ᵀ + bias for n_tok <= 32 and k % 64 == 0; bf16 inputs; pitches in elements;
+// y[n_tok, m_out] (mode) = x[n_tok, k] · w[m_out, k]ᵀ + bias for n_tok <= 64 and k % 64 == 0; bf16 inputs; pitches in elements;
 // modes as llmi_gemm_tc (0 store, 1 fp32 store, 2 fp32 add, 3 gated with alternating gate/up rows).
 // emit_w/emit_h/emit_ss (mode 2 only, or all null): also write h = bf16(emit_w * y_new) and the per-tile sums of
 // y_new^2, emit_ss[ceil(m_out/16), 32].  in_ss/in_tiles/in_eps (or null): x is such an h; the accumulators are
@@ -343,14 +347,15 @@ LLMI_EXPORT int llmi_gemm_skinny(const void* x, long ldx, const void* w, long ld
                                  int n_tok, int m_out, int k, int mode, const float* emit_w, void* emit_h, long emit_ldh,
                                  float* emit_ss, const float* in_ss, int in_tiles, float in_eps, int* error_flag,
                                  cudaStream_t stream) {
-  if (n_tok <= 0 || n_tok > 32 || m_out <= 0 || k <= 0) return LLMI_ERR_BAD_SIZE;
+  if (n_tok <= 0 || n_tok > 64 || m_out <= 0 || k <= 0) return LLMI_ERR_BAD_SIZE;
+  if (n_tok > SK_SS_STRIDE && (emit_w || in_ss)) return LLMI_ERR_UNSUPPORTED;   // the sums of squares hold 32 tokens a tile
   if (mode < 0 || mode > 3) return LLMI_ERR_UNSUPPORTED;
   if (mode == SK_SWIGLU && ((m_out & 1) || bias)) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (ldw & 7)) return LLMI_ERR_ALIGN;
   if (k % 64) return LLMI_ERR_UNSUPPORTED;   // the 3-D view of the matrices needs whole 64-wide k slices
   if (emit_w && (mode != SK_ADD_F32 || !emit_h || !emit_ss)) return LLMI_ERR_UNSUPPORTED;
   if (in_ss && in_tiles <= 0) return LLMI_ERR_BAD_SIZE;
-  const int nt = n_tok <= 8 ? 1 : (n_tok <= 16 ? 2 : 4);
+  const int nt = n_tok <= 8 ? 1 : (n_tok <= 16 ? 2 : (n_tok <= 32 ? 4 : 8));
   CUtensorMap mw, mx;
   int rc = sk_make_map(&mw, w, m_out, k, ldw, SK_ROWS);
   if (rc != LLMI_OK) return rc;
@@ -361,5 +366,6 @@ LLMI_EXPORT int llmi_gemm_skinny(const void* x, long ldx, const void* w, long ld
   const int m_tiles = (m_out + SK_ROWS - 1) / SK_ROWS;
   if (nt == 1) return launch_skinny<1>(mw, mx, p, m_tiles, stream);
   if (nt == 2) return launch_skinny<2>(mw, mx, p, m_tiles, stream);
-  return launch_skinny<4>(mw, mx, p, m_tiles, stream);
+  if (nt == 4) return launch_skinny<4>(mw, mx, p, m_tiles, stream);
+  return launch_skinny<8>(mw, mx, p, m_tiles, stream);
 }

@@ -255,7 +255,7 @@ class DeferredNorm:
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
                 mode: int = OUT_STORE, then_norm: DeferredNorm | None = None, scale_from: DeferredNorm | None = None) -> None:
-    """The same product for at most 32 tokens: the weight-streaming kernel (``csrc/gemm_skinny.cu``).
+    """The same product for at most 64 tokens: the weight-streaming kernel (``csrc/gemm_skinny.cu``).
 
     ``then_norm`` (mode OUT_ADD_F32): also fill that deferred norm from the updated ``out``.
     ``scale_from``: ``x`` is that deferred norm's ``h``; apply its scale to the accumulators."""
@@ -289,15 +289,18 @@ _FUSE_NORM = os.environ.get("LLMI_FUSE_NORM", "1") != "0"
 
 
 SKINNY_SMALL_WEIGHT = 8 << 20     # elements: up to here the weight-streaming kernel also takes 17 to 32 tokens
+SKINNY_TINY_WEIGHT = 3 << 20      # and up to here 33 to 64 tokens
 
 
 def skinny_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
-    """Whether the product x·wᵀ goes to the weight-streaming kernel: up to 16 tokens, and up to 32 for a small
-    weight matrix, where the tcgen05 kernel's fixed cost (cluster, TMEM, reduction: 6 to 7 us) is most of its time
+    """Whether the product x·wᵀ goes to the weight-streaming kernel: up to 16 tokens, and more for a small weight
+    matrix, where the tcgen05 kernel's fixed cost (cluster, TMEM, reduction: 6 to 9 us) is most of its time
     (576 x 576 at 32 tokens: 2.8 against 5.9 us; 2,048 x 2,048: 6.3 against 7.4; 16,384 x 2,048: 23.3 against 17.1)."""
     n = x.shape[0]
-    return bool(not _FORCE_SIMT and not _NO_SKINNY and gemm_tc_eligible(x, w) and x.shape[1] % 64 == 0
-                and (n <= SKINNY_MAX_TOKENS or (n <= 32 and w.numel() <= SKINNY_SMALL_WEIGHT)))
+    if _FORCE_SIMT or _NO_SKINNY or x.shape[1] % 64 or not gemm_tc_eligible(x, w):
+        return False
+    return bool(n <= SKINNY_MAX_TOKENS or (n <= 32 and w.numel() <= SKINNY_SMALL_WEIGHT)
+                or (n <= 64 and w.numel() <= SKINNY_TINY_WEIGHT))
 
 
 def norm_deferrable(n_tokens: int, width: int, dtype) -> bool:

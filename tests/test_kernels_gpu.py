@@ -607,9 +607,10 @@ def test_gemm_tc_gated_epilogue(n_tok, inner, k):
 
 
 @pytest.mark.parametrize("n_tok,m_out,k", [(1, 200, 64), (5, 64, 64), (8, 2048, 2048), (8, 130, 8192), (16, 384, 192),
-                                           (17, 6144, 2048), (32, 520, 960), (3, 16, 320)])
+                                           (17, 6144, 2048), (32, 520, 960), (3, 16, 320), (33, 1728, 576), (64, 576, 1536),
+                                           (50, 130, 960), (64, 3072, 576)])
 def test_gemm_skinny_all_modes(n_tok, m_out, k):
-    """The weight-streaming product (at most 32 tokens) against fp64, ragged shapes, every epilogue."""
+    """The weight-streaming product (at most 64 tokens) against fp64, ragged shapes, every epilogue."""
     kk = K()
     torch.manual_seed(n_tok * 7 + m_out + k)
     x = torch.randn(n_tok, k, device="cuda").to(torch.bfloat16)
