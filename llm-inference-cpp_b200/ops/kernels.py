@@ -241,6 +241,7 @@ class DeferredNorm:
 
     def __init__(self, weight: torch.Tensor, eps: float, h: torch.Tensor, ss: torch.Tensor):
         self.weight, self.eps, self.h, self.ss = weight, float(eps), h, ss
+        self.source = None       # the x that the filling product updated: a reader that cannot scale normalises from it
         self.n_tiles = (h.shape[1] + 15) // 16
         assert ss.dtype == torch.float32 and ss.numel() >= self.n_tiles * self.SS_STRIDE and weight.dtype == torch.float32
 
@@ -274,6 +275,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch
         assert scale_from.h.data_ptr() == x.data_ptr() and scale_from.h.shape == (M, K)
     sc = tc_scratch(x.device)
     e, f = then_norm, scale_from
+    if e is not None:
+        e.source = out
     _check("gemm_skinny", lib().llmi_gemm_skinny(
         _ptr(x), c_long(x.stride(0)), _ptr(w), c_long(w.stride(0)), _ptr(bias), _ptr(out), c_long(out.stride(0)),
         c_int(M), c_int(N), c_int(K), c_int(mode),
@@ -306,7 +309,7 @@ def skinny_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
 def norm_deferrable(n_tokens: int, width: int, dtype) -> bool:
     """Whether a norm over ``width`` of ``n_tokens`` rows can be split over the products around it."""
     return bool(_FUSE_NORM and not _FORCE_SIMT and not _NO_SKINNY and dtype == torch.bfloat16
-                and n_tokens <= SKINNY_MAX_TOKENS and width % 64 == 0)
+                and n_tokens <= DeferredNorm.SS_STRIDE and width % 64 == 0)
 
 
 def gemm_bf16(x, w, out, bias=None, mode: int = OUT_STORE, then_norm: DeferredNorm | None = None) -> bool:
@@ -318,7 +321,11 @@ def gemm_bf16(x, w, out, bias=None, mode: int = OUT_STORE, then_norm: DeferredNo
         gemm_skinny(xin, w, out, bias, mode, then_norm, pending)
         return then_norm is not None
     if pending is not None:
-        raise KernelError("a deferred norm can only feed the weight-streaming product")
+        # this reader cannot apply the scale to its accumulators: the norm is run the plain way after all, over the
+        # h that the filling product left (one launch, as without the deferral)
+        if pending.source is None:
+            raise KernelError("a deferred norm that no product has filled")
+        rmsnorm(pending.source, pending.weight, pending.h, pending.eps)
     gemm_tc(xin, w, out, bias, mode)
     return False
 
@@ -330,9 +337,11 @@ def linear(x, w, out, bias=None, mode: int = OUT_STORE, then_norm: DeferredNorm 
     xin = x.h if isinstance(x, DeferredNorm) else x
     if not _FORCE_SIMT and gemm_tc_eligible(xin, w):
         return gemm_bf16(x, w, out, bias, mode, then_norm)
-    if isinstance(x, DeferredNorm):
-        raise KernelError("a deferred norm can only feed the weight-streaming product")
-    linear_simt(x, w, out, bias, mode)
+    if isinstance(x, DeferredNorm):      # a reader that cannot scale: the norm the plain way after all
+        if x.source is None:
+            raise KernelError("a deferred norm that no product has filled")
+        rmsnorm(x.source, x.weight, x.h, x.eps)
+    linear_simt(xin, w, out, bias, mode)
     return False
 
 

@@ -183,7 +183,9 @@ def test_rope_store_long_prompt_same_bits(dtype, nh, nkv, hd):
                            torch.from_numpy(o[t, (nh + nkv) * hd:].reshape(nkv, hd)))
 
 
-@pytest.mark.parametrize("T,H,K1,M2,mode2", [(5, 320, 192, 96, 0), (8, 2048, 128, 512, 3), (13, 192, 448, 64, 1), (1, 64, 64, 48, 2)])
+@pytest.mark.parametrize("T,H,K1,M2,mode2", [(5, 320, 192, 96, 0), (8, 2048, 128, 512, 3), (13, 192, 448, 64, 1), (1, 64, 64, 48, 2),
+                                             (24, 576, 1536, 1728, 0), (32, 960, 128, 256, 3),
+                                             (20, 2048, 128, 6144, 0)])     # the last: a reader too large to scale
 def test_deferred_norm_between_two_products(T, H, K1, M2, mode2):
     """A norm split over the products around it: the first (residual add) also writes weight*x and the tiles'
     sums of squares, the second scales its accumulators.  Against the plain formulas in float64."""
