@@ -41,7 +41,7 @@ template <int NT> struct SkStages { static constexpr int value = NT >= 8 ? 3 : 6
 constexpr int SK_CONSUMERS = 4;
 constexpr int SK_THREADS = (SK_CONSUMERS + 1) * 32;
 
-constexpr int SK_SS_STRIDE = 32;     // floats per tile in the sums of squares (tokens <= 32)
+constexpr int SK_SS_STRIDE = 64;     // floats per tile in the sums of squares (tokens <= 64)
 
 constexpr int SK_STORE = 0, SK_STORE_F32 = 1, SK_ADD_F32 = 2, SK_SWIGLU = 3;
 
@@ -341,14 +341,13 @@ LLMI_EXPORT int llmi_gemm_skinny_max_tokens() { return 64; }
 // y[n_tok, m_out] (mode) = x[n_tok, k] · w[m_out, k]ᵀ + bias for n_tok <= 64 and k % 64 == 0; bf16 inputs; pitches in elements;
 // modes as llmi_gemm_tc (0 store, 1 fp32 store, 2 fp32 add, 3 gated with alternating gate/up rows).
 // emit_w/emit_h/emit_ss (mode 2 only, or all null): also write h = bf16(emit_w * y_new) and the per-tile sums of
-// y_new^2, emit_ss[ceil(m_out/16), 32].  in_ss/in_tiles/in_eps (or null): x is such an h; the accumulators are
+// y_new^2, emit_ss[ceil(m_out/16), 64].  in_ss/in_tiles/in_eps (or null): x is such an h; the accumulators are
 // multiplied by 1/sqrt(sum of the tiles' sums / k + in_eps) before the bias.
 LLMI_EXPORT int llmi_gemm_skinny(const void* x, long ldx, const void* w, long ldw, const float* bias, void* y, long ldy,
                                  int n_tok, int m_out, int k, int mode, const float* emit_w, void* emit_h, long emit_ldh,
                                  float* emit_ss, const float* in_ss, int in_tiles, float in_eps, int* error_flag,
                                  cudaStream_t stream) {
   if (n_tok <= 0 || n_tok > 64 || m_out <= 0 || k <= 0) return LLMI_ERR_BAD_SIZE;
-  if (n_tok > SK_SS_STRIDE && (emit_w || in_ss)) return LLMI_ERR_UNSUPPORTED;   // the sums of squares hold 32 tokens a tile
   if (mode < 0 || mode > 3) return LLMI_ERR_UNSUPPORTED;
   if (mode == SK_SWIGLU && ((m_out & 1) || bias)) return LLMI_ERR_UNSUPPORTED;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (ldx & 7) || (ldw & 7)) return LLMI_ERR_ALIGN;

@@ -233,11 +233,12 @@ class DeferredNorm:
 
     The product that last updates x (a residual add) fills ``h`` = compute-type(weight * x) and ``ss`` — the sum
     of x^2 over each 16-row tile of its output, per token — and the product that reads the norm's output
-    takes ``h`` as its input and multiplies its accumulators by 1/sqrt(sum(ss)/width + eps).  A norm of a
+    takes ``h`` as its input and multiplies its accumulators by 1/sqrt(sum(ss)/width + eps) (a reader that cannot
+    do that runs the norm the plain way over ``source``, the x the filling product updated).  A norm of a
     handful of rows is all launch and latency; this way it costs no kernel.  Made by a norm part
     (``deferred``), filled by ``linear(..., then_norm=)``, consumed by passing it as ``linear``'s input.
     """
-    SS_STRIDE = 32
+    SS_STRIDE = 64
 
     def __init__(self, weight: torch.Tensor, eps: float, h: torch.Tensor, ss: torch.Tensor):
         self.weight, self.eps, self.h, self.ss = weight, float(eps), h, ss

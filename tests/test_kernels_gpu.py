@@ -185,7 +185,8 @@ def test_rope_store_long_prompt_same_bits(dtype, nh, nkv, hd):
 
 @pytest.mark.parametrize("T,H,K1,M2,mode2", [(5, 320, 192, 96, 0), (8, 2048, 128, 512, 3), (13, 192, 448, 64, 1), (1, 64, 64, 48, 2),
                                              (24, 576, 1536, 1728, 0), (32, 960, 128, 256, 3),
-                                             (20, 2048, 128, 6144, 0)])     # the last: a reader too large to scale
+                                             (20, 2048, 128, 6144, 0),      # a reader too large to scale
+                                             (64, 576, 1536, 1728, 0), (40, 576, 576, 3072, 3)])
 def test_deferred_norm_between_two_products(T, H, K1, M2, mode2):
     """A norm split over the products around it: the first (residual add) also writes weight*x and the tiles'
     sums of squares, the second scales its accumulators.  Against the plain formulas in float64."""
@@ -200,7 +201,7 @@ def test_deferred_norm_between_two_products(T, H, K1, M2, mode2):
     eps = 3e-5
     x_ref = x.double() + a.double() @ w1.double().T + b1.double()
     d = kk.DeferredNorm(nw, eps, torch.full((T, H), float("nan"), device="cuda", dtype=torch.bfloat16),
-                        torch.full(((H + 15) // 16, 32), float("nan"), device="cuda"))
+                        torch.full(((H + 15) // 16, kk.DeferredNorm.SS_STRIDE), float("nan"), device="cuda"))
     assert kk.linear(a, w1, x, b1, kk.OUT_ADD_F32, then_norm=d)
     assert rel(x, x_ref) < 1e-6 * 50
     assert rel(d.h, nw.double() * x_ref) < 5e-3
