@@ -79,6 +79,7 @@ class PagePool:
         self._free = list(range(n_pages - 1, -1, -1))
         self._pages: dict[int, list[int]] = {}     # slot -> page ids by position (-1: released)
         self._length: dict[int, int] = {}
+        self._released: dict[int, int] = {}        # slot -> how many leading pages of its table were given back
         # the same tables as one int32 matrix [slot, page], kept in step with the lists, so that a step can
         # gather the page tables of its sequences with one indexing operation
         self.matrix = None
@@ -92,6 +93,7 @@ class PagePool:
             raise CacheError(f"cache: slot {slot} is already open in this group")
         self._pages[slot] = []
         self._length[slot] = 0
+        self._released[slot] = 0
         if self.matrix is not None and slot < self.matrix.shape[0]:
             self.matrix[slot, :] = -1
 
@@ -102,6 +104,7 @@ class PagePool:
             if p >= 0:
                 self._free.append(p)
         del self._length[slot]
+        del self._released[slot]
         if self.matrix is not None and slot < self.matrix.shape[0]:
             self.matrix[slot, :] = -1
 
@@ -110,15 +113,36 @@ class PagePool:
         have = len(self._pages[slot])
         return max(0, pages_for(self._length[slot] + n_new, self.page_size) - have)
 
-    def page_events(self, bases):
+    def releasable(self, slot: int) -> int:
+        """Pages of a slot that lie wholly before the window of its NEXT position: what its next growth gives
+        back before it takes anything (0 without a window)."""
+        if self.window <= 0:
+            return 0
+        first_needed = self._length[slot] - self.window + 1
+        dead = min(len(self._pages[slot]), max(0, first_needed) // self.page_size)
+        return max(0, dead - self._released[slot])
+
+    def release_dead(self, slot: int) -> int:
+        """Give back what :meth:`releasable` counts; returns how many pages that were."""
+        n = self.releasable(slot)
+        if n:
+            self._release_before(slot, self._length[slot] - self.window + 1)
+        return n
+
+    def page_events(self, bases, slots=None):
         """For sequences of lengths ``bases`` (an integer array) that grow by one position: which of them
-        take a new page, and which give one back (a window's oldest page falling out of reach)."""
+        take a new page, and how many pages each gives back first (a window's oldest pages out of reach; with
+        ``slots`` the exact count for these slots — after a long prompt that can be several at once —, without
+        them the one page that falls out when the window's start crosses a page end)."""
+        import numpy as np
         takes = (bases % self.page_size) == 0
-        if self.window > 0:
-            first_needed = bases - self.window + 1
-            gives = (first_needed > 0) & ((first_needed % self.page_size) == 0)
+        if self.window <= 0:
+            gives = np.zeros(len(bases), dtype=np.int64)
+        elif slots is not None:
+            gives = np.fromiter((self.releasable(s) for s in slots), dtype=np.int64, count=len(bases))
         else:
-            gives = takes & False
+            first_needed = bases - self.window + 1
+            gives = ((first_needed > 0) & ((first_needed % self.page_size) == 0)).astype(np.int64)
         return takes, gives
 
     def grow_quietly(self, slot: int) -> None:
@@ -130,11 +154,10 @@ class PagePool:
         if slot not in self._pages:
             raise CacheError(f"cache: slot {slot} is not open in this group")
         base = self._length[slot]
-        if self.window > 0:
-            self._release_before(slot, base - self.window + 1)
         need = self.pages_needed(slot, n_new)
-        if need > len(self._free):
-            raise CacheError("cache is full")
+        if need > len(self._free) + self.releasable(slot):
+            raise CacheError("cache is full")          # nothing has changed
+        self.release_dead(slot)
         for _ in range(need):
             page = self._free.pop()
             if self.matrix is not None and slot < self.matrix.shape[0] and len(self._pages[slot]) < self.matrix.shape[1]:
@@ -149,6 +172,7 @@ class PagePool:
             if table[i] >= 0:
                 self._free.append(table[i])
                 table[i] = -1
+                self._released[slot] = max(self._released[slot], i + 1)
                 if self.matrix is not None and slot < self.matrix.shape[0] and i < self.matrix.shape[1]:
                     self.matrix[slot, i] = -1
 

@@ -15,6 +15,7 @@ Groups with different requests have storage and page pools of their own.
 """
 from __future__ import annotations
 
+import itertools
 from dataclasses import dataclass
 
 import numpy as np
@@ -70,14 +71,21 @@ class StateGroup:
         self.data[:, slot].zero_()
 
 
+_cache_serials = itertools.count(1)
+
+
 class SequenceCache:
-    """Slots, their lengths, and the groups' storage.  Sized by the most tokens held at once."""
+    """Slots, their lengths, and the groups' storage.  Sized by the most tokens held at once.
+
+    ``serial`` numbers the caches of a process: unlike ``id(cache)`` it is never handed out again, so
+    whatever remembers device addresses of a cache (a recorded graph) can tell it from a later one."""
 
     def __init__(self, kv_requests, state_requests, max_tokens: int, max_positions: int, dtype, device,
                  page_size: int = PAGE_SIZE, n_slots: int | None = None):
         """``kv_requests`` / ``state_requests``: lists of (request, number of calls)."""
         if max_tokens < page_size:
             raise CacheError(f"cache: max_tokens must be at least one page ({page_size} tokens)")
+        self.serial = next(_cache_serials)
         self.page_size = page_size
         self.max_positions = max_positions
         n_pages = max_tokens // page_size
@@ -114,7 +122,8 @@ class SequenceCache:
 
     # -- growth ----------------------------------------------------------------------------
     def can_extend(self, wanted: dict) -> None:
-        """Raise unless every slot of ``wanted`` (slot → new tokens) fits, in every group."""
+        """Raise unless every slot of ``wanted`` (slot → new tokens) fits, in every group.  A windowed group
+        counts the pages its slots give back before they take new ones."""
         for slot, n_new in wanted.items():
             if slot not in self._length:
                 raise CacheError(f"cache: slot {slot} is not live")
@@ -122,16 +131,35 @@ class SequenceCache:
                 raise CacheError("sequence longer than the model's context")
         for g in self.kv_groups:
             need = sum(g.pool.pages_needed(s, n) for s, n in wanted.items())
-            if need > g.pool.n_free and g.pool.window == 0:
+            if need > g.pool.n_free + sum(g.pool.releasable(s) for s in wanted):
                 raise CacheError("cache is full")
 
     def extend(self, slot: int, n_new: int) -> int:
         """Reserve room for ``n_new`` positions of a slot; returns its first new position."""
+        self.can_extend({slot: n_new})
         base = self._length[slot]
         for g in self.kv_groups:
             g.pool.extend(slot, n_new)
         self._length[slot] = base + n_new
         return base
+
+    def extend_all(self, wanted: dict) -> list:
+        """Reserve room for a whole step (slot → new tokens) or, if it does not fit, raise with NOTHING changed:
+        the check covers every slot and every group first; then every group first takes back the pages its
+        slots no longer need and only then hands out new ones, so that no slot finds the pool empty because a
+        later slot has not given its pages back yet.  Returns the first new position of each slot."""
+        self.can_extend(wanted)
+        for g in self.kv_groups:
+            if g.pool.window > 0:
+                for s in wanted:
+                    g.pool.release_dead(s)
+            for s, n in wanted.items():
+                g.pool.extend(s, n)
+        bases = []
+        for s, n in wanted.items():
+            bases.append(self._length[s])
+            self._length[s] += n
+        return bases
 
     def extend_each_by_one(self, slots) -> "np.ndarray":
         """One more position for every slot of ``slots`` (distinct, live): the decode step's growth, with the
@@ -146,14 +174,18 @@ class SequenceCache:
             raise CacheError("sequence longer than the model's context")
         events = []
         for g in self.kv_groups:
-            takes, gives = g.pool.page_events(bases)
-            if g.pool.window == 0 and int(takes.sum()) > g.pool.n_free:
+            takes, gives = g.pool.page_events(bases, slots)
+            if int(takes.sum()) > g.pool.n_free + int(gives.sum()):
                 raise CacheError("cache is full")
-            events.append(takes | gives)
-        for g, ev in zip(self.kv_groups, events):
+            events.append((takes, gives))
+        for g, (takes, gives) in zip(self.kv_groups, events):
             pool = g.pool
-            if ev.any():
-                for s, e in zip(slots, ev):
+            if gives.any():
+                for s, n in zip(slots, gives):
+                    if n:
+                        pool.release_dead(s)
+            if takes.any():
+                for s, e in zip(slots, takes):
                     if e:
                         pool.extend(s, 1)
                     else:

@@ -1,10 +1,14 @@
 """A step's batch: validation on the host, and the index arrays the kernels read.
 
-One step runs the next tokens of some sequences — all at their first token, with
-unequal lengths (prompts), or all continuing by one token (decode).  The reference's
-step takes one sequence (src/model/transformer.cpp:192-212); its checks are kept per
-sequence: no tokens, id out of range, cache full, context exceeded — plus a slot named
-twice.  Tokens are flattened in sequence order; each token carries the index of its
+One step runs the next tokens of some sequences: any number of tokens each, at any
+cache length — prompts of unequal lengths that start together, one token each (decode),
+or a prompt that goes on in portions beside sequences that decode, as the reference's
+``forward_cached`` takes T >= 1 new tokens at any length (include/llmi/model/transformer.hpp:89-95;
+used for a chat's next turn, apps/llmi-chat/main.cpp:137-146).  The reference's step takes
+one sequence (src/model/transformer.cpp:192-212); its checks are kept per sequence: no
+tokens, id out of range, cache full, context exceeded — plus a slot named twice.  A step
+whose sequences all bring one token runs the decode kernels; every other step runs the
+prompt kernels, which take a sequence's earlier positions from the cache.  Tokens are flattened in sequence order; each token carries the index of its
 sequence and its absolute position, and every cache group gets the page table of the
 step's sequences.  All of it travels to the device as one int32 block in one copy.
 """
@@ -121,11 +125,7 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
             if not (0 <= int(w) < n):
                 raise StepError(f"step: wanted place {w} is not among the {n} tokens given")
     bases = [cache.length(slot) for slot in slots]          # raises CacheError for a slot that is not live
-    if not decode and any(bases):
-        raise StepError("step: sequences must all start at their first token or all continue by one token")
-    cache.can_extend(dict(zip(slots, lens)))
-    for slot, n in zip(slots, lens):
-        cache.extend(slot, n)
+    cache.extend_all(dict(zip(slots, lens)))       # raises with nothing reserved if the step does not fit
 
     n_seqs = max(n_real, pad_seqs_to) if decode else n_real
     n_pad = n_seqs - n_real

@@ -7,12 +7,15 @@ device block — so the whole step (embedding … head … choice of the next to
 once per shape and replayed: the host writes the index block, copies it, and launches one
 graph.  Batches are padded up to a power of two of sequences and page tables to a power of
 two of pages; padding sequences have index -1 and are skipped by every kernel, so padding
-changes no result.  A graph holds raw addresses: it is dropped when a scratch buffer it
-uses is reallocated (``Runtime.generation``) or when it was recorded for another cache.
+changes no result.  A graph holds raw addresses: it is keyed by the serial number of the
+cache it was recorded for (never by the object's identity, which a later cache can get
+again), it is not used once a scratch buffer it reads is reallocated
+(``Runtime.generation``), and it is dropped when its cache dies.
 """
 from __future__ import annotations
 
 import os
+import weakref
 
 import torch
 
@@ -27,13 +30,32 @@ def bucket(n: int) -> int:
     return b
 
 
+def _drop_graphs_of(graphs_ref, serial: int) -> None:
+    graphs = graphs_ref()
+    if graphs is not None:
+        graphs._drop_cache(serial)
+
+
 class DecodeGraphs:
     def __init__(self, model):
         self.model = model
         self.graphs = {}
         self.replays = 0
         self.kernels_per_graph = {}
-        self._last = None        # (cache, page bucket, context, buffer identity) of the step before
+        self._last = None        # (weak cache, page bucket, context, buffer identity) of the step before
+        self._watched = set()    # serials of the caches whose death drops their graphs
+
+    def _drop_cache(self, serial: int) -> None:
+        for key in [k for k in self.graphs if k[3] == serial]:
+            del self.graphs[key]
+            self.kernels_per_graph.pop(key, None)
+        self._watched.discard(serial)
+        if self._last is not None and self._last[0]() is None:
+            self._last = None        # its context holds the dead cache's groups
+
+    def _key(self, B, P, choice, cache):
+        m = self.model
+        return (B, P, choice, cache.serial, m.rt.generation, m.buffers.dev.data_ptr())
 
     def step(self, cache, seqs, sampler, streams=None):
         """A decode step (one token per sequence) followed by the choice; returns device int32 ids
@@ -47,7 +69,7 @@ class DecodeGraphs:
         if last is not None:
             l_cache, P, l_ctx, l_ident = last
             slots = l_ctx.layout.slots
-            if (l_cache is cache and slots == tuple(s.slot for s in seqs) and cache.slots.all_live(slots)
+            if (l_cache() is cache and slots == tuple(s.slot for s in seqs) and cache.slots.all_live(slots)
                     and l_ident == (m.rt.generation, m.buffers.dev.data_ptr(), m.buffers.serial)
                     and (max(cache.length(s) for s in slots) + cache.page_size) // cache.page_size <= P):
                 # the same sequences one token on, and nobody used the index block in between:
@@ -59,29 +81,40 @@ class DecodeGraphs:
             need_pages = max((cache.length(s.slot) + 1 + cache.page_size - 1) // cache.page_size for s in seqs)
             P = max(need_pages, min(bucket(need_pages), cache.max_pages_per_seq))
             ctx = plan_step(cache, seqs, m.spec.vocab_size, m.buffers, pad_seqs_to=B, pad_pages_to=P)
-        self._last = (cache, P, ctx, (m.rt.generation, m.buffers.dev.data_ptr(), m.buffers.serial))
+        self._last = (weakref.ref(cache), P, ctx, (m.rt.generation, m.buffers.dev.data_ptr(), m.buffers.serial))
         m._last_h2d = ctx.h2d_bytes
         sampler.prepare(B, streams)
         choice = (sampler.params.temperature, sampler.params.top_k, sampler.params.top_p)
-        key = (B, P, choice, id(cache), m.rt.generation, m.buffers.dev.data_ptr())
+        key = self._key(B, P, choice, cache)
         entry = self.graphs.get(key)
         if entry is None:
             # first time for this shape: run it plainly (this also sizes every scratch buffer), then record
-            ids = sampler.launch(m.run(ctx, cache), B)
-            key = (B, P, choice, id(cache), m.rt.generation, m.buffers.dev.data_ptr())
+            logits = m.run(ctx, cache)
+            ids = sampler.launch(logits, B)
+            m.last_logits = logits[:n_real]
+            key = self._key(B, P, choice, cache)     # the plain run may have grown a scratch buffer
             if RECORD and key not in self.graphs:
+                # graphs of shapes recorded before a buffer moved can never be replayed again
+                for stale in [k for k in self.graphs if k[3] == cache.serial and k[4:] != key[4:]]:
+                    del self.graphs[stale]
+                    self.kernels_per_graph.pop(stale, None)
+                if cache.serial not in self._watched:
+                    self._watched.add(cache.serial)
+                    weakref.finalize(cache, _drop_graphs_of, weakref.ref(self), cache.serial)
                 from ..ops import kernels
                 torch.cuda.synchronize()
                 g = torch.cuda.CUDAGraph()
                 before = kernels.launch_count()
                 with torch.cuda.graph(g):
-                    rec_ids = sampler.launch(m.run(ctx, cache), B)
+                    rec_logits = m.run(ctx, cache)
+                    rec_ids = sampler.launch(rec_logits, B)
                 self.kernels_per_graph[key] = kernels.launch_count() - before
                 kernels.launch_count(-(kernels.launch_count() - before))   # recording launches nothing
-                self.graphs[key] = (g, rec_ids)
+                self.graphs[key] = (g, rec_ids, rec_logits)
             return ids[:n_real]
-        g, rec_ids = entry
+        g, rec_ids, rec_logits = entry
         g.replay()
+        m.last_logits = rec_logits[:n_real]
         self.replays += 1
         from ..ops import kernels
         kernels.launch_count(self.kernels_per_graph[key])

@@ -37,7 +37,7 @@ def load_model(model_dir: str, dtype="bfloat16", device="cuda:0") -> Model:
     decls = expected_tensors(spec)
     f = SafetensorsFile(os.path.join(model_dir, "model.safetensors"))
     try:
-        tensors = load_tensors(f, {n: d.shape for n, d in decls.items()}, device, arch.tolerated_extra_tensors)
+        tensors = load_tensors(f, decls, device, arch.tolerated_extra_tensors)
     finally:
         f.close()
     return Model(spec, tensors, parse_dtype(dtype), device, config=cfg)

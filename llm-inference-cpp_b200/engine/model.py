@@ -32,6 +32,7 @@ class Model:
                 raise ValueError(f"schedule call {i} reads the cache of call {call.cache_of}, which does not exist")
         self.buffers = StepBuffers(self.rt.device, self.rt)
         self._graphs = None
+        self.last_logits = None      # fp32 [rows, vocab] of the latest step_and_choose (scratch: valid until the next step)
         self.parameter_count = sum(int(torch.tensor(d.shape).prod()) for d in expected_tensors(spec).values())
 
     # -- sizes -----------------------------------------------------------------------------
@@ -143,13 +144,15 @@ class Model:
         return self.head.forward(h)
 
     def step_and_choose(self, cache, seqs, sampler, streams=None, use_graphs: bool = True):
-        """One step followed by the choice of one token per wanted row; returns the ids on the host."""
+        """One step followed by the choice of one token per wanted row; returns the ids on the host.
+        The logits the choice was made from stay in ``last_logits`` until the next step."""
         if use_graphs and all(len(s.tokens) == 1 for s in seqs) and all(s.want == [0] for s in seqs):
             if self._graphs is None:
                 from .graphs import DecodeGraphs
                 self._graphs = DecodeGraphs(self)
             return self._graphs.step(cache, seqs, sampler, streams).cpu()
         logits = self.step(cache, seqs)
+        self.last_logits = logits
         ids = sampler.choose(logits, streams)
         return ids.cpu()
 

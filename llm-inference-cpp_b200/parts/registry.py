@@ -47,7 +47,9 @@ _PARTS: dict[str, dict[str, type]] = {f: {} for f in FAMILIES}
 @dataclass(frozen=True)
 class TensorDecl:
     shape: tuple
-    role: str = "matrix"     # "matrix" | "norm_scale" | "bias" | "table": how random weights draw it
+    # "matrix" | "norm_scale" | "bias" | "table": floating tensors (the role says how random weights draw them);
+    # "int_table": the only role a file may store as integers
+    role: str = "matrix"
 
 
 def register_part(family: str, kind: str, cls: type, *, replace: bool = False) -> None:

@@ -30,6 +30,8 @@ def _tensor_seed(seed: int, name: str) -> int:
 
 def random_tensor(name: str, shape, role: str, seed: int, device="cpu") -> torch.Tensor:
     """One fp32 tensor of the given role, reproducible from (seed, name) on a given device type."""
+    if role not in ("matrix", "norm_scale", "bias", "table"):
+        raise ValueError(f"random weights: no rule for a tensor of role {role!r} ({name})")
     gen = torch.Generator(device=device)
     gen.manual_seed(_tensor_seed(seed, name))
     noise = torch.randn(tuple(shape), generator=gen, device=device, dtype=torch.float32)

@@ -58,7 +58,7 @@ def model_dirs(tmp_path_factory):
         if key not in made:
             d = tmp_path_factory.mktemp(f"tiny_{name}_{storage}_{seed}")
             write_random_model(str(d), TINY_CONFIGS[name], seed,
-                               torch.float32 if storage == "F32" else torch.bfloat16)
+                               {"F32": torch.float32, "F16": torch.float16, "BF16": torch.bfloat16}[storage])
             made[key] = str(d)
         return made[key]
     return get

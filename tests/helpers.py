@@ -63,6 +63,43 @@ def trace_batches(requests, batch_size, prompt_lens):
     return steps, most
 
 
+def trace_portions(requests, portion, n_last=4):
+    """Each request alone: its tokens but the last ``n_last`` in portions of ``portion`` tokens (the last portion is
+    what is left), then one token a step — a prompt fed in parts, as a chat's next turn continues a sequence."""
+    steps, k = [], 0
+    for rid, toks in requests.items():
+        cut = max(1, len(toks) - n_last)
+        for a in range(0, cut, portion):
+            b = min(a + portion, cut)
+            steps.append({"step": k, "entries": [{"id": rid, "tokens": toks[a:b], "want": list(range(b - a))}],
+                          "end": [rid] if b == len(toks) else []})
+            k += 1
+        for t in range(cut, len(toks)):
+            steps.append({"step": k, "entries": [{"id": rid, "tokens": [toks[t]], "want": [0]}],
+                          "end": [rid] if t == len(toks) - 1 else []})
+            k += 1
+    return steps, max(round_up(len(t)) for t in requests.values())
+
+
+def trace_mixed(requests, first, portion):
+    """All requests in one batch: request r starts with ``first[r]`` tokens and then goes on by ``portion[r]`` tokens a
+    step (1: it decodes) until it ends — steps in which some sequences continue a prompt and others decode."""
+    ids = list(requests)
+    fed = {r: 0 for r in ids}
+    steps, k, live = [], 0, list(ids)
+    while live:
+        entries = []
+        for r in live:
+            n = min(first[r] if fed[r] == 0 else portion[r], len(requests[r]) - fed[r])
+            entries.append({"id": r, "tokens": requests[r][fed[r]:fed[r] + n], "want": list(range(n))})
+            fed[r] += n
+        ending = [r for r in live if fed[r] == len(requests[r])]
+        steps.append({"step": k, "entries": entries, "end": ending})
+        k += 1
+        live = [r for r in live if r not in ending]
+    return steps, sum(round_up(len(t)) for t in requests.values())
+
+
 def collect(steps, outputs, vocab):
     """{id: [T, vocab]} from the per-step outputs of a replay (None where nothing was wanted)."""
     rows = {}

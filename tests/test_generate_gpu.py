@@ -190,3 +190,79 @@ def test_recorded_decode_steps_survive_other_steps_in_between(model_dirs, dtype)
     for n in list(hist):
         cache.free_slot(hist.pop(n)[0])
     cache.check()
+
+
+WIDTH_576 = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 576, "num_attention_heads": 9,
+             "num_key_value_heads": 3, "head_dim": 64, "intermediate_size": 1536, "vocab_size": 49152, "rope_theta": 100000.0,
+             "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 8192, "hidden_act": "silu"}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "width576"])
+def test_logits_of_recorded_padded_decode_steps(model_dirs, tmp_path, name, dtype):
+    """The path that generation and the benchmark run — ``step_and_choose`` with recorded graphs: batches padded to a
+    power of two with sequences of index -1, padded page tables, the index block patched from one step to the next —
+    compared on LOGITS with the plain implementation after every step (with tied random weights greedy decoding falls
+    into a fixed point, so equal tokens would say little).  The tokens fed are given, not the chosen ones, so that
+    one whole-sequence pass of the plain implementation gives every step's reference.  Batch sizes that are no power
+    of two (5, 3), sequences that leave one by one, pages' ends crossed while decoding."""
+    import torch
+    import helpers as H
+    import llmi_b200 as L
+    from llmi_b200.sampling import Sampler
+    if name == "width576":
+        d = str(tmp_path)
+        L.write_random_model(d, WIDTH_576, 8, torch.float32 if dtype == "float32" else torch.bfloat16)
+        prompt_lens, totals = [60, 3, 64, 127, 20], [75, 12, 70, 133, 26]
+    else:
+        d = model_dirs(name, STORAGE[dtype])
+        ctx_len = TINY_CONFIGS[name]["max_position_embeddings"]
+        prompt_lens, totals = [60, 3, 64, 120, 20], [75, 12, 70, min(128, ctx_len), 26]
+    cfg, w = P.read_model(d)
+    model = L.load(d, dtype)
+    V = cfg["vocab_size"]
+    rng = np.random.default_rng(17)
+    toks = [rng.integers(0, V, n).tolist() for n in totals]
+    refs = [P.forward(cfg, w, t) for t in toks]
+    sampler = Sampler(L.SamplingParams(), model.rt)
+    for round_ in range(2):                    # twice: the second cache replays nothing of the first one's graphs
+        cache = model.new_cache(sum(H.round_up(n) for n in totals) + 64 * round_, n_slots=8)
+        slots = [cache.alloc_slot() for _ in toks]
+        fed = list(prompt_lens)
+        model.step(cache, [L.SequenceStep(s, t[:n], []) for s, t, n in zip(slots, toks, fed)])
+        live = list(range(len(toks)))
+        n_steps = 0
+        while live:
+            ids = model.step_and_choose(cache, [L.SequenceStep(slots[i], [toks[i][fed[i]]], [0]) for i in live], sampler)
+            logits = model.last_logits.cpu().numpy()
+            assert logits.shape == (len(live), V)
+            assert ids.tolist() == logits.argmax(1).tolist()
+            for row, i in enumerate(live):
+                assert np.isfinite(logits[row]).all()
+                assert H.rel_to_max(logits[row], refs[i][fed[i]]) < H.TOL[dtype], (name, round_, i, fed[i])
+                fed[i] += 1
+            for i in [i for i in live if fed[i] == totals[i]]:
+                cache.free_slot(slots[i])
+                live.remove(i)
+            n_steps += 1
+        cache.check()
+        assert model._graphs is not None and model._graphs.replays > 0
+    assert n_steps == max(t - p for t, p in zip(totals, prompt_lens))
+
+
+def test_one_model_many_caches_of_different_sizes(model_dirs):
+    """A model is reused across ``generate`` calls that each make a cache of their own, of different sizes but the same
+    batch and page bucket: a recorded step must never be replayed against another cache's memory."""
+    import gc
+    import llmi_b200 as L
+    d = model_dirs("C", "F32")
+    cfg, w = P.read_model(d)
+    model = L.load(d, "float32")
+    prompts = prompts_for("C", [30, 5, 17])
+    ref = [P.generate_greedy(cfg, w, p, 40) for p in prompts]
+    for max_new in (9, 40, 23, 33, 12):
+        got = L.generate(model, prompts, max_new=max_new, ignore_eos=True)
+        assert got == [r[:max_new] for r in ref], max_new
+        gc.collect()
+        serials = {k[3] for k in model._graphs.graphs}
+        assert len(serials) <= 1, "graphs of dead caches must be dropped"

@@ -14,6 +14,7 @@ from conftest import ROOT, TINY_CONFIGS
 pytestmark = pytest.mark.gpu
 
 STORAGE = {"float32": "F32", "bfloat16": "BF16"}
+CONFIG_NAMES = ["A", "B", "C"]
 LENGTHS = {"A": [5, 9, 17, 40, 100, 128], "B": [1, 12, 30, 64, 65, 200], "C": [3, 33, 64, 129, 300, 700]}
 
 
@@ -55,6 +56,27 @@ def test_whole_requests(loaded, name, dtype):
     check(H.collect(steps, H.replay(model, steps, most), model.vocab_size), refs, dtype)
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_f16_weights_are_used_exactly_in_the_32_bit_path(model_dirs, name):
+    """A folder stored as F16 and run in fp32 computes with the file's values (src/model/safetensors.cpp:290-299 widens
+    each element exactly): all three ways of cutting match the plain implementation, which reads F16 exactly, at the
+    32-bit tolerance.  (Rounding the weights to bf16 on the way would miss it by two orders of magnitude.)"""
+    import llmi_b200 as L
+    d = model_dirs(name, "F16")
+    cfg, w = P.read_model(d)
+    model = L.load(d, "float32")
+    reqs = make_requests(name)
+    refs = {r: P.forward(cfg, w, t) for r, t in reqs.items()}
+    rng = np.random.default_rng(3)
+    prompt_lens = {r: int(rng.integers(1, len(t) + 1)) for r, t in reqs.items()}
+    for steps, most in (H.trace_whole(reqs), H.trace_last_decoded(reqs, 32), H.trace_batches(reqs, 3, prompt_lens)):
+        check(H.collect(steps, H.replay(model, steps, most), model.vocab_size), refs, "float32")
+    # and in bf16 the one rounding is that of the compute type
+    fast = L.load(d, "bfloat16")
+    steps, most = H.trace_whole(reqs)
+    check(H.collect(steps, H.replay(fast, steps, most), fast.vocab_size), refs, "bfloat16")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_last_32_tokens_one_by_one(loaded, name, dtype):
@@ -87,14 +109,57 @@ def test_long_decoding_and_first_tokens(loaded, dtype):
     assert H.rel_to_max(got["r5"][:3], refs["r5"][:3]) < H.TOL[dtype]
 
 
-def test_cutting_does_not_change_fp32_logits_beyond_rounding(loaded):
-    model, reqs, refs, _ = loaded("C", "float32")
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("portion", [7, 64, 100])
+@pytest.mark.parametrize("name", CONFIG_NAMES)
+def test_prompt_in_portions(loaded, name, portion, dtype):
+    """A prompt fed in portions, then decoded: every portion but the first continues a sequence by more than one
+    token (include/llmi/model/transformer.hpp:89-95), across page ends (64) and inside pages (7, 100)."""
+    model, reqs, refs, _ = loaded(name, dtype)
+    steps, most = H.trace_portions(reqs, portion)
+    check(H.collect(steps, H.replay(model, steps, most), model.vocab_size), refs, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", CONFIG_NAMES)
+def test_portions_beside_decoding_sequences(loaded, name, dtype):
+    """One batch whose steps mix sequences that continue their prompt by several tokens with sequences that decode."""
+    model, reqs, refs, _ = loaded(name, dtype)
+    ids = list(reqs)
+    first = {r: max(1, len(reqs[r]) // 3) for r in ids}
+    portion = {r: (1, 2, 63, 1, 65, 5)[i % 6] for i, r in enumerate(ids)}
+    steps, most = H.trace_mixed(reqs, first, portion)
+    assert any(len({len(e["tokens"]) for e in s["entries"]}) > 1 and s["step"] > 0 for s in steps)
+    check(H.collect(steps, H.replay(model, steps, most), model.vocab_size), refs, dtype)
+
+
+@pytest.mark.parametrize("name", CONFIG_NAMES)
+def test_cutting_does_not_change_fp32_logits_at_all(loaded, name):
+    """In the 32-bit path every reduction runs in an order that depends on absolute positions only, so the logits of a
+    position are the same BITS whole, token by token, in portions and in unequal batches — the reference's own claim
+    for its cache (include/llmi/model/transformer.hpp:25-28; tests/transformer_test.cpp:322-411)."""
+    model, reqs, refs, _ = loaded(name, "float32")
+    V = model.vocab_size
     s1, m1 = H.trace_whole(reqs)
-    s2, m2 = H.trace_last_decoded(reqs, 32)
-    a = H.collect(s1, H.replay(model, s1, m1), model.vocab_size)
-    b = H.collect(s2, H.replay(model, s2, m2), model.vocab_size)
-    for r in reqs:
-        assert H.rel_to_max(a[r], b[r].astype(np.float64)) < 2e-6
+    whole = H.collect(s1, H.replay(model, s1, m1), V)
+    rng = np.random.default_rng(3)
+    prompt_lens = {r: int(rng.integers(1, len(t) + 1)) for r, t in reqs.items()}
+    ids = list(reqs)
+    cuts = {
+        "last 32 one by one": H.trace_last_decoded(reqs, 32),
+        "unequal batches": H.trace_batches(reqs, 3, prompt_lens),
+        "portions of 1": H.trace_portions(reqs, 1),
+        "portions of 2": H.trace_portions(reqs, 2),
+        "portions of 63": H.trace_portions(reqs, 63),
+        "portions of 64": H.trace_portions(reqs, 64),
+        "portions of 65": H.trace_portions(reqs, 65),
+        "mixed": H.trace_mixed(reqs, {r: max(1, len(reqs[r]) // 2) for r in ids},
+                               {r: (1, 3, 64)[i % 3] for i, r in enumerate(ids)}),
+    }
+    for how, (steps, most) in cuts.items():
+        got = H.collect(steps, H.replay(model, steps, most), V)
+        for r in reqs:
+            assert np.array_equal(got[r], whole[r]), (how, r)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -140,8 +205,10 @@ def test_step_errors(loaded):
         model.step(cache, [L.SequenceStep(s2, [1] * 65, [0])])
     assert cache.length(s2) == 0                       # a refused step reserves nothing
     model.step(cache, [L.SequenceStep(s2, [1] * 64, [0])])
-    with pytest.raises(L.StepError, match="all start|continue"):
-        model.step(cache, [L.SequenceStep(s, [1, 2], [0])])
+    cache.free_slot(s2)
+    model.step(cache, [L.SequenceStep(s, [1, 2], [0])])        # a sequence may go on by more than one token
+    assert cache.length(s) == 66
+    s2 = cache.alloc_slot()
     other = model.new_cache(64)
     with pytest.raises(ValueError, match="not created"):
         L.load(loaded("A", "float32")[3], "float32").step(other, [L.SequenceStep(0, [1], [0])])

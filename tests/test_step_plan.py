@@ -53,6 +53,26 @@ def test_block_of_a_prompt_step():
     assert pages.shape == (2, 1) and pages[0, 0] != pages[1, 0]
 
 
+def test_block_of_a_step_that_continues_by_several_tokens():
+    """Sequences already hold tokens; one goes on by three, one by one, one starts: positions go on from each
+    sequence's length, lengths are length + new tokens, and the page tables cover the earlier positions too."""
+    cache = make_cache()
+    a, b, c = cache.alloc_slot(), cache.alloc_slot(), cache.alloc_slot()
+    buf = HostBuffers()
+    plan_step(cache, [SequenceStep(a, [1] * 62, []), SequenceStep(b, [2] * 10, [])], 50, buf)
+    ctx = plan_step(cache, [SequenceStep(a, [5, 6, 7], [2]), SequenceStep(b, [9], [0]), SequenceStep(c, [1, 2], [0, 1])], 50, buf)
+    assert not ctx.decode
+    assert ctx.tok_pos.tolist() == [62, 63, 64, 10, 0, 1]
+    assert ctx.tok_seq.tolist() == [0, 0, 0, 1, 2, 2]
+    assert ctx.seq_kv_len.tolist() == [65, 11, 2]
+    assert ctx.seq_q_start.tolist() == [0, 3, 4, 6]
+    assert ctx.want_rows.tolist() == [2, 3, 4, 5]
+    assert ctx.host_q_lens == [3, 1, 2] and ctx.host_kv_lens == [65, 11, 2]
+    pages = ctx.pages_of(cache.kv_groups[0])
+    assert pages.shape == (3, 2) and pages[0, 1] >= 0 and pages[1, 1] == -1
+    assert cache.length(a) == 65 and cache.length(b) == 11 and cache.length(c) == 2
+
+
 @pytest.mark.parametrize("window", [0, 100])
 def test_continued_decode_step_equals_planning_anew(window):
     """Two caches in lockstep: one is stepped by plan_step every time, the other by continue_decode_step.
@@ -113,3 +133,53 @@ def test_continued_decode_step_refusals_change_nothing():
     cache.free_slot(b)
     with pytest.raises(CacheError, match="not live"):
         continue_decode_step(cache, ctx, [1, 2], 50, buf)
+
+
+def test_a_step_that_does_not_fit_a_windowed_group_reserves_nothing():
+    """A global group with room and a windowed group without: the step is refused before anything is reserved, in
+    every group and for every slot, for a prompt step and for a continued decode step."""
+    reqs = [(KVRequest(2, 16, 0), 1), (KVRequest(1, 16, 64), 1)]
+    cache = SequenceCache(reqs, [], max_tokens=64 * 4, max_positions=1000, dtype=torch.float32, device="meta",
+                          page_size=64, n_slots=4)
+    glob, win = cache.kv_groups[0].pool, cache.kv_groups[1].pool
+    a, b = cache.alloc_slot(), cache.alloc_slot()
+    buf = HostBuffers()
+    plan_step(cache, [SequenceStep(a, [1] * 64, []), SequenceStep(b, [1] * 64, [])], 50, buf)     # 2 of 4 pages each group
+    c = cache.alloc_slot()
+    before = (glob.n_free, win.n_free, cache.length(a), cache.length(b), cache.length(c))
+    with pytest.raises(CacheError, match="full"):        # a and b take one page each, c would need two more
+        plan_step(cache, [SequenceStep(a, [1], []), SequenceStep(b, [1], []), SequenceStep(c, [1] * 65, [])], 50, buf)
+    assert (glob.n_free, win.n_free, cache.length(a), cache.length(b), cache.length(c)) == before
+    assert glob.length(a) == 64 and win.length(a) == 64
+    cache.check()
+    # the windowed group alone is out of pages: fill it with a third sequence whose window holds two pages
+    plan_step(cache, [SequenceStep(c, [1] * 128, [])], 50, buf)
+    assert win.n_free == 0 and glob.n_free == 0
+    ctx = None
+    with pytest.raises(CacheError, match="full"):
+        plan_step(cache, [SequenceStep(a, [1], [])], 50, buf)
+    assert cache.length(a) == 64 and glob.length(a) == 64 and win.length(a) == 64
+    cache.check()
+
+
+def test_a_window_gives_back_a_long_prompts_dead_pages_at_the_next_step():
+    """After a prompt of five pages a window of 64 positions needs two of them: the first decode step gives back
+    the other three at once, not one at every later page end, and both ways of growing agree."""
+    for grow in ("plan", "continue"):
+        reqs = [(KVRequest(1, 16, 64), 1)]
+        cache = SequenceCache(reqs, [], max_tokens=64 * 6, max_positions=1000, dtype=torch.float32, device="meta",
+                              page_size=64, n_slots=2)
+        pool = cache.kv_groups[0].pool
+        a = cache.alloc_slot()
+        buf = HostBuffers()
+        plan_step(cache, [SequenceStep(a, [1] * 300, [])], 50, buf)
+        assert pool.n_free == 1
+        ctx = plan_step(cache, [SequenceStep(a, [2], [0])], 50, buf, pad_seqs_to=1, pad_pages_to=8)
+        # position 300 sees 237..300: pages 0, 1, 2 are dead (page 3 starts at 192)
+        assert pool.n_free == 4 and pool.table(a)[:3] == [-1, -1, -1] and pool.table(a)[3] >= 0
+        if grow == "continue":
+            continue_decode_step(cache, ctx, [3], 50, buf)
+        else:
+            plan_step(cache, [SequenceStep(a, [3], [0])], 50, buf)
+        assert pool.n_free == 4 and cache.length(a) == 302
+        cache.check()

@@ -107,10 +107,48 @@ def test_one_error_lists_everything_wrong(tmp_path):
 
 def test_storage_rules():
     assert storage_form(torch.zeros(2, dtype=torch.bfloat16)).dtype == torch.bfloat16
-    assert storage_form(torch.zeros(2, dtype=torch.float16)).dtype == torch.bfloat16
+    # F16 stays F16 until a part converts it: widening to fp32 is exact (src/model/safetensors.cpp:290-299), so the
+    # 32-bit path computes with the file's values, and the bf16 path rounds them once
+    assert storage_form(torch.zeros(2, dtype=torch.float16)).dtype == torch.float16
     assert storage_form(torch.zeros(2, dtype=torch.float32)).dtype == torch.float32      # 32-bit stays 32-bit
     assert storage_form(torch.zeros(2, dtype=torch.int64)).dtype == torch.int32          # integer tables
     assert storage_form(torch.zeros(2, dtype=torch.int32)).dtype == torch.int32
+
+
+def test_integer_storage_is_refused_for_what_a_model_multiplies_with(tmp_path):
+    """src/model/model.cpp:185-187: a weight is F32, F16 or BF16; tests/model_test.cpp:111-151."""
+    arch, c = parse_config(TINY_A)
+    decls = expected_tensors(arch.model_spec(c))
+    found = {n: ("F32", d.shape) for n, d in decls.items()}
+    check_tensors(decls, found)
+    for storage in ("I32", "I64"):
+        for name in ("model.layers.0.self_attn.q_proj.weight", "model.norm.weight", "model.embed_tokens.weight"):
+            bad = dict(found)
+            bad[name] = (storage, decls[name].shape)
+            with pytest.raises(WeightBindingError, match=f"{name} has dtype {storage}, expected F32, F16 or BF16"):
+                check_tensors(decls, bad)
+    # the one role a file may store as integers
+    from llmi_b200.parts.registry import TensorDecl
+    table = {"ids": TensorDecl((4,), "int_table")}
+    check_tensors(table, {"ids": ("I64", (4,))})
+    with pytest.raises(WeightBindingError, match="ids has dtype F32, expected I32 or I64"):
+        check_tensors(table, {"ids": ("F32", (4,))})
+
+
+def test_f16_folder_is_read_exactly(tmp_path):
+    """An F16 file's values reach the loader's output unrounded (the plain reader widens them the same way)."""
+    d = write_random_model(str(tmp_path / "h"), TINY_A, 5, torch.float16)
+    f = SafetensorsFile(d + "/model.safetensors")
+    arch, c = parse_config(TINY_A)
+    decls = expected_tensors(arch.model_spec(c))
+    name = "model.layers.1.mlp.up_proj.weight"
+    assert f.tensors[name].dtype == "F16"
+    got = load_tensors(f, decls, "cpu")
+    _, pw = P.read_model(d)
+    for n in decls:
+        assert got[n].dtype == torch.float16
+        assert np.array_equal(got[n].double().numpy(), pw[n])
+    assert not torch.equal(got[name].to(torch.bfloat16).float(), got[name].float())     # bf16 would have lost bits
 
 
 def raw_file(path, header: dict, data: bytes, pad=True):
