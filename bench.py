@@ -201,10 +201,14 @@ def main():
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a CMake C++ project without setup.py or pyproject.toml: "
-                          "the offline pip install ends with 'Neither setup.py nor pyproject.toml found'"}))
-        return 0
+        if args.gpus != 1:
+            print(json.dumps({"impl": "reference", "unavailable": "the reference runs on the CPU of one machine; --gpus must be 1"}))
+            return 0
+        # the unmodified reference through its own command line (a CMake C++ project: the offline pip install has
+        # nothing to install — 'Neither setup.py nor pyproject.toml found' — so it is built with its own CMake files)
+        from baseline import reference_arm
+        return reference_arm.main(dict(CONFIG, num_hidden_layers=args.layers), args.batch, args.context, PREFILL_TOKENS,
+                                  args.steps, args.warmup, FULL_LAYERS)
     if args.gpus != 1:
         print("bench.py: this library runs on one GPU; --gpus must be 1")
         return 2

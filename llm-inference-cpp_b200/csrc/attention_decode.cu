@@ -546,16 +546,15 @@ attention_decode_kernel(DecodeParams p, int n_items) {
 template <int HD, int G>
 int decode_resident() {
   using C = DecCfg<HD>;
-  static int resident = 0;
+  static PerDevice<int> resident_on;
+  int& resident = resident_on.here();
   if (!resident) {
     cudaFuncSetAttribute(attention_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-    int per_sm = 0, sms = 0, dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int per_sm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<HD, G>, DEC_THREADS,
                                                       C::SMEM_BYTES) != cudaSuccess || per_sm < 1)
       per_sm = 1;
-    resident = per_sm * (sms > 0 ? sms : 148);
+    resident = per_sm * sm_count();
   }
   return resident;
 }
@@ -563,7 +562,8 @@ int decode_resident() {
 template <int HD, int G>
 int launch_decode(const DecodeParams& p, int n_seqs, cudaStream_t stream) {
   using C = DecCfg<HD>;
-  static bool configured = false;
+  static PerDevice<bool> configured_on;
+  bool& configured = configured_on.here();
   if (!configured) {
     if (cudaFuncSetAttribute(attention_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::SMEM_BYTES) != cudaSuccess)

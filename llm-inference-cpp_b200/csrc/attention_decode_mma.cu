@@ -555,8 +555,11 @@ static int dm_cache_map(CUtensorMap* map, const void* ptr, long rows, int head_d
 template <int HD>
 static int dm_resident(int group) {
   using C = DmCfg<HD>;
-  static int resident[17] = {};
-  static bool configured = false;
+  struct PerGroup { int n[17] = {}; };
+  static PerDevice<PerGroup> resident_on;
+  int* resident = resident_on.here().n;
+  static PerDevice<bool> configured_on;
+  bool& configured = configured_on.here();
   if (!configured) {
     if (cudaFuncSetAttribute(attention_decode_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::smem_bytes(16)) != cudaSuccess)
@@ -564,13 +567,11 @@ static int dm_resident(int group) {
     configured = true;
   }
   if (!resident[group]) {
-    int per_sm = 0, sms = 0, dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int per_sm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_mma_kernel<HD>, DM_THREADS,
                                                       C::smem_bytes(group)) != cudaSuccess || per_sm < 1)
       per_sm = 1;
-    resident[group] = per_sm * (sms > 0 ? sms : 148);
+    resident[group] = per_sm * sm_count();
   }
   return resident[group];
 }

@@ -307,7 +307,8 @@ template <int HD>
 static int launch_prefill(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p, int n_blocks,
                           cudaStream_t stream) {
   constexpr int SMEM = PF_STAGES * 2 * (HD / 64) * PF_PAGE * 64 * 2 + 1024 + 64;
-  static bool configured = false;
+  static PerDevice<bool> configured_on;
+  bool& configured = configured_on.here();
   if (!configured) {
     if (cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
       return LLMI_ERR_LAUNCH;

@@ -558,7 +558,8 @@ template <int HD>
 static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const PrefillTcParams& p, dim3 grid,
                      cudaStream_t stream) {
   using C = FtCfg<HD>;
-  static bool configured = false;
+  static PerDevice<bool> configured_on;
+  bool& configured = configured_on.here();
   if (!configured) {
     if (cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
       return LLMI_ERR_LAUNCH;

@@ -74,6 +74,32 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // size selects.
 __device__ __forceinline__ float rot_lo(float a, float b, float c, float s) { return __fmaf_rn(a, c, -__fmul_rn(b, s)); }
 __device__ __forceinline__ float rot_hi(float a, float b, float c, float s) { return __fmaf_rn(b, c, __fmul_rn(a, s)); }
+// Facts and one-time set-up per device.  A process may drive several GPUs, and a function attribute (the
+// dynamic shared memory a kernel may ask for) or a count derived from the device (how many blocks are
+// resident at once) belongs to the device that was current when it was set or read.
+constexpr int MAX_DEVICES = 64;
+inline int current_device() {
+  int d = 0;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= MAX_DEVICES) d = 0;
+  return d;
+}
+// Streaming multiprocessors of the current device (a B200 has 148; a part with fewer enabled has fewer).
+inline int sm_count() {
+  static int n[MAX_DEVICES] = {};
+  const int d = current_device();
+  if (n[d] == 0) {
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, d);
+    n[d] = v > 0 ? v : 1;
+  }
+  return n[d];
+}
+// `static PerDevice<bool> configured; if (!configured.here()) { ...; configured.here() = true; }`
+template <typename V> struct PerDevice {
+  V v[MAX_DEVICES] = {};
+  V& here() { return v[current_device()]; }
+};
+
 inline int launch_status() { return cudaPeekAtLastError() == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH; }
 
 // Programmatic dependent launch.  A kernel launched with launch_pdl may start while the kernel before

@@ -315,17 +315,16 @@ static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& mx, const Ski
                          cudaStream_t stream) {
   constexpr int SK_STAGES = SkStages<NT>::value;
   constexpr int SMEM = SK_STAGES * (4 * SK_ROWS * 128 + 4 * NT * 8 * 128) + 1024 + 8 * 2 * SK_STAGES + 16;
-  static int resident = 0;
+  static PerDevice<int> resident_on;
+  int& resident = resident_on.here();
   if (!resident) {
     if (cudaFuncSetAttribute(gemm_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
       return LLMI_ERR_LAUNCH;
-    int per_sm = 0, sms = 0, dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int per_sm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_skinny_kernel<NT>, SK_THREADS, SMEM) != cudaSuccess ||
         per_sm < 1)
       per_sm = 1;
-    resident = per_sm * (sms > 0 ? sms : 148);
+    resident = per_sm * sm_count();
   }
   const int grid = m_tiles < resident ? m_tiles : resident;
   return launch_pdl(PDL_GEMM, gemm_skinny_kernel<NT>, grid, SK_THREADS, SMEM, stream, mw, mx, p, m_tiles);

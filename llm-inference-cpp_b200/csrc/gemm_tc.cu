@@ -490,7 +490,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   }
 }
 
-// Width of the token tile for a product on pairs of SMs.  The 74 pairs take the (256 rows x bn tokens) tiles in
+// Width of the token tile for a product on pairs of SMs.  The device's pairs (74 on a B200) take the (256 rows x bn tokens) tiles in
 // rounds, and a last round that is nearly empty costs as much as a full one: 2,048 tokens x 6,144 rows are 192
 // tiles of 256 tokens (2.6 rounds, paid as 3), but 216 tiles of 240 tokens (2.9 rounds of 240/256 the length).
 // A narrower tile also needs more bytes from L2 per flop (128 weight rows + bn/2 token rows a stage and SM), which
@@ -503,11 +503,12 @@ static int pair_token_tile(int n_tok, int m_out) {
   }
   if (fixed >= 128 && fixed <= 256 && fixed % 16 == 0) return fixed;
   const long m_tiles = (m_out + 255) / 256;
+  const long n_pairs = sm_count() / 2 > 0 ? sm_count() / 2 : 1;
   int best = TP_BN;
   double best_cost = 0;
   for (int bn = TP_BN; bn >= 128; bn -= 16) {
     const long units = m_tiles * ((n_tok + bn - 1) / bn);
-    const long rounds = (units + 73) / 74;
+    const long rounds = (units + n_pairs - 1) / n_pairs;
     const double by_loads = 0.93 * (256 + bn) / 2;
     const double cost = rounds * (bn > by_loads ? bn : by_loads);
     if (bn == TP_BN || cost < best_cost * 0.97) {
@@ -520,14 +521,16 @@ static int pair_token_tile(int n_tok, int m_out) {
 
 static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, TcParams p, int m_tiles,
                           int n_tiles, int bn, cudaStream_t stream) {
-  static bool configured = false;
+  static PerDevice<bool> configured_on;
+  bool& configured = configured_on.here();
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM) != cudaSuccess)
       return LLMI_ERR_LAUNCH;
     configured = true;
   }
   const long n_units = (long)m_tiles * n_tiles;
-  const long pairs = n_units < 74 ? n_units : 74;     // 148 SMs
+  const long n_pairs = sm_count() / 2 > 0 ? sm_count() / 2 : 1;     // one resident pair of CTAs per pair of SMs
+  const long pairs = n_units < n_pairs ? n_units : n_pairs;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs));
   cfg.blockDim = dim3(TC_THREADS);
@@ -760,7 +763,8 @@ template <int BN>
 static int launch_tc_ksplit(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int m_tiles, int n_tiles, int S,
                             cudaStream_t stream) {
   using C = KsConfig<BN>;
-  static bool configured = false;
+  static PerDevice<bool> configured_on;
+  bool& configured = configured_on.here();
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tc_ksplit_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
       return LLMI_ERR_LAUNCH;
@@ -835,14 +839,15 @@ template <int BN>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int m_tiles, int n_tiles,
                      cudaStream_t stream) {
   using C = TcConfig<BN>;
-  static bool configured = false;
+  static PerDevice<bool> configured_on;
+  bool& configured = configured_on.here();
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
       return LLMI_ERR_LAUNCH;
     configured = true;
   }
   const long n_units = (long)m_tiles * n_tiles * p.splits;
-  const long resident = 148L * C::CTAS_PER_SM;
+  const long resident = (long)sm_count() * C::CTAS_PER_SM;
   const int grid = (int)(n_units < resident ? n_units : resident);
   return launch_pdl(PDL_GEMM, gemm_tc_kernel<BN>, grid, TC_THREADS, C::SMEM_BYTES, stream, mw, mx, p, m_tiles, n_tiles);
 }
@@ -859,7 +864,7 @@ using namespace llmi;
 static int tc_bn(int n_tok, int m_out) {
   if (n_tok <= 128) return n_tok <= 16 ? 16 : n_tok <= 32 ? 32 : n_tok <= 64 ? 64 : 128;
   const long tiles128 = (long)((m_out + TC_BM - 1) / TC_BM) * ((n_tok + 127) / 128);
-  return tiles128 <= 148 ? 128 : 256;
+  return tiles128 <= sm_count() ? 128 : 256;
 }
 static int tc_ctas_per_sm(int bn) { return bn <= 32 ? LLMI_TC_SMALL_CTAS : (bn == 64 ? 2 : 1); }
 
@@ -869,7 +874,7 @@ LLMI_EXPORT int llmi_gemm_tc_splits(int n_tok, int m_out, int k) {
   const int bn = tc_bn(n_tok, m_out);
   const long tiles = (long)((m_out + TC_BM - 1) / TC_BM) * ((n_tok + bn - 1) / bn);
   const int kblocks = (k + TC_BK - 1) / TC_BK;
-  const long slots = 148L * tc_ctas_per_sm(bn);
+  const long slots = (long)sm_count() * tc_ctas_per_sm(bn);
   if (tiles * 2 > slots || kblocks < 8) return 1;
   int s = (int)(slots / tiles);
   if (s > kblocks / 4) s = kblocks / 4;
@@ -889,7 +894,7 @@ static int tc_cluster_size(int n_tok, int m_out, int k) {
   if (!enabled || bn < 32 || bn > 128 || llmi_gemm_tc_splits(n_tok, m_out, k) <= 1) return 1;
   const long tiles = (long)((m_out + TC_BM - 1) / TC_BM) * ((n_tok + bn - 1) / bn);
   const int per_sm = bn == 32 ? ksplit_per_sm<32>() : (bn == 64 ? ksplit_per_sm<64>() : ksplit_per_sm<128>());
-  return ksplit_cluster(tiles, (k + TC_BK - 1) / TC_BK, 148L * per_sm, bn);
+  return ksplit_cluster(tiles, (k + TC_BK - 1) / TC_BK, (long)sm_count() * per_sm, bn);
 }
 
 // 64-wide k blocks that one CTA accumulates before partial sums are added across CTAs (the whole k range when

@@ -36,7 +36,12 @@
  * after the other.
  *
  * error_out (optional, device pointer to one int, caller-owned): receives 0, or the code of a bounded wait
- * inside the kernel that gave up (then `out` is invalid).  Pass NULL to ignore it.
+ * inside the kernel that gave up (then `out` is invalid).  It is written by a copy queued on `stream` after
+ * the kernel, like `out` itself: read it only after the stream (or an event recorded behind the call) has
+ * been synchronised.  Pass NULL to ignore it.
+ *
+ * Several GPUs.  Each device that calls has its own copy of the array, its own resolved address and its own
+ * launch set-up; make each device's first call with that device current.
  *
  * Returns 0, or a negative LLMI_ERR_* code (common.cuh): -2 bad size, -4 misaligned pointer or pitch,
  * -5 no kernel for this head size and group, -6 the runtime refused cudaGetDevice/cudaGetSymbolAddress,

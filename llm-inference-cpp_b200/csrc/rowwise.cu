@@ -200,11 +200,15 @@ LLMI_EXPORT int llmi_rmsnorm(int out_dtype, const float* x, const float* weight,
   return launch_status();
 }
 
+// Streaming multiprocessors of the current device, for dispatch rules that live on the host side of the library.
+LLMI_EXPORT int llmi_sm_count() { return sm_count(); }
+
 LLMI_EXPORT int llmi_swiglu(int dtype, const void* gate_up, void* out, int n_rows, int inner, cudaStream_t stream) {
   if (n_rows <= 0 || inner <= 0) return LLMI_ERR_BAD_SIZE;
   const size_t total = (size_t)n_rows * inner;
   const int threads = 256;
-  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  const size_t most = (size_t)sm_count() * 16;       // a grid-stride loop takes the rest
+  const int blocks = (int)((total + threads - 1) / threads < most ? (total + threads - 1) / threads : most);
   if (dtype == LLMI_DTYPE_F32)
     return launch_pdl(PDL_SMALL, swiglu_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, inner, total);
   else if (dtype == LLMI_DTYPE_BF16)

@@ -1,4 +1,4 @@
-// Pieces shared by the tcgen05 matrix-product kernels (gemm_tc.cu, gemm_tc_quad.cu): tile constants, the
+// Pieces shared by the tcgen05 matrix-product kernels (gemm_tc.cu): tile constants, the
 // shared-memory operand descriptor, MMA / commit / TMEM-load wrappers, the parameter block and the epilogue
 // of one thread.
 #pragma once

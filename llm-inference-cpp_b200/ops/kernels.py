@@ -109,7 +109,8 @@ def lib():
                      "llmi_attention_decode_fused", "llmi_attention_decode_mma", "llmi_attention_decode_mma_supported",
                      "llmi_attention_decode_mma_resident",
                      "llmi_attention_prefill", "llmi_attention_prefill_supported", "llmi_gemm_skinny",
-                     "llmi_gemm_skinny_max_tokens", "llmi_attention_prefill_tc", "llmi_attention_prefill_tc_supported"):
+                     "llmi_gemm_skinny_max_tokens", "llmi_attention_prefill_tc", "llmi_attention_prefill_tc_supported",
+                     "llmi_sm_count"):
             getattr(l, name).restype = c_int
         l.llmi_gemm_tc_workspace.restype = c_long
         l.llmi_attention_decode_workspace.restype = c_long
@@ -204,6 +205,17 @@ def check_device_errors(device) -> None:
         if code:
             sc.error.zero_()
             raise KernelError(f"a bounded wait inside a kernel timed out (code {code}); results are invalid")
+
+
+_sm_count = None
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the device the kernels run on (asked once; a B200 has 148)."""
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = max(1, int(lib().llmi_sm_count()))
+    return _sm_count
 
 
 def gemm_tc_eligible(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -651,7 +663,7 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
             # 49.3 -> 50.5 us; 2,048 x 32: 42.1 -> 49.6 us).
             split = None
             q_lens, kv_lens = getattr(ctx, "host_q_lens", None), getattr(ctx, "host_kv_lens", None)
-            if _PREFILL_SPLIT and rt is not None and q_lens is not None and ctx.n_q_blocks * n_heads < 148:
+            if _PREFILL_SPLIT and rt is not None and q_lens is not None and ctx.n_q_blocks * n_heads < sm_count():
                 jobs = prefill_split_jobs(q_lens, kv_lens, window, PREFILL_SPLIT_PAGES)
                 if jobs > ctx.n_q_blocks:
                     ws = rt.scratch("attn_prefill_partials", (jobs * n_heads * (head_dim + 2) * 128,), torch.float32)

@@ -9,8 +9,12 @@ two tiny model folders into a temporary folder with weights from an integer hash
 every platform, no random-number library involved), runs
 ``llmi-generate DIR --ids ... --max-new 0 --dump FILE`` for the all-position logits and layer
 states and ``--max-new 8 --ignore-eos --json [--kv-cache]`` for greedy ids, and stores the
-results.  ``tests/test_plain_reference.py`` rebuilds the same folders with ``write_model`` below
-and checks the plain implementation (``tests/plain_llama.py``) against the stored outputs.
+results.  Two things the programs do not print come from ``reference_driver.cpp`` (beside this file),
+which it compiles against the reference's ``libllmi.a``: the probabilities the reference's sampler draws
+from (``llmi::sampling_probabilities``) for a few rows of logits under several settings, exact ties
+included, and the logits of ``forward_cached`` fed in portions of several tokens (a sequence continued by
+more than one token).  ``tests/test_plain_reference.py`` rebuilds the same folders with ``write_model``
+below and checks the plain implementation (``tests/plain_llama.py``) against the stored outputs.
 """
 import json
 import os
@@ -96,6 +100,24 @@ def write_model(model_dir, name):
     return cfg
 
 
+# (temperature, top_k, top_p) settings for the sampler's probabilities; the reference's defaults are 1, 0, 1
+SAMPLING = [(0.8, 0, 1.0), (1.0, 40, 1.0), (1.0, 0, 0.9), (0.7, 50, 0.95), (1.5, 3, 0.5), (0.0, 0, 1.0)]
+PORTIONS = {"A": 5, "B": 7}
+
+
+def sampling_rows(out):
+    """Rows of logits for the sampler: real rows of both models (scaled up, so that top-p has something to cut)
+    and made-up rows with exact ties — at the maximum, at the top-k border and inside the nucleus."""
+    rows = {"A": out["A_logits"][[0, 7, 16]] * 8.0, "B": out["B_logits"][[1, 20]] * 8.0}
+    ties = np.zeros((4, 16), dtype=np.float32)
+    ties[0, [3, 9]] = 2.0                                   # two equal maxima
+    ties[1] = np.repeat(np.arange(8, dtype=np.float32), 2)  # pairs of equal values everywhere
+    ties[2, :] = 1.0                                        # all equal
+    ties[3] = np.array([5, 5, 5, 1, 1, 1, 0, 0, -1, -1, -2, -2, -3, -3, -30, -30], dtype=np.float32)
+    rows["ties"] = ties
+    return rows
+
+
 def main():
     src = sys.argv[1]
     build = sys.argv[2] if len(sys.argv) > 2 else tempfile.mkdtemp(prefix="llmi-build-")
@@ -104,6 +126,11 @@ def main():
         subprocess.run(["cmake", "-S", src, "-B", build, "-G", "Ninja", "-DCMAKE_BUILD_TYPE=Release",
                         "-DLLMI_BUILD_TESTS=OFF"], check=True)
         subprocess.run(["cmake", "--build", build, "--target", "llmi-generate"], check=True)
+    here = os.path.dirname(os.path.abspath(__file__))
+    driver = os.path.join(build, "reference_driver")
+    subprocess.run(["cmake", "--build", build, "--target", "llmi"], check=True)
+    subprocess.run(["g++", "-std=c++20", "-O2", "-I", os.path.join(src, "include"), os.path.join(here, "reference_driver.cpp"),
+                    os.path.join(build, "libllmi.a"), "-lpthread", "-o", driver], check=True)
     out = {}
     with tempfile.TemporaryDirectory() as tmp:
         for name in CONFIGS:
@@ -122,7 +149,19 @@ def main():
                 r = subprocess.run([binary, d, "--ids", ids, "--max-new", "8", "--ignore-eos", "--json", *flag],
                                    check=True, capture_output=True, text=True)
                 out[f"{name}_{key}"] = np.asarray(json.loads(r.stdout)["generated_ids"], dtype=np.int32)
-    np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_tiny.npz"), **out)
+            part = os.path.join(tmp, f"{name}_portions.f32")
+            subprocess.run([driver, "portions", d, ids, str(PORTIONS[name]), part], check=True)
+            out[f"{name}_portions_logits"] = np.fromfile(part, dtype="<f4").reshape(t, v).copy()
+        for name, rows in sampling_rows(out).items():
+            out[f"sampling_{name}_logits"] = rows
+            fin = os.path.join(tmp, f"s_{name}.f32")
+            rows.astype("<f4").tofile(fin)
+            for i, (temp, k, p) in enumerate(SAMPLING):
+                fout = os.path.join(tmp, f"s_{name}_{i}.f32")
+                subprocess.run([driver, "sampling", fin, str(rows.shape[0]), str(rows.shape[1]), repr(temp), str(k),
+                                repr(p), fout], check=True)
+                out[f"sampling_{name}_{i}"] = np.fromfile(fout, dtype="<f4").reshape(rows.shape).copy()
+    np.savez_compressed(os.path.join(here, "reference_tiny.npz"), **out)
     print({k: v.shape for k, v in out.items()})
 
 

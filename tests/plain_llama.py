@@ -160,10 +160,11 @@ def decoder_layer(x, w, i, sz, positions, inv_freq):
     return x + swiglu_ffn(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
 
 
-def forward(cfg, w, tokens, dtype=np.float64, return_states=False):
+def forward(cfg, w, tokens, dtype=np.float64, return_states=False, rows=None):
     """Logits at every position of one whole sequence, [T, V] (src/model/transformer.cpp:78-166).
     ``return_states``: also embeddings, each layer's output and the final norm
-    (include/llmi/model/transformer.hpp:14-16)."""
+    (include/llmi/model/transformer.hpp:14-16).  ``rows``: the head for these positions only (the
+    reference's last-position mode, src/model/transformer.cpp:161-165, for any positions)."""
     sz = sizes(cfg)
     w = {k: v.astype(dtype) for k, v in w.items()}
     positions = np.arange(len(tokens))
@@ -176,7 +177,7 @@ def forward(cfg, w, tokens, dtype=np.float64, return_states=False):
     h = rmsnorm(x, w["model.norm.weight"], sz["eps"])
     states.append(h)
     head = w["model.embed_tokens.weight"] if sz["tied"] else w["lm_head.weight"]
-    logits = linear(h, head)
+    logits = linear(h if rows is None else h[np.asarray(rows)], head)
     return (logits, states) if return_states else logits
 
 

@@ -1,8 +1,9 @@
 """The kernels that only large shapes reach — the product on pairs of SMs (256 tokens and more), the cluster
 k-split (17 to about 1,000 tokens), the tcgen05 prompt attention (head sizes 64 and 128), the tensor-core decode
 attention for grouped queries — inside the model: two layers at SmolLM2-1.7B width, and two at the width of an
-8B Llama (4,096 wide, 32 heads of 128 over 8 kv heads, feed-forward 14,336), the bf16 path against the 32-bit
-path of the same seeded weights (GPU)."""
+8B Llama (4,096 wide, 32 heads of 128 over 8 kv heads, feed-forward 14,336): both paths against the plain
+implementation on a few hundred tokens, and the bf16 path against the 32-bit path of the same seeded weights on
+thousands (GPU)."""
 import numpy as np
 import pytest
 
@@ -57,3 +58,53 @@ def test_bf16_path_follows_the_32_bit_path_at_8b_width():
     for a, b in zip(fast, exact):
         assert np.isfinite(a).all()
         assert float(np.abs(a - b).max() / np.abs(b).max()) < 3e-2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape", ["width-2048", "width-4096"])
+def test_full_width_layers_follow_the_plain_implementation(shape, dtype):
+    """The oracle for the kernels the benchmark consists of is the plain implementation, not the engine's other path:
+    two layers at full width, prompts of a few hundred tokens in one step (more than 512 tokens at width 2,048, so
+    that the product runs on pairs of SMs; 129 to 511 at width 4,096, where its k range is cut over a cluster; the
+    tcgen05 prompt attention at both head sizes), then decode steps through the recorded-graph path."""
+    import torch
+    import helpers as H
+    import plain_llama as P
+    import llmi_b200 as L
+    from llmi_b200.config import parse_config
+    from llmi_b200.engine.model import Model
+    from llmi_b200.sampling import Sampler
+    from llmi_b200.weights.random_weights import random_tensors
+    cfg = dict(CONFIG) if shape == "width-2048" else dict(WIDE, vocab_size=8000)
+    lens = [400, 130, 1] if shape == "width-2048" else [300, 60]
+    n_decode = 3
+    V = cfg["vocab_size"]
+    arch, typed = parse_config(cfg)
+    spec = arch.model_spec(typed)
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    tensors = random_tensors(spec, 21, "cpu", store)
+    w = {n: t.double().numpy() for n, t in tensors.items()}
+    model = Model(spec, tensors, store, "cuda:0", config=typed)
+    del tensors
+    rng = np.random.default_rng(4)
+    toks = [rng.integers(0, V, n + n_decode).tolist() for n in lens]
+    refs = [P.forward(cfg, w, t, rows=list(range(n - 1, n + n_decode))) for t, n in zip(toks, lens)]
+    del w
+    cache = model.new_cache(sum(H.round_up(len(t)) for t in toks), n_slots=len(toks))
+    slots = [cache.alloc_slot() for _ in toks]
+    got = [[] for _ in toks]
+    out = model.step(cache, [L.SequenceStep(s, t[:n], [n - 1]) for s, t, n in zip(slots, toks, lens)]).cpu().numpy()
+    for i in range(len(toks)):
+        got[i].append(out[i].copy())
+    sampler = Sampler(L.SamplingParams(), model.rt)
+    for j in range(n_decode):
+        model.step_and_choose(cache, [L.SequenceStep(s, [t[n + j]], [0]) for s, t, n in zip(slots, toks, lens)], sampler)
+        out = model.last_logits.cpu().numpy()
+        for i in range(len(toks)):
+            got[i].append(out[i].copy())
+    from llmi_b200.ops import kernels
+    kernels.check_device_errors("cuda:0")
+    for i in range(len(toks)):
+        g = np.stack(got[i])
+        assert np.isfinite(g).all()
+        assert H.rel_to_max(g, refs[i]) < H.TOL[dtype], (shape, dtype, i)

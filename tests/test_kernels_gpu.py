@@ -349,6 +349,37 @@ def test_sample_matches_plain(temperature, top_k, top_p):
         assert P.sampling_probabilities(logits[i].cpu().numpy(), temperature, top_k, top_p)[tok] > 0
 
 
+@pytest.mark.parametrize("rows", ["A", "B", "ties"])
+def test_sample_follows_the_reference_librarys_distribution(rows):
+    """The device sampler against the probabilities recorded from the reference's own library
+    (tests/golden/make_golden.py: llmi::sampling_probabilities, src/model/sampling.cpp:11-58; exact ties included):
+    for a grid of uniform numbers every draw is the first id, in ascending order, at which the recorded cumulative
+    probability reaches the number (src/model/sampling.cpp:60-76) — so no token outside the recorded support is ever
+    drawn, and none inside it is skipped."""
+    import os
+    from golden import make_golden as G
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_tiny.npz"))
+    logits = gold[f"sampling_{rows}_logits"]
+    R, V = logits.shape
+    grid = np.concatenate([np.linspace(0.0005, 0.9995, 400), [1e-9, 1 - 1e-9]])
+    for i, (temperature, top_k, top_p) in enumerate(G.SAMPLING):
+        ref = gold[f"sampling_{rows}_{i}"].astype(np.float64)
+        for r in range(R):
+            dev = torch.from_numpy(np.repeat(logits[r:r + 1], len(grid), 0)).cuda()
+            u = torch.from_numpy(grid).cuda()
+            out = torch.empty(len(grid), dtype=torch.int32, device="cuda")
+            if temperature <= 0:
+                K().argmax(dev, out)
+            else:
+                K().sample(dev, temperature, top_k, top_p, u, torch.empty(len(grid), V, device="cuda"), out)
+            got = out.cpu().numpy()
+            cum = np.cumsum(ref[r])
+            assert (ref[r][got] > 0).all(), (rows, i, r)
+            for g, x in zip(got, grid):
+                want = int(np.nonzero((cum >= x) & (ref[r] > 0))[0][0]) if (cum >= x).any() else int(np.nonzero(ref[r] > 0)[0][-1])
+                assert g == want or np.min(np.abs(cum - x)) < 2e-6, (rows, i, r, x, g, want)
+
+
 def test_sample_distribution():
     """Many draws from one row follow the filtered distribution."""
     torch.manual_seed(2)

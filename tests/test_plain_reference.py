@@ -100,3 +100,28 @@ def test_parts_alone():
     assert np.count_nonzero(p) == 2 and np.isclose(p.sum(), 1.0)
     p = P.sampling_probabilities(np.array([0.0, 0.0, 10.0]), 1.0, top_p=0.5)
     assert np.count_nonzero(p) == 1
+
+
+@pytest.mark.parametrize("rows", ["A", "B", "ties"])
+def test_sampling_probabilities_match_the_reference_library(rows):
+    """The distribution the sampler draws from (src/model/sampling.cpp:11-58), recorded from the reference's own
+    library for real and made-up rows of logits, exact ties included: the same tokens survive top-k and top-p, and
+    their probabilities agree to float rounding."""
+    logits = GOLD[f"sampling_{rows}_logits"]
+    for i, (temperature, top_k, top_p) in enumerate(G.SAMPLING):
+        ref = GOLD[f"sampling_{rows}_{i}"]
+        for r in range(logits.shape[0]):
+            p = P.sampling_probabilities(logits[r], temperature, top_k, top_p)
+            assert np.array_equal(p > 0, ref[r] > 0), (rows, i, r)
+            assert np.allclose(p, ref[r], rtol=2e-6, atol=1e-12), (rows, i, r)
+            assert abs(ref[r].sum() - 1.0) < 1e-5
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_a_sequence_continued_in_portions_is_the_whole_sequence(tmp_path, name):
+    """The reference's ``forward_cached`` fed in portions of several tokens gives its whole-sequence logits bit for bit
+    (include/llmi/model/transformer.hpp:25-28), so the plain whole-sequence pass is the oracle for portions too."""
+    assert np.array_equal(GOLD[f"{name}_portions_logits"], GOLD[f"{name}_logits"])
+    G.write_model(str(tmp_path), name)
+    cfg, w = P.read_model(str(tmp_path))
+    assert rel(P.forward(cfg, w, G.PROMPTS[name]), GOLD[f"{name}_portions_logits"]) < 2e-6

@@ -105,3 +105,15 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     torch.cuda.synchronize()
     assert rc == -7                               # LLMI_ERR_STATIC_SCRATCH: refused, nothing launched
     assert (out == 7.0).all()
+    # 2,000 sequences of 8 kv heads fit the tickets (16,000 of 16,384) but their partial results do not:
+    # 2,000 x 8 heads x 8 splits x (64 + 2) floats are far more than the array's 1,048,576
+    wide = dict(pr, S=2000)
+    rc = _call_static(lib, wide, out, 1, torch.zeros(1, dtype=torch.int32, device="cuda"))
+    torch.cuda.synchronize()
+    assert rc == -7
+    assert (out == 7.0).all()
+    # and the same sizes with few enough sequences run
+    err = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    rc = _call_static(lib, pr, out, 1, err)
+    torch.cuda.synchronize()
+    assert rc == 0 and int(err.item()) == 0 and torch.isfinite(out.float()).all()
