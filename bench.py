@@ -1,6 +1,7 @@
 """Decode and prefill throughput of the library at SmolLM2-1.7B shape (random bf16 weights, one B200).
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --workload smollm2-360m|smollm2-135m [--workload-dtypes bfloat16,float32]
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and context 4096 (a
 "step" is one decode step of the whole batch), timed on the device with CUDA events around
@@ -62,7 +63,7 @@ class ClockSampler:
         """Start sampling (the tool takes a moment to come up: call this before the warm-up)."""
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
-                                          "-i", "0", "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-i", "0", "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -184,6 +185,56 @@ def prefill_flops(cfg, layers, T):
     return 2 * T * per_token + attn + 2 * H * V              # the head runs on the last row only
 
 
+# The other two shapes of the benchmark set: whole requests through generate() (prefill and decoding in one time)
+WORKLOADS = {
+    "smollm2-360m": {
+        "config": {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 32, "hidden_size": 960, "num_attention_heads": 15,
+                   "num_key_value_heads": 5, "head_dim": 64, "intermediate_size": 2560, "vocab_size": 49152, "rope_theta": 100000.0,
+                   "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 8192, "hidden_act": "silu"},
+        "prompts": lambda rng: [int(n) for n in rng.integers(16, 1025, 8)], "max_new": 256, "max_new_fp32": 256,
+        "what": "8 prompts of 16..1,024 uniform random ids, 256 new tokens each"},
+    "smollm2-135m": {
+        "config": {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 30, "hidden_size": 576, "num_attention_heads": 9,
+                   "num_key_value_heads": 3, "head_dim": 64, "intermediate_size": 1536, "vocab_size": 49152, "rope_theta": 100000.0,
+                   "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 8192, "hidden_act": "silu"},
+        "prompts": lambda rng: [512] * 64, "max_new": 512, "max_new_fp32": 64,
+        "what": "64 prompts of 512 uniform random ids, 512 new tokens each (64 in fp32)"},
+}
+
+
+def workload_run(name, dtypes):
+    """One of the other benchmark shapes through the public entry point; prints one JSON line."""
+    import numpy as np
+    import torch
+    import llmi_b200 as L
+    wl = WORKLOADS[name]
+    rng = np.random.default_rng(0)
+    lens = wl["prompts"](rng)
+    V = wl["config"]["vocab_size"]
+    prompts = [rng.integers(0, V, n).tolist() for n in lens]
+    out = {"workload": name, "what": wl["what"], "impl": "ours", "data": "synthetic (random weights, uniform random token ids)",
+           "prompt_tokens": int(sum(lens)), "runs": {}}
+    for dtype in dtypes:
+        max_new = wl["max_new"] if dtype == "bfloat16" else wl["max_new_fp32"]
+        model = L.random_model(wl["config"], seed=0, dtype=dtype, on_device=True)
+        L.generate(model, prompts[:2], max_new=4, ignore_eos=True)          # builds the kernels' one-time state
+        best = None
+        for _ in range(2):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            got, info = L.generate(model, prompts, max_new=max_new, ignore_eos=True, return_details=True)
+            torch.cuda.synchronize()
+            sec = time.perf_counter() - t0
+            best = sec if best is None else min(best, sec)
+        new = sum(len(g) for g in got)
+        out["runs"][dtype] = {"seconds": round(best, 4), "new_tokens": new, "new_tokens_per_s": round(new / best, 1),
+                              "steps": info["steps"], "batches": info["batches"]}
+        del model
+        torch.cuda.empty_cache()
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -196,6 +247,9 @@ def main():
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print its numbers (for profiling one kernel class; not a bench line)")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
+                    help="run one of the other benchmark shapes whole, through generate(), and print its own JSON line")
+    ap.add_argument("--workload-dtypes", default="bfloat16", help="comma-separated: bfloat16, float32")
     ap.add_argument("--kv-heads", type=int, default=None,
                     help="with --only: another number of key/value heads (grouped queries), to profile their kernels")
     args = ap.parse_args()
@@ -212,6 +266,8 @@ def main():
     if args.gpus != 1:
         print("bench.py: this library runs on one GPU; --gpus must be 1")
         return 2
+    if args.workload:
+        return workload_run(args.workload, [d.strip() for d in args.workload_dtypes.split(",") if d.strip()])
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)
 

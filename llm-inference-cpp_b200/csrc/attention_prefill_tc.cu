@@ -565,8 +565,9 @@ static int ft_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
       return LLMI_ERR_LAUNCH;
     configured = true;
   }
-  attention_prefill_tc_kernel<HD><<<grid, C::THREADS, C::SMEM, stream>>>(mq, mk, mv, p);
-  return launch_status();
+  // a programmatic dependent: its blocks set themselves up (barriers, tensor memory, descriptors) while the kernel
+  // before drains; the producer waits before its first copy, and nothing else reads or writes global memory earlier
+  return launch_pdl(PDL_ATTENTION, attention_prefill_tc_kernel<HD>, grid, dim3(C::THREADS), C::SMEM, stream, mq, mk, mv, p);
 }
 }  // namespace llmi
 

@@ -53,8 +53,7 @@ class Model:
         total = self.embedding.weight_bytes() + self.head.weight_bytes()
         used = {call.layer for call in self.spec.schedule}
         for i in used:
-            blk = self.layers[i].block
-            for p in (blk.mixer, blk.ffn):
+            for p in self.layers[i].parts.values():
                 total += p.weight_bytes() if hasattr(p, "weight_bytes") else 0
         return total
 

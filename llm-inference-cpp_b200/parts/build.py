@@ -15,10 +15,8 @@ from .spec import ModelSpec, PartSpec
 def _part_specs(spec: ModelSpec):
     yield "embedding", spec.embedding
     for layer in spec.layers:
-        yield "norm", layer.mixer_norm
-        yield "mixer", layer.mixer
-        yield "norm", layer.ffn_norm
-        yield "ffn", layer.ffn
+        for _, family, ps in layer.slots():
+            yield family, ps
     yield "norm", spec.final_norm
     yield "head", spec.head
 
@@ -41,22 +39,31 @@ def _make(family: str, ps: PartSpec, tensors: dict, rt, **context):
     return cls(ps, local, rt, **context)
 
 
+class NoMixer:
+    """Stands in for the mixer of a layer that has none: it keeps no cache."""
+
+    def cache_request(self):
+        return None
+
+
 class BuiltLayer:
-    def __init__(self, block_part, mixer):
+    def __init__(self, block_part, parts: dict):
         self.block = block_part
-        self.mixer = mixer
+        self.parts = parts                              # slot -> built part
+        self.mixer = parts.get("mixer") or NoMixer()    # the part whose cache the layer keeps
 
 
 def build_parts(spec: ModelSpec, tensors: dict, rt):
     """-> (embedding, [BuiltLayer], final_norm, head)."""
     emb = _make("embedding", spec.embedding, tensors, rt)
     layers = []
-    for ls in spec.layers:
-        mixer_norm = _make("norm", ls.mixer_norm, tensors, rt)
-        mixer = _make("mixer", ls.mixer, tensors, rt)
-        ffn_norm = _make("norm", ls.ffn_norm, tensors, rt)
-        ffn = _make("ffn", ls.ffn, tensors, rt)
-        layers.append(BuiltLayer(get_part("block", ls.block)(mixer_norm, mixer, ffn_norm, ffn), mixer))
+    for i, ls in enumerate(spec.layers):
+        parts = {slot: _make(family, ps, tensors, rt) for slot, family, ps in ls.slots()}
+        try:
+            block = get_part("block", ls.block)(**parts)
+        except TypeError as e:
+            raise ValueError(f"layer {i}: the arrangement {ls.block!r} does not take the slots {sorted(parts)}: {e}") from None
+        layers.append(BuiltLayer(block, parts))
     final_norm = _make("norm", spec.final_norm, tensors, rt)
     head = _make("head", spec.head, tensors, rt, embedding=emb)
     return emb, layers, final_norm, head

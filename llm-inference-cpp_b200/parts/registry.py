@@ -13,7 +13,9 @@ Families and what the engine calls on their members (``rt`` is the
 ``mixer``      ``cache_request() -> KVRequest | StateRequest | None`` and
                ``forward(h, x, ctx, binding)``: adds its output to ``x``
 ``ffn``        ``forward(h, x, ctx)``: adds its output to ``x``
-``block``      ``forward(x, ctx, binding)``: one layer's arrangement of the above
+``block``      ``forward(x, ctx, binding)``: one layer's arrangement of the above; built with one keyword argument
+               per filled slot of its ``LayerSpec`` (``mixer_norm``, ``mixer``, ``ffn_norm``, ``ffn`` and whatever
+               the spec adds under ``more``)
 ``embedding``  ``forward(token_ids, ctx) -> x`` and ``table()`` (for a tied head)
 ``head``       ``forward(h_rows) -> logits fp32 [rows, vocab]``
 

@@ -20,12 +20,30 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: an arrangement (``block``) of a mixer and a feed-forward with their norms."""
+    """One layer: an arrangement (``block``) and the parts it arranges, each in a named slot.
+
+    The four usual slots have fields of their own; any of them may be None (a layer without a
+    feed-forward, say), and ``more`` adds slots by name — ``(slot, family, PartSpec)`` triples, for an
+    arrangement with further norms or a second feed-forward.  The block class is built with one keyword
+    argument per filled slot.  The part in the slot ``mixer``, if any, is the one whose cache the layer keeps.
+    """
     block: str                      # arrangement, e.g. "prenorm"
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    ffn_norm: PartSpec
-    ffn: PartSpec
+    mixer_norm: Optional[PartSpec] = None
+    mixer: Optional[PartSpec] = None
+    ffn_norm: Optional[PartSpec] = None
+    ffn: Optional[PartSpec] = None
+    more: tuple = ()                # ((slot, family, PartSpec), ...)
+
+    def slots(self):
+        """(slot, family, PartSpec) of every filled slot, in the order the tensors are declared."""
+        for slot, family in (("mixer_norm", "norm"), ("mixer", "mixer"), ("ffn_norm", "norm"), ("ffn", "ffn")):
+            ps = getattr(self, slot)
+            if ps is not None:
+                yield slot, family, ps
+        for slot, family, ps in self.more:
+            if slot in ("mixer_norm", "mixer", "ffn_norm", "ffn", "block", "more"):
+                raise ValueError(f"layer: the slot name {slot!r} is taken")
+            yield slot, family, ps
 
 
 @dataclass(frozen=True)

@@ -426,3 +426,81 @@ def test_toy_routed_ffn_and_learned_positions(tmp_path):
         for r in reqs:
             assert np.isfinite(got[r]).all()
             assert H.rel_to_max(got[r], refs[r]) < 2e-5, r
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_an_arrangement_with_other_slots_without_touching_the_library(tmp_path, dtype):
+    """A layer is an arrangement and the parts in its named slots.  Here an arrangement defined in the test puts a norm
+    AFTER the mixer as well ("sandwich": x += post_norm(attention(norm(x)))), one layer has a feed-forward and the
+    other has none, and the library's own norm, attention and feed-forward parts fill the slots: spec, builder,
+    weights, cache, step and replay are the library's, unchanged."""
+    import llmi_b200 as L
+    from llmi_b200.config.registry import Architecture
+    from llmi_b200.parts import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from llmi_b200.parts.registry import register_part
+
+    W, NH, NKV, HD, F, V, MAXPOS, EPS, THETA = 80, 5, 1, 16, 112, 150, 256, 1e-5, 20000.0
+
+    class Sandwich:
+        """x += post_mixer_norm(mixer(mixer_norm(x))); then, if the layer has them, x += ffn(ffn_norm(x))."""
+
+        def __init__(self, mixer_norm, mixer, post_mixer_norm, ffn_norm=None, ffn=None):
+            self.mixer_norm, self.mixer, self.post, self.ffn_norm, self.ffn = mixer_norm, mixer, post_mixer_norm, ffn_norm, ffn
+
+        def forward(self, x, ctx, binding):
+            branch = torch.zeros_like(x)                         # the library's mixers ADD their output to what they are given
+            self.mixer.forward(self.mixer_norm.forward(x), branch, ctx, binding)
+            x += self.post.forward(branch, scratch_name="sandwich_post").float()
+            if self.ffn is not None:
+                self.ffn.forward(self.ffn_norm.forward(x), x, ctx)
+
+    register_part("block", "toy_sandwich", Sandwich, replace=True)
+
+    def norm(prefix):
+        return PartSpec("rms", {"width": W, "eps": EPS}, prefix)
+
+    def toy_spec(c):
+        pos = PartSpec("rotary_half", {"head_dim": HD, "theta": THETA})
+        layers = []
+        for i in range(2):
+            p = f"model.layers.{i}."
+            layers.append(LayerSpec(
+                "toy_sandwich", mixer_norm=norm(p + "input_layernorm."),
+                mixer=PartSpec("gqa", {"width": W, "n_heads": NH, "n_kv_heads": NKV, "head_dim": HD, "bias": False,
+                                       "position": pos}, p + "self_attn."),
+                ffn_norm=norm(p + "post_attention_layernorm.") if i == 0 else None,
+                ffn=PartSpec("swiglu", {"width": W, "inner": F}, p + "mlp.") if i == 0 else None,
+                more=(("post_mixer_norm", "norm", norm(p + "post_mixer_norm.")),)))
+        return ModelSpec("ToySandwichLM", V, W, MAXPOS, PartSpec("token_table", {"vocab": V, "width": W}, "model.embed_tokens."),
+                         tuple(layers), (ScheduleEntry(0), ScheduleEntry(1)), norm("model.norm."),
+                         PartSpec("linear_head", {"vocab": V, "width": W, "tied": True}, "lm_head."))
+
+    L.register_architecture(Architecture("ToySandwichLM", lambda root: dict(root), toy_spec), replace=True)
+    L.write_random_model(str(tmp_path), {"architectures": ["ToySandwichLM"]}, 3, torch.float32 if dtype == "float32" else torch.bfloat16)
+    model = L.load(str(tmp_path), dtype)
+    w = P.read_safetensors(str(tmp_path / "model.safetensors"))
+    assert "model.layers.1.mlp.up_proj.weight" not in w and "model.layers.1.post_mixer_norm.weight" in w
+    assert model.weight_bytes() > 0
+    sz = dict(nh=NH, nkv=NKV, hd=HD, eps=EPS, bias=False)
+
+    def plain(tokens):
+        T = len(tokens)
+        inv = P.rope_inv_freq(HD, THETA)
+        x = P.embedding(w["model.embed_tokens.weight"], tokens)
+        for i in range(2):
+            p = f"model.layers.{i}."
+            x = x + P.rmsnorm(P.attention_block(x, w, p, sz, np.arange(T), inv), w[p + "post_mixer_norm.weight"], EPS)
+            if i == 0:
+                h = P.rmsnorm(x, w[p + "post_attention_layernorm.weight"], EPS)
+                x = x + P.swiglu_ffn(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+        return P.linear(P.rmsnorm(x, w["model.norm.weight"], EPS), w["model.embed_tokens.weight"])
+
+    rng = np.random.default_rng(6)
+    reqs = {"a": rng.integers(0, V, 70).tolist(), "b": rng.integers(0, V, 9).tolist(), "c": rng.integers(0, V, 130).tolist()}
+    refs = {r: plain(t) for r, t in reqs.items()}
+    for steps, most in (H.trace_whole(reqs), H.trace_last_decoded(reqs, 32), H.trace_batches(reqs, 3, {"a": 30, "b": 9, "c": 70}),
+                        H.trace_portions(reqs, 50)):
+        got = H.collect(steps, H.replay(model, steps, max(most, 512)), V)
+        for r in reqs:
+            assert np.isfinite(got[r]).all()
+            assert H.rel_to_max(got[r], refs[r]) < H.TOL[dtype], r
