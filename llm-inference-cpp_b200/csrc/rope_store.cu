@@ -128,7 +128,7 @@ rope_store_vec_kernel(T* __restrict__ qkv, long ld, const float* __restrict__ in
 // its partner chunk in the second half, computes the chunk's sines and cosines once, and walks over every
 // ROWS_HEAD_LANES-th head of the token with 16-byte loads and stores.  The arithmetic of an element is
 // that of the kernels above, so the results are the same bits.
-constexpr int ROWS_HEAD_LANES = 8;
+constexpr int ROWS_HEAD_LANES = 16;
 
 template <typename T> struct Chunk;
 template <> struct Chunk<float> {
