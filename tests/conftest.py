@@ -43,7 +43,14 @@ TINY_C = {
     "num_key_value_heads": 3, "head_dim": 32, "intermediate_size": 200, "vocab_size": 500, "rope_theta": 50000.0,
     "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 1024, "hidden_act": "silu",
 }
-TINY_CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# And one whose sizes fit no fast kernel: rows of 72 bytes (no 16-byte alignment), head size 12, an odd vocabulary.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 36, "num_attention_heads": 3,
+    "num_key_value_heads": 3, "head_dim": 12, "intermediate_size": 50, "vocab_size": 77, "rope_theta": 300.0,
+    "rms_norm_eps": 1e-4, "tie_word_embeddings": False, "max_position_embeddings": 200, "hidden_act": "silu",
+    "attention_bias": True,
+}
+TINY_CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 @pytest.fixture(scope="session")

@@ -198,7 +198,7 @@ WIDTH_576 = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hid
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "width576"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "width576"])
 def test_logits_of_recorded_padded_decode_steps(model_dirs, tmp_path, name, dtype):
     """The path that generation and the benchmark run — ``step_and_choose`` with recorded graphs: batches padded to a
     power of two with sequences of index -1, padded page tables, the index block patched from one step to the next —

@@ -14,8 +14,9 @@ from conftest import ROOT, TINY_CONFIGS
 pytestmark = pytest.mark.gpu
 
 STORAGE = {"float32": "F32", "bfloat16": "BF16"}
-CONFIG_NAMES = ["A", "B", "C"]
-LENGTHS = {"A": [5, 9, 17, 40, 100, 128], "B": [1, 12, 30, 64, 65, 200], "C": [3, 33, 64, 129, 300, 700]}
+CONFIG_NAMES = ["A", "B", "C", "D"]
+LENGTHS = {"A": [5, 9, 17, 40, 100, 128], "B": [1, 12, 30, 64, 65, 200], "C": [3, 33, 64, 129, 300, 700],
+           "D": [2, 31, 64, 66, 150, 199]}
 
 
 def make_requests(name, seed=11):
@@ -49,7 +50,7 @@ def check(got, refs, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", CONFIG_NAMES)
 def test_whole_requests(loaded, name, dtype):
     model, reqs, refs, _ = loaded(name, dtype)
     steps, most = H.trace_whole(reqs)
@@ -78,7 +79,7 @@ def test_f16_weights_are_used_exactly_in_the_32_bit_path(model_dirs, name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", CONFIG_NAMES)
 def test_last_32_tokens_one_by_one(loaded, name, dtype):
     model, reqs, refs, _ = loaded(name, dtype)
     steps, most = H.trace_last_decoded(reqs, 32)
@@ -86,7 +87,7 @@ def test_last_32_tokens_one_by_one(loaded, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", CONFIG_NAMES)
 def test_unequal_batches_one_after_another(loaded, name, dtype):
     model, reqs, refs, _ = loaded(name, dtype)
     rng = np.random.default_rng(3)
