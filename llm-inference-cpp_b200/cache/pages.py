@@ -166,6 +166,22 @@ class PagePool:
         self._length[slot] = base + n_new
         return base
 
+    def shrink_by_one(self, slot: int) -> None:
+        """Take back the newest position of a slot (the undo of ``extend(slot, 1)``; pools without a window only:
+        a window's growth may have given pages back, which cannot be undone)."""
+        if self.window > 0:
+            raise CacheError("cache: a windowed group cannot take a position back")
+        n = self._length[slot] - 1
+        if n < 0:
+            raise CacheError(f"cache: slot {slot} holds no position to take back")
+        if n % self.page_size == 0:            # the position opened a page: the page goes back to where it came from
+            page = self._pages[slot].pop()
+            self._free.append(page)
+            i = len(self._pages[slot])
+            if self.matrix is not None and slot < self.matrix.shape[0] and i < self.matrix.shape[1]:
+                self.matrix[slot, i] = -1
+        self._length[slot] = n
+
     def _release_before(self, slot: int, first_needed: int) -> None:
         table = self._pages[slot]
         for i in range(min(len(table), max(0, first_needed) // self.page_size)):

@@ -96,11 +96,13 @@ class SequenceCache:
                           for r, n in kv_requests]
         self.state_groups = [StateGroup(r, n, self.n_slots, device) for r, n in state_requests]
         self._length: dict[int, int] = {}
+        self._ahead: tuple = ()          # slots whose next position is reserved already (see speculate_each_by_one)
         self.device = device
         self.dtype = dtype
 
     # -- slots -----------------------------------------------------------------------------
     def alloc_slot(self) -> int:
+        self.settle()
         slot = self.slots.alloc()
         for g in self.kv_groups:
             g.pool.open(slot)
@@ -111,19 +113,55 @@ class SequenceCache:
 
     def free_slot(self, slot: int) -> None:
         self.slots.free(slot)          # raises on a slot that is not live
+        if slot in self._ahead:        # everything the slot holds goes back below, a reserved next position included
+            self._ahead = tuple(s for s in self._ahead if s != slot)
         for g in self.kv_groups:
             g.pool.close(slot)
         del self._length[slot]
 
     def length(self, slot: int) -> int:
+        """Positions the slot holds (a position reserved ahead of its step does not count)."""
         if slot not in self._length:
             raise CacheError(f"cache: slot {slot} is not live")
-        return self._length[slot]
+        return self._length[slot] - (1 if slot in self._ahead else 0)
+
+    # -- one step ahead --------------------------------------------------------------------
+    # While the device runs a decode step, the host can already lay out the next one — positions, lengths, page
+    # tables — if the same sequences go on; only their tokens are missing.  That needs the next positions reserved
+    # before it is known whether the step will come.  The reservation is invisible (``length`` does not count it) and
+    # is taken back (``settle``) by whatever touches the cache next, unless the expected step arrives and commits it.
+    def can_speculate(self) -> bool:
+        return all(g.pool.window == 0 for g in self.kv_groups)
+
+    def speculate_each_by_one(self, slots) -> "np.ndarray":
+        """Reserve one more position for every slot of ``slots`` ahead of its step; returns the positions.
+        Raises (and reserves nothing) where :meth:`extend_each_by_one` would."""
+        self.settle()
+        if not self.can_speculate():
+            raise CacheError("cache: a windowed group cannot reserve ahead")
+        bases = self._extend_each_by_one(slots)
+        self._ahead = tuple(slots)
+        return bases
+
+    def commit_speculation(self) -> None:
+        """The step the positions were reserved for has come: they count from now on."""
+        self._ahead = ()
+
+    def settle(self) -> None:
+        """Take back positions that were reserved ahead of a step that has not come."""
+        if self._ahead:
+            ahead, self._ahead = self._ahead, ()
+            for s in ahead:
+                if s in self._length:
+                    for g in self.kv_groups:
+                        g.pool.shrink_by_one(s)
+                    self._length[s] -= 1
 
     # -- growth ----------------------------------------------------------------------------
     def can_extend(self, wanted: dict) -> None:
         """Raise unless every slot of ``wanted`` (slot → new tokens) fits, in every group.  A windowed group
         counts the pages its slots give back before they take new ones."""
+        self.settle()
         for slot, n_new in wanted.items():
             if slot not in self._length:
                 raise CacheError(f"cache: slot {slot} is not live")
@@ -165,6 +203,10 @@ class SequenceCache:
         """One more position for every slot of ``slots`` (distinct, live): the decode step's growth, with the
         checks of :meth:`can_extend` and without a loop over the slots that need no page.  Nothing changes
         if it raises.  Returns the new positions."""
+        self.settle()
+        return self._extend_each_by_one(slots)
+
+    def _extend_each_by_one(self, slots) -> "np.ndarray":
         if not self.slots.all_live(slots):
             bad = next(s for s in slots if not self.slots.is_live(s))
             raise CacheError(f"cache: slot {bad} is not live")

@@ -104,6 +104,7 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
     """
     if not seqs:
         raise StepError("step: no sequences")
+    cache.settle()                 # positions reserved ahead of a step that did not come go back first
     n_real = len(seqs)
     lens = [len(s.tokens) for s in seqs]
     if min(lens) == 0:
@@ -125,7 +126,7 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
             if not (0 <= int(w) < n):
                 raise StepError(f"step: wanted place {w} is not among the {n} tokens given")
     bases = [cache.length(slot) for slot in slots]          # raises CacheError for a slot that is not live
-    cache.extend_all(dict(zip(slots, lens)))       # raises with nothing reserved if the step does not fit
+    cache.extend_all(dict(zip(slots, lens)))       # raises with nothing reserved if the step does not fit (it first takes back what was reserved ahead)
 
     n_seqs = max(n_real, pad_seqs_to) if decode else n_real
     n_pad = n_seqs - n_real
@@ -238,20 +239,61 @@ def continue_decode_step(cache, prev: StepContext, tokens, vocab_size: int, buff
     the same sizes) by one token each: only the token ids, the positions, the lengths and the page tables
     change, so the block is copied and patched instead of being planned anew.  The checks are those of
     :func:`plan_step`.  The caller makes sure that the page tables still fit ``prev``'s width."""
-    lay = prev.layout
-    n_real = len(lay.slots)
+    toks = _check_continuing_tokens(prev, tokens, vocab_size)
+    bases = cache.extend_each_by_one(prev.layout.slots)
+    host = _patched_block(prev, bases, buffers)
+    _finish_block(prev, host, toks, bases, buffers)
+
+
+@dataclass
+class PendingStep:
+    """A continued decode step laid out ahead of its tokens (see :func:`prepare_continue`)."""
+    host: torch.Tensor
+    bases: "np.ndarray"
+    serial: int
+
+
+def prepare_continue(cache, prev: StepContext, buffers: StepBuffers) -> PendingStep:
+    """Everything of :func:`continue_decode_step` that does not need the tokens, done while the device still runs
+    ``prev``: the next positions are reserved ahead (``cache.speculate_each_by_one``) and the block is copied and
+    patched.  :func:`finish_continue` adds the tokens and uploads it; if the step never comes, ``cache.settle()``
+    takes the reservation back and the block is forgotten.  Raises CacheError (nothing reserved) if the cache has
+    no room or cannot reserve ahead."""
+    bases = cache.speculate_each_by_one(prev.layout.slots)
+    host = _patched_block(prev, bases, buffers)
+    return PendingStep(host, bases, buffers.serial)
+
+
+def finish_continue(cache, prev: StepContext, pending: PendingStep, tokens, vocab_size: int, buffers: StepBuffers) -> None:
+    """The tokens of a step laid out by :func:`prepare_continue` have come: check them, upload the block, and let
+    the reserved positions count.  A bad token id raises with the reservation taken back."""
+    try:
+        toks = _check_continuing_tokens(prev, tokens, vocab_size)
+    except StepError:
+        cache.settle()
+        raise
+    cache.commit_speculation()
+    _finish_block(prev, pending.host, toks, pending.bases, buffers)
+
+
+def _check_continuing_tokens(prev: StepContext, tokens, vocab_size: int):
+    n_real = len(prev.layout.slots)
     toks = np.asarray(tokens, dtype=np.int64)
     if toks.shape != (n_real,):
         raise StepError("step: one token for each sequence of the step before")
     if toks.min() < 0 or toks.max() >= vocab_size:
         bad = int(toks[(toks < 0) | (toks >= vocab_size)][0])
         raise StepError(f"step: token id {bad} out of range")
-    bases = cache.extend_each_by_one(lay.slots)
+    return toks
+
+
+def _patched_block(prev: StepContext, bases, buffers: StepBuffers):
+    """A fresh host block holding ``prev``'s arrays with positions, lengths and page tables one token on."""
+    lay = prev.layout
+    n_real = len(lay.slots)
     host, _ = buffers.stage(lay.n_int32)
     h = host.numpy()
     h[:lay.n_int32] = lay.host.numpy()[:lay.n_int32]
-    a = lay.offsets["token_ids"][0]
-    h[a:a + n_real] = toks
     a = lay.offsets["tok_pos"][0]
     h[a:a + n_real] = bases
     a = lay.offsets["seq_kv_len"][0]
@@ -268,6 +310,13 @@ def continue_decode_step(cache, prev: StepContext, tokens, vocab_size: int, buff
             for i, slot in enumerate(lay.slots):
                 pages = g.pool.table(slot)
                 table[i, :len(pages)] = pages
+    return host
+
+
+def _finish_block(prev: StepContext, host, toks, bases, buffers: StepBuffers) -> None:
+    lay = prev.layout
+    a = lay.offsets["token_ids"][0]
+    host.numpy()[a:a + len(lay.slots)] = toks
     buffers.upload(lay.n_int32)
     lay.host = host
     prev.max_kv_len = int(bases.max()) + 1

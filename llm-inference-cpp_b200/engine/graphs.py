@@ -11,6 +11,14 @@ changes no result.  A graph holds raw addresses: it is keyed by the serial numbe
 cache it was recorded for (never by the object's identity, which a later cache can get
 again), it is not used once a scratch buffer it reads is reallocated
 (``Runtime.generation``), and it is dropped when its cache dies.
+
+One step ahead: between two decode steps the device would wait for the host to lay out the next index
+block (about 80 us at batch 8, of a step of 1.8 ms).  So, right after a step is launched, the next one is
+laid out as if the same sequences went on — positions reserved ahead in the cache, lengths and page tables
+patched — while the device computes; when the caller comes back with exactly those sequences, only their
+tokens are filled in and the block is uploaded.  If another step comes instead (a sequence ended, a prompt
+in between), the reservation is taken back (``SequenceCache.settle``) and the step is planned the ordinary
+way.  ``LLMI_AHEAD=0`` switches it off.
 """
 from __future__ import annotations
 
@@ -21,6 +29,8 @@ import torch
 
 # LLMI_GRAPHS=0 runs every decode step launch by launch (for profilers that want single kernels).
 RECORD = os.environ.get("LLMI_GRAPHS", "1") != "0"
+# LLMI_AHEAD=0: never lay the next decode step out ahead of its tokens.
+AHEAD = os.environ.get("LLMI_AHEAD", "1") != "0"
 
 
 def bucket(n: int) -> int:
@@ -44,6 +54,8 @@ class DecodeGraphs:
         self.kernels_per_graph = {}
         self._last = None        # (weak cache, page bucket, context, buffer identity) of the step before
         self._watched = set()    # serials of the caches whose death drops their graphs
+        self._pending = None     # (weak cache, page bucket, context, PendingStep, buffer identity): the next step, laid out ahead
+        self.ahead_used = 0      # steps that were laid out ahead and then came
 
     def _drop_cache(self, serial: int) -> None:
         for key in [k for k in self.graphs if k[3] == serial]:
@@ -60,12 +72,23 @@ class DecodeGraphs:
     def step(self, cache, seqs, sampler, streams=None):
         """A decode step (one token per sequence) followed by the choice; returns device int32 ids
         of the real sequences (valid until the next step)."""
-        from .batch import continue_decode_step, plan_step
+        from .batch import continue_decode_step, finish_continue, plan_step
         m = self.model
         n_real = len(seqs)
         B = bucket(n_real)
         ctx = None
-        last = self._last
+        pend, self._pending = self._pending, None
+        if pend is not None:
+            p_cache, P, p_ctx, p_step, p_ident = pend
+            if (p_cache() is cache and p_ctx.layout.slots == tuple(s.slot for s in seqs) and cache.slots.all_live(p_ctx.layout.slots)
+                    and p_ident == (m.rt.generation, m.buffers.dev.data_ptr(), m.buffers.serial)):
+                # the step that was laid out ahead has come: its tokens, one upload
+                finish_continue(cache, p_ctx, p_step, [s.tokens[0] for s in seqs], m.spec.vocab_size, m.buffers)
+                ctx = p_ctx
+                self.ahead_used += 1
+            elif p_cache() is not None:
+                p_cache().settle()
+        last = self._last if ctx is None else None
         if last is not None:
             l_cache, P, l_ctx, l_ident = last
             slots = l_ctx.layout.slots
@@ -111,6 +134,7 @@ class DecodeGraphs:
                 self.kernels_per_graph[key] = kernels.launch_count() - before
                 kernels.launch_count(-(kernels.launch_count() - before))   # recording launches nothing
                 self.graphs[key] = (g, rec_ids, rec_logits)
+            self._lay_out_next(cache, ctx, P)
             return ids[:n_real]
         g, rec_ids, rec_logits = entry
         g.replay()
@@ -118,4 +142,21 @@ class DecodeGraphs:
         self.replays += 1
         from ..ops import kernels
         kernels.launch_count(self.kernels_per_graph[key])
+        self._lay_out_next(cache, ctx, P)
         return rec_ids[:n_real]
+
+    def _lay_out_next(self, cache, ctx, P) -> None:
+        """While the device runs the step just launched: the next step's block, as if the same sequences went on."""
+        if not AHEAD or not cache.can_speculate():
+            return
+        from ..cache.pages import CacheError
+        from .batch import prepare_continue
+        slots = ctx.layout.slots
+        if (max(cache.length(s) for s in slots) + cache.page_size) // cache.page_size > P:
+            return                              # the page tables would outgrow this shape: the next step is planned anew
+        m = self.model
+        try:
+            step = prepare_continue(cache, ctx, m.buffers)
+        except CacheError:
+            return                              # no room (or the context's end): whatever comes next will say so
+        self._pending = (weakref.ref(cache), P, ctx, step, (m.rt.generation, m.buffers.dev.data_ptr(), m.buffers.serial))

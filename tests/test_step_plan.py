@@ -183,3 +183,95 @@ def test_a_window_gives_back_a_long_prompts_dead_pages_at_the_next_step():
             plan_step(cache, [SequenceStep(a, [3], [0])], 50, buf)
         assert pool.n_free == 4 and cache.length(a) == 302
         cache.check()
+
+
+def snapshot(cache):
+    g = cache.kv_groups[0].pool
+    return (sorted(g._free), {s: list(t) for s, t in g._pages.items()}, dict(g._length), dict(cache._length),
+            g.matrix.copy().tolist())
+
+
+def test_a_step_laid_out_ahead_equals_planning_anew_and_can_be_taken_back():
+    """prepare_continue / finish_continue (the next decode step's block made while the device still runs this one)
+    against plan_step, over page ends; a reservation that is not used leaves no trace, whatever happens meanwhile."""
+    from llmi_b200.engine.batch import finish_continue, prepare_continue
+    rng = np.random.default_rng(1)
+    starts = [60, 127, 3, 190]
+    caches, bufs, slots = [make_cache(), make_cache()], [HostBuffers(), HostBuffers()], []
+    for c, b in zip(caches, bufs):
+        ss = [c.alloc_slot() for _ in starts]
+        plan_step(c, [SequenceStep(s, [1] * n, []) for s, n in zip(ss, starts)], 50, b)
+        slots.append(ss)
+    prev = None
+    for step in range(140):
+        toks = rng.integers(0, 50, len(starts)).tolist()
+        ref = plan_step(caches[0], [SequenceStep(s, [t], [0]) for s, t in zip(slots[0], toks)], 50, bufs[0], pad_seqs_to=4, pad_pages_to=8)
+        if prev is None:
+            prev = plan_step(caches[1], [SequenceStep(s, [t], [0]) for s, t in zip(slots[1], toks)], 50, bufs[1], pad_seqs_to=4, pad_pages_to=8)
+        else:
+            before = snapshot(caches[1])
+            lens = [caches[1].length(s) for s in slots[1]]
+            pending = prepare_continue(caches[1], prev, bufs[1])
+            assert [caches[1].length(s) for s in slots[1]] == lens        # a reservation does not count as length
+            if step % 7 == 3:                          # now and then something else comes first: the reservation goes back
+                caches[1].settle()                     # and the step is planned the ordinary way
+                assert snapshot(caches[1]) == before
+                prev = plan_step(caches[1], [SequenceStep(s, [t], [0]) for s, t in zip(slots[1], toks)], 50, bufs[1],
+                                 pad_seqs_to=4, pad_pages_to=8)
+            else:
+                finish_continue(caches[1], prev, pending, toks, 50, bufs[1])
+            assert [caches[1].length(s) for s in slots[1]] == [n + 1 for n in lens]
+        n = ref.layout.n_int32
+        assert bufs[0].dev[:n].tolist() == bufs[1].dev[:n].tolist(), step
+        assert prev.max_kv_len == ref.max_kv_len
+        caches[1].check()
+
+
+def test_reservations_ahead_and_everything_else_that_touches_the_cache():
+    from llmi_b200.engine.batch import finish_continue, prepare_continue
+    cache = make_cache(max_tokens=64 * 4, n_slots=4)
+    a, b = cache.alloc_slot(), cache.alloc_slot()
+    buf = HostBuffers()
+    plan_step(cache, [SequenceStep(a, [1] * 63, []), SequenceStep(b, [1] * 64, [])], 50, buf)
+    ctx = plan_step(cache, [SequenceStep(a, [1], [0]), SequenceStep(b, [1], [0])], 50, buf, pad_seqs_to=2, pad_pages_to=4)
+    pool = cache.kv_groups[0].pool
+    assert pool.n_free == 1                               # a: 1 page (64 positions), b: 2 pages
+    # the next step ahead: a opens its second page
+    before = snapshot(cache)
+    prepare_continue(cache, ctx, buf)
+    assert pool.n_free == 0 and cache.length(a) == 64 and cache.length(b) == 65
+    # a sequence ends instead: its slot is freed with the reservation; the other's reservation goes back on the next touch
+    cache.free_slot(a)
+    assert cache.length(b) == 65
+    c = cache.alloc_slot()                                # settles
+    assert pool.n_free == 2 and pool.length(b) == 65 and cache.length(b) == 65
+    cache.check()
+    # a prompt in between (plan_step) takes the reservation back before it reserves its own room
+    ctx = plan_step(cache, [SequenceStep(b, [1], [0])], 50, buf, pad_seqs_to=1, pad_pages_to=4)
+    prepare_continue(cache, ctx, buf)
+    plan_step(cache, [SequenceStep(c, [1] * 128, [])], 50, buf)       # would not fit if b's reservation... it does fit: 2 pages free
+    assert cache.length(b) == 66 and cache.length(c) == 128 and pool.n_free == 0
+    # no room for a reservation: refused, nothing changes; a bad token takes the reservation back
+    ctx = plan_step(cache, [SequenceStep(b, [1], [0])], 50, buf, pad_seqs_to=1, pad_pages_to=4)
+    for _ in range(60):
+        pending = prepare_continue(cache, ctx, buf)
+        finish_continue(cache, ctx, pending, [1], 50, buf)
+    assert cache.length(b) == 127
+    pending = prepare_continue(cache, ctx, buf)
+    with pytest.raises(StepError, match="out of range"):
+        finish_continue(cache, ctx, pending, [50], 50, buf)
+    assert cache.length(b) == 127 and pool.length(b) == 127
+    pending = prepare_continue(cache, ctx, buf)
+    finish_continue(cache, ctx, pending, [2], 50, buf)
+    before = snapshot(cache)
+    with pytest.raises(CacheError, match="full"):          # position 128 needs a page and none is free
+        prepare_continue(cache, ctx, buf)
+    assert snapshot(cache) == before
+    cache.check()
+    # a windowed group cannot reserve ahead
+    w = make_cache(window=100)
+    s = w.alloc_slot()
+    ctx = plan_step(w, [SequenceStep(s, [1], [0])], 50, buf, pad_seqs_to=1, pad_pages_to=4)
+    assert not w.can_speculate()
+    with pytest.raises(CacheError, match="windowed"):
+        prepare_continue(w, ctx, buf)
