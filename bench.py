@@ -245,6 +245,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --only prefill: another prompt length")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print its numbers (for profiling one kernel class; not a bench line)")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
@@ -285,13 +286,19 @@ def main():
     weight_bytes = model.weight_bytes()
 
     if args.only == "prefill":
-        pre_ms = prefill_run(model, PREFILL_TOKENS, iters=3)
-        print(json.dumps({"only": "prefill", "ms": round(pre_ms, 3), "tokens": PREFILL_TOKENS, "layers": args.layers}))
+        T = args.prefill_tokens
+        pre_ms = prefill_run(model, T, iters=3)
+        frac = prefill_flops(cfg, args.layers, T) / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
+        print(json.dumps({"only": "prefill", "ms": round(pre_ms, 3), "tokens": T, "layers": args.layers,
+                          "tokens_per_s": round(T * 1000.0 / pre_ms, 1), "frac_of_bf16_peak": round(frac, 4), "peaks": pk_kind}))
         return 0
     if args.only == "decode":
-        ms, launches, *_ = decode_run(model, args.batch, args.context, steps, warmup)
-        print(json.dumps({"only": "decode", "ms_per_step": round(ms, 4), "batch": args.batch, "layers": args.layers,
-                          "kv_heads": cfg["num_key_value_heads"], "gpu_launches": launches}))
+        ms, launches, _, _, cache_bytes = decode_run(model, args.batch, args.context, steps, warmup)
+        gbs = (weight_bytes + cache_bytes) / (ms * 1e-3) / 1e9
+        print(json.dumps({"only": "decode", "ms_per_step": round(ms, 4), "batch": args.batch, "context": args.context,
+                          "layers": args.layers, "kv_heads": cfg["num_key_value_heads"], "gpu_launches": launches,
+                          "tokens_per_s": round(args.batch * 1000.0 / ms, 1), "gb_per_s": round(gbs, 1),
+                          "frac_of_hbm_peak": round(gbs / pk["hbm_gbs"], 4), "peaks": pk_kind}))
         return 0
 
     clocks = ClockSampler()
