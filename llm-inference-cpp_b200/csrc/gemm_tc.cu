@@ -579,6 +579,63 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
   return v;
 }
 
+// Part 2 of the cluster kernels' epilogue, run by NT threads (whole warps; `te` = 0..NT-1): rows rank*128/S .. of the
+// tile, added over the cluster's S partial tiles in rank order through distributed shared memory, and their epilogue.
+// A thread asks for everything it adds — BN*128/NT values, 16-byte loads — before it uses any of it: the loads are
+// round trips to other SMs, and a thread that waited for each batch before the next spent 8 to 11 us on a tile of
+// 128 tokens (more than the product's whole k loop).
+template <int BN, int RED_STRIDE, int NT, int S>
+__device__ __forceinline__ void ks_reduce_and_store_s(const TcParams& p, uint32_t base, int rank, int mt, int nt, int te) {
+  constexpr int ROWS_PER = TC_BM / S;
+  constexpr int GROUPS = NT / ROWS_PER;         // groups of columns (tokens)
+  constexpr int CPT = BN / GROUPS;              // columns per thread
+  static_assert(CPT >= 4 && CPT % 4 == 0, "a thread takes whole 16-byte pieces");
+  constexpr int NQ = CPT / 4;
+  const int row = rank * ROWS_PER + te % ROWS_PER;
+  const int cg = te / ROWS_PER;
+  const int m = mt * TC_BM + row;
+  const uint32_t my_addr = base + (uint32_t)(row * RED_STRIDE + cg * CPT) * 4u;
+  float4 t[NQ][S];
+#pragma unroll
+  for (int q = 0; q < NQ; ++q)
+#pragma unroll
+    for (int r = 0; r < S; ++r) {
+      const uint32_t addr = my_addr + (uint32_t)(4 * q) * 4u;
+      if (S == 1) asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(t[q][r].x), "=f"(t[q][r].y), "=f"(t[q][r].z), "=f"(t[q][r].w) : "r"(addr));
+      else t[q][r] = ld_cluster_f4(map_to_rank(addr, (uint32_t)r));
+    }
+  constexpr int CHUNKS = (CPT + 15) / 16;
+#pragma unroll
+  for (int ch = 0; ch < CHUNKS; ++ch) {
+    float v[16];
+#pragma unroll
+    for (int c = 0; c < 16; ++c) v[c] = 0.f;
+#pragma unroll
+    for (int qq = 0; qq < 4; ++qq) {
+      const int q = ch * 4 + qq;
+      if (q < NQ) {
+#pragma unroll
+        for (int r = 0; r < S; ++r) {      // rank order
+          v[4 * qq] += t[q][r].x;
+          v[4 * qq + 1] += t[q][r].y;
+          v[4 * qq + 2] += t[q][r].z;
+          v[4 * qq + 3] += t[q][r].w;
+        }
+      }
+    }
+    const int n_base = nt * BN + cg * CPT + ch * 16;
+    const int width = CPT - ch * 16 < 16 ? CPT - ch * 16 : 16;
+    tc_epilogue_store<BN>(p, v, m, n_base, min(width, p.n_tok - n_base));
+  }
+}
+template <int BN, int RED_STRIDE, int NT>
+__device__ __forceinline__ void ks_reduce_and_store(const TcParams& p, uint32_t base, int rank, int S, int mt, int nt, int te) {
+  if (S == 1) ks_reduce_and_store_s<BN, RED_STRIDE, NT, 1>(p, base, rank, mt, nt, te);
+  else if (S == 2) ks_reduce_and_store_s<BN, RED_STRIDE, NT, 2>(p, base, rank, mt, nt, te);
+  else if (S == 4) ks_reduce_and_store_s<BN, RED_STRIDE, NT, 4>(p, base, rank, mt, nt, te);
+  else ks_reduce_and_store_s<BN, RED_STRIDE, NT, 8>(p, base, rank, mt, nt, te);
+}
+
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_ksplit_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p,
@@ -691,51 +748,326 @@ gemm_tc_ksplit_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 
-  if (warp >= 2) {
-    // ---- part 2: rows rank*128/S .. of the tile, added over the cluster in rank order, and their epilogue ----
-    const int te = threadIdx.x - 64;
-    const int rows_per = TC_BM / S;
-    const int row = rank * rows_per + te % rows_per;
-    const int cg = te / rows_per;            // 0..S-1: this thread's group of columns (tokens)
-    const int cpt = BN / S;                  // columns per thread: a multiple of 4
-    const int m = mt * TC_BM + row;
-    const uint32_t my_addr = base + (uint32_t)(row * C::RED_STRIDE + cg * cpt) * 4u;
-    for (int c0 = 0; c0 < cpt; c0 += 16) {
-      const int width = min(16, cpt - c0);
-      float v[16];
+  if (warp >= 2) ks_reduce_and_store<BN, C::RED_STRIDE, 128>(p, base, rank, S, mt, nt, threadIdx.x - 64);
+  // nobody leaves while a peer may still read its shared memory
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(C::TMEM_COLS));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The cluster kernel with WIDE stages, for products whose output tiles are fewer than the SMs.
+//
+// A thread that issues a tensor copy is busy with it for about half a microsecond whatever its size up to 32 KB, and
+// one thread's copies do not overlap (a block alone on its SM whose one producer thread requests 16 KB tiles takes in
+// 30 GB/s whatever the depth of its ring; with 32 KB tiles 45 to 50, with 64 KB tiles up to 108 when few blocks run;
+// two threads that take the stages in turn: 43 to 49 GB/s with 16 KB tiles).  Here a stage holds TWO 64-wide k blocks
+// of both operands, each fetched by ONE copy of a three-dimensional box (k within a block, row, k block), and four
+// threads in four warps issue the copies: two take the weight boxes of the stages in turn, two the token boxes.  One
+// block per SM with a ring of about 190 KB.
+//
+// The way out.  Loads from another CTA's shared memory by threads are slow (a CTA that read 48 KB of its three
+// peers' partial tiles with 16-byte loads, all in flight at once, took 5.4 us: 9 GB/s), and so are stores of 2 or 4
+// bytes a lane while the next kernel's weight tiles queue at the memory.  So:
+//   1. every CTA leaves its partial tile P [128 rows][BN tokens] fp32 in its own shared memory (over the ring);
+//   2. after a cluster barrier one thread per peer sends that peer's rows of P by a bulk copy (shared memory to the
+//      peer's shared memory, completion on the peer's mbarrier) into the slot R[sender] there;
+//   3. the CTA of rank r adds rows r*128/S.. of P and of the R slots in rank order — local reads only —, applies the
+//      epilogue and lays the result out token-major in a staging tile;
+//   4. one thread stores (or, for the residual stream, adds) the staging tile by TMA.
+// Outputs whose base or pitch is not a multiple of 16 bytes take the stores of the threads instead of step 4.
+template <int BN>
+struct WideConfig {
+  static constexpr int KBS = 2;                                  // 64-wide k blocks per stage
+  static constexpr int A_KB = TC_BM * TC_BK * 2;                 // one k block of the weight tile: 16 KB
+  static constexpr int B_KB = BN * TC_BK * 2;
+  static constexpr int A_BYTES = KBS * A_KB, B_BYTES = KBS * B_KB;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = BN == 128 ? 3 : 4;
+  static constexpr int RED_STRIDE = BN + 4;                      // floats per row of P (16-byte skew: no bank conflicts)
+  static constexpr int RED_BYTES = TC_BM * RED_STRIDE * 4;       // P; the S slots of R together are as large
+  static constexpr int STAGING_BYTES = BN * TC_BM * 4;           // at most (one CTA of a cluster of S fills 1/S of it)
+  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+  // cluster of one: P, staging; larger: P, R, staging / 2 at most
+  static constexpr int OUT_BYTES_1 = RED_BYTES + STAGING_BYTES, OUT_BYTES_S = 2 * RED_BYTES + STAGING_BYTES / 2;
+  static constexpr int OUT_BYTES = OUT_BYTES_1 > OUT_BYTES_S ? OUT_BYTES_1 : OUT_BYTES_S;
+  static constexpr int DATA_BYTES = RING_BYTES > OUT_BYTES ? RING_BYTES : OUT_BYTES;
+  static constexpr int SMEM_BYTES = DATA_BYTES + 1024 + 8 * (2 * STAGES + 3) + 16;
+  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+};
+constexpr int TW_THREADS = 288;     // warp 0, 6: weight producers; 1: MMA; 2..5: epilogue; 7, 8: token producers
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+// this CTA's shared memory to a peer's (both addresses 16-byte aligned, bytes a multiple of 16); completes on the peer's barrier
+__device__ __forceinline__ void bulk_send(uint32_t dst_cluster, uint32_t src, uint32_t bytes, uint32_t bar_cluster) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_cluster), "r"(src), "r"(bytes), "r"(bar_cluster)
+               : "memory");
+}
+
+// Steps 3 and 4 for a cluster of S, run by NT threads (whole warps, te = 0..NT-1, named barrier 2).
+template <int BN, int NT, int S>
+__device__ __forceinline__ void wide_way_out(const TcParams& p, const CUtensorMap* map_out, int out_tma, uint32_t base, uint8_t* smem_base,
+                                             int rank, int mt, int nt, int te) {   // smem_base: the generic address of `base`
+  using C = WideConfig<BN>;
+  constexpr int RP = TC_BM / S;                 // rows of this CTA
+  constexpr int GROUPS = NT / RP;               // groups of columns (tokens)
+  constexpr int CPT = BN / GROUPS;              // columns per thread
+  static_assert(CPT >= 4 && CPT % 4 == 0, "a thread takes whole 16-byte pieces");
+  constexpr int NQ = CPT / 4;
+  constexpr uint32_t SLICE_BYTES = RP * C::RED_STRIDE * 4;
+  const int row = te % RP, cg = te / RP;
+  const int m = mt * TC_BM + rank * RP + row;
+  // own rows of P and of the slots, the own slot excepted (nobody sends to itself)
+  float v[CPT];
 #pragma unroll
-      for (int c = 0; c < 16; ++c) v[c] = 0.f;
-      // eight 16-byte loads over the cluster are in flight at a time (a dependent add after every load would
-      // make each of them a round trip of its own); the additions are in rank order
-      const int nq = width / 4, qb = 8 / S;               // quads of columns in this chunk; quads per batch
-      for (int q0 = 0; q0 < nq; q0 += qb) {
-        float4 t[8];
+  for (int c = 0; c < CPT; ++c) v[c] = 0.f;
+  {
+    float4 t[NQ][S];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int pr = j % S, q = q0 + j / S;          // S is 1, 2, 4 or 8
-          if (j < S * qb && q < nq) t[j] = ld_cluster_f4(map_to_rank(my_addr + (uint32_t)(c0 + 4 * q) * 4u, (uint32_t)pr));
-          else t[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+    for (int r = 0; r < S; ++r) {
+      const uint32_t src = r == rank ? base + (uint32_t)(rank * RP) * (C::RED_STRIDE * 4) : base + C::RED_BYTES + (uint32_t)r * SLICE_BYTES;
+      const uint32_t addr = src + (uint32_t)(row * C::RED_STRIDE + cg * CPT) * 4u;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int q = q0 + j / S;
-          if (j < S * qb && q < nq) {
+      for (int q = 0; q < NQ; ++q)
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(t[q][r].x), "=f"(t[q][r].y), "=f"(t[q][r].z), "=f"(t[q][r].w) : "r"(addr + 16u * q));
+    }
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              // v is indexed with compile-time constants only after full unrolling of the chunk: 4 quads
+    for (int q = 0; q < NQ; ++q)
 #pragma unroll
-              for (int qq = 0; qq < 4; ++qq)
-                if (qq == q) v[4 * qq + e] += (e == 0 ? t[j].x : e == 1 ? t[j].y : e == 2 ? t[j].z : t[j].w);
-            }
+      for (int r = 0; r < S; ++r) {      // rank order
+        v[4 * q] += t[q][r].x;
+        v[4 * q + 1] += t[q][r].y;
+        v[4 * q + 2] += t[q][r].z;
+        v[4 * q + 3] += t[q][r].w;
+      }
+  }
+  const int n_base = nt * BN + cg * CPT;
+  if (!out_tma) {
+#pragma unroll
+    for (int ch = 0; ch < (CPT + 15) / 16; ++ch) {
+      float w[16];
+#pragma unroll
+      for (int c = 0; c < 16; ++c) w[c] = ch * 16 + c < CPT ? v[ch * 16 + c] : 0.f;
+      const int width = CPT - ch * 16 < 16 ? CPT - ch * 16 : 16;
+      tc_epilogue_store<BN>(p, w, m, n_base + ch * 16, min(width, p.n_tok - (n_base + ch * 16)));
+    }
+    return;
+  }
+  // the staging tile: [BN tokens][RP rows] (gated: [BN][RP / 2] features), dense.  Plain stores, all values first: a
+  // chain of exchange, exponential, division and store per token, each waiting for the one before, cost 5 us a tile.
+  const uint32_t staging_off = S == 1 ? C::RED_BYTES : 2 * C::RED_BYTES;
+  const uint32_t staging = base + staging_off;
+  uint8_t* const stg = smem_base + staging_off;
+  if (p.mode == OUT_SWIGLU) {
+    // rows alternate gate and up (src/model/transformer.cpp:290; src/model/kernels.cpp:148): the even lane takes the
+    // odd lane's up and finishes feature row / 2
+    __nv_bfloat16* o = (__nv_bfloat16*)stg + (size_t)(cg * CPT) * (RP / 2) + (row >> 1);
+    float up[CPT];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) up[c] = __shfl_down_sync(0xffffffffu, v[c], 1);
+    if (!(row & 1)) {
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) o[c * (RP / 2)] = __float2bfloat16_rn(__fdividef(v[c], 1.0f + __expf(-v[c])) * up[c]);
+    }
+  } else {
+    const float b = (p.bias && m < p.m_out) ? p.bias[m] : 0.f;
+    if (p.mode == OUT_STORE) {
+      __nv_bfloat16* o = (__nv_bfloat16*)stg + (size_t)(cg * CPT) * RP + row;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) o[c * RP] = __float2bfloat16_rn(v[c] + b);
+    } else {
+      float* o = (float*)stg + (size_t)(cg * CPT) * RP + row;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) o[c * RP] = v[c] + b;
+    }
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the staging tile is read by the async proxy
+  asm volatile("bar.sync 2, %0;" ::"n"(NT) : "memory");
+  if (te == 0) {
+    const int m0 = mt * TC_BM + rank * RP;
+    const int c0 = p.mode == OUT_SWIGLU ? (m0 >> 1) : m0, c1 = nt * BN;
+    if (p.mode == OUT_ADD_F32)
+      asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                   ::"l"(map_out), "r"(c0), "r"(c1), "r"(staging) : "memory");
+    else
+      asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                   ::"l"(map_out), "r"(c0), "r"(c1), "r"(staging) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the staging tile has been read: the block may end
+  }
+}
+
+// boxed3d: the operand maps are three-dimensional (k a multiple of 64); else two-dimensional, one copy per k block.
+// out_tma: map_out describes the output for step 4 (box [BN tokens][128 / S rows], gated: half the rows).
+template <int BN>
+__global__ void __launch_bounds__(TW_THREADS)
+gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    const __grid_constant__ CUtensorMap map_out, TcParams p, int m_tiles, int S, int boxed3d,
+                    int out_tma) {   // gridDim.x = tiles * S, cluster (S, 1, 1); S in {1, 2, 4}
+  using C = WideConfig<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* const smem_base = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + C::DATA_BYTES;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+  const uint32_t acc_full = bars + 8u * (2 * C::STAGES);
+  const uint32_t recv_bar = bars + 8u * (2 * C::STAGES + 1);
+  const uint32_t tmem_slot = bars + 8u * (2 * C::STAGES + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = (int)cluster_rank();
+  const int tile = blockIdx.x / S;
+  const int mt = tile % m_tiles, nt = tile / m_tiles;
+  const int kblocks = (p.k + TC_BK - 1) / TC_BK;
+  const int per = (kblocks + S - 1) / S;
+  const int kb0 = rank * per;
+  const int nkb = max(0, min(kblocks, kb0 + per) - kb0);
+  const int nst = (nkb + C::KBS - 1) / C::KBS;          // stages; the last one may hold one k block that counts
+  const uint32_t slice_bytes = (uint32_t)(TC_BM / S) * (C::RED_STRIDE * 4);
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    if (out_tma) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_out) : "memory");
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(recv_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (S > 1) mbar_expect_tx(recv_bar, (uint32_t)(S - 1) * slice_bytes);    // what the peers will send, long before they do
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(C::TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  uint32_t tmem_d;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_d) : "r"(tmem_slot));
+
+  pdl_launch_dependents();
+  if (warp == 0 || warp >= 6) {
+    if (lane == 0) {
+      // ---- producers.  The weights do not depend on the kernel before, the tokens do.  A stage's full barrier is in
+      // its new phase once its empty barrier has completed, so token bytes that land before the weight producer has
+      // announced the stage still count for the right phase.
+      const bool tokens = warp >= 7;
+      const int me = tokens ? warp - 7 : (warp == 0 ? 0 : 1);
+      if (tokens) pdl_wait();
+      for (int i = me; i < nst; i += 2) {
+        const int s = i % C::STAGES;
+        if (i >= C::STAGES && !mbar_wait(empty_bar(s), ((i / C::STAGES) - 1) & 1, p.error_flag, tokens ? 26 : 21)) break;
+        const int kb = kb0 + i * C::KBS;           // (a k block past this CTA's range is fetched and not multiplied)
+        const uint32_t dst = base + s * C::STAGE_BYTES + (tokens ? C::A_BYTES : 0);
+        if (!tokens) mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+        if (boxed3d) {
+          if (tokens) tma_load_3d(dst, &map_x, 0, nt * BN, kb, full_bar(s));
+          else tma_load_3d(dst, &map_w, 0, mt * TC_BM, kb, full_bar(s));
+        } else {
+#pragma unroll
+          for (int j = 0; j < C::KBS; ++j) {
+            if (tokens) tma_load_2d(dst + j * C::B_KB, &map_x, (kb + j) * TC_BK, nt * BN, full_bar(s));
+            else tma_load_2d(dst + j * C::A_KB, &map_w, (kb + j) * TC_BK, mt * TC_BM, full_bar(s));
           }
         }
       }
-      const int n_base = nt * BN + cg * cpt + c0;
-      tc_epilogue_store<BN>(p, v, m, n_base, min(width, p.n_tok - n_base));
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer ----
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+      bool ok = true;
+      for (int i = 0; i < nst; ++i) {
+        const int s = i % C::STAGES;
+        ok = mbar_wait(full_bar(s), (i / C::STAGES) & 1, p.error_flag, 22);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = base + s * C::STAGE_BYTES;
+        const int nk = min(C::KBS, nkb - i * C::KBS);
+        for (int j = 0; j < nk; ++j) {
+          const uint64_t a_desc = umma_desc(a_addr + j * C::A_KB), b_desc = umma_desc(a_addr + C::A_BYTES + j * C::B_KB);
+#pragma unroll
+          for (int k4 = 0; k4 < TC_BK / 16; ++k4)
+            umma_bf16(tmem_d, a_desc + 2 * k4, b_desc + 2 * k4, idesc, (i > 0 || j > 0 || k4 > 0) ? 1u : 0u);
+        }
+        umma_commit(empty_bar(s));
+      }
+      if (nkb > 0 && ok) umma_commit(acc_full);   // arrives when every product above has finished
+      else mbar_arrive(acc_full);
+    }
+  } else {
+    // ---- epilogue warps (2..5), step 1: this CTA's partial tile into its own shared memory (over the ring) ----
+    const int quad = warp & 3;
+    pdl_wait();
+    mbar_wait(acc_full, 0, p.error_flag, 23);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t row_addr = base + (uint32_t)((quad * 32 + lane) * C::RED_STRIDE) * 4u;
+    const uint32_t t_base = tmem_d + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 16) {
+      float v[16];
+      if (nkb > 0) tmem_ld16(t_base + c0, v);
+      else {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) v[c] = 0.f;
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (uint32_t)(c0 + 4 * q) * 4u), "f"(v[4 * q]),
+                     "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3])
+                     : "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // P is read by the bulk copies below
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  bool received = true;
+  if (S > 1) {
+    // every CTA's partial tile is in place and its ring is free
+    cluster_sync_all();
+    // ---- step 2: one thread per peer sends that peer's rows ----
+    if (lane == 0 && warp >= 1 && warp <= S && warp - 1 != rank) {
+      const uint32_t peer = (uint32_t)(warp - 1);
+      bulk_send(map_to_rank(base + C::RED_BYTES + (uint32_t)rank * slice_bytes, peer), base + peer * slice_bytes, slice_bytes,
+                map_to_rank(recv_bar, peer));
+    }
+    received = mbar_wait(recv_bar, 0, p.error_flag, 27);
+    // Nobody may leave while a copy that it sent still reads its shared memory: every peer says here that it has
+    // received, and the wait is at the end, behind the way out.
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  } else {
+    __syncthreads();
+  }
+  // ---- steps 3 and 4 (the producer and MMA warps have nothing left to do: all but warp 0 help where the tile is wide enough)
+  if (received) {
+    if constexpr (BN >= 64) {
+      if (warp >= 1) {
+        const int te = threadIdx.x - 32;
+        if (S == 1) wide_way_out<BN, 256, 1>(p, &map_out, out_tma, base, smem_base, rank, mt, nt, te);
+        else if (S == 2) wide_way_out<BN, 256, 2>(p, &map_out, out_tma, base, smem_base, rank, mt, nt, te);
+        else wide_way_out<BN, 256, 4>(p, &map_out, out_tma, base, smem_base, rank, mt, nt, te);
+      }
+    } else {
+      if (warp >= 2 && warp < 6) {
+        const int te = threadIdx.x - 64;
+        if (S == 1) wide_way_out<BN, 128, 1>(p, &map_out, out_tma, base, smem_base, rank, mt, nt, te);
+        else if (S == 2) wide_way_out<BN, 128, 2>(p, &map_out, out_tma, base, smem_base, rank, mt, nt, te);
+        else wide_way_out<BN, 128, 4>(p, &map_out, out_tma, base, smem_base, rank, mt, nt, te);
+      }
     }
   }
-  // nobody leaves while a peer may still read its shared memory
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (S > 1) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  else __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(C::TMEM_COLS));
   }
@@ -788,6 +1120,36 @@ static int launch_tc_ksplit(const CUtensorMap& mw, const CUtensorMap& mx, TcPara
   return cudaLaunchKernelEx(&cfg, gemm_tc_ksplit_kernel<BN>, mw, mx, p, m_tiles, S) == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH;
 }
 
+template <int BN>
+static int launch_tc_wide(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, TcParams p, int m_tiles, int n_tiles,
+                          int S, int boxed3d, int out_tma, cudaStream_t stream) {
+  using C = WideConfig<BN>;
+  static PerDevice<bool> configured_on;
+  bool& configured = configured_on.here();
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tc_wide_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+      return LLMI_ERR_LAUNCH;
+    configured = true;
+  }
+  const long tiles = (long)m_tiles * n_tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(tiles * S));
+  cfg.blockDim = dim3(TW_THREADS);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled(PDL_GEMM) ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return cudaLaunchKernelEx(&cfg, gemm_tc_wide_kernel<BN>, mw, mx, mo, p, m_tiles, S, boxed3d, out_tma) == cudaSuccess ? LLMI_OK
+                                                                                                               : LLMI_ERR_LAUNCH;
+}
+
 // ------------------------------------------------------------------------------------------- host
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -817,6 +1179,20 @@ static int make_map(CUtensorMap* map, const void* ptr, long rows, long k, long l
   const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LLMI_OK : LLMI_ERR_DRIVER;
+}
+
+// The same matrix (k a multiple of 64) seen as (k within a 64-wide block, row, k block): boxes of [kbs][box_rows][64].
+static int make_map_3d(CUtensorMap* map, const void* ptr, long rows, long k, long ld, int box_rows, int kbs) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return LLMI_ERR_DRIVER;
+  const cuuint64_t dims[3] = {(cuuint64_t)TC_BK, (cuuint64_t)rows, (cuuint64_t)(k / TC_BK)};
+  const cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)TC_BK * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows, (cuuint32_t)kbs};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, elem,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? LLMI_OK : LLMI_ERR_DRIVER;
@@ -897,12 +1273,45 @@ static int tc_cluster_size(int n_tok, int m_out, int k) {
   return ksplit_cluster(tiles, (k + TC_BK - 1) / TC_BK, (long)sm_count() * per_sm, bn);
 }
 
+// The output of the wide-stage kernel as [n_tok][cols] of bf16 or fp32 with boxes of [box_tok tokens][box_cols]: the way
+// out by TMA.  LLMI_ERR_ALIGN if its base or pitch is not a multiple of 16 bytes (the caller then lets the threads store).
+static int make_wide_out_map(CUtensorMap* map, void* out, long n_tok, long cols, long ldo, int elem_bytes, int box_cols, int box_tok) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return LLMI_ERR_DRIVER;
+  if (((uintptr_t)out & 15) || ((ldo * elem_bytes) & 15) || ((box_cols * elem_bytes) & 15)) return LLMI_ERR_ALIGN;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)n_tok};
+  const cuuint64_t strides[1] = {(cuuint64_t)ldo * elem_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_tok};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, strides,
+                        box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? LLMI_OK : LLMI_ERR_DRIVER;
+}
+
+// The wide-stage cluster kernel takes the products of 17 to a few hundred tokens whose 128-row tiles are no more than the
+// SMs (one block per SM): its cluster size, 0 if the product is not its own.  (LLMI_TC_WIDE=0 switches it off.)
+static int tc_wide_cluster(int n_tok, int m_out, int k) {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("LLMI_TC_WIDE");
+    enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  const int bn = tc_bn(n_tok, m_out);
+  if (!enabled || bn < 32 || bn > 128) return 0;
+  const long tiles = (long)((m_out + TC_BM - 1) / TC_BM) * ((n_tok + bn - 1) / bn);
+  if (tiles > sm_count()) return 0;
+  // (one block per SM: clusters of eight have few places on the device, so four at most)
+  return ksplit_cluster(tiles, (k + TC_BK - 1) / TC_BK, sm_count(), 128);
+}
+
 // 64-wide k blocks that one CTA accumulates before partial sums are added across CTAs (the whole k range when
 // nothing is cut): two products of the same weights add in the same order exactly when this number agrees.
 LLMI_EXPORT int llmi_gemm_tc_k_per_cta(int n_tok, int m_out, int k) {
   const int kblocks = (k + TC_BK - 1) / TC_BK;
-  const int S = tc_cluster_size(n_tok, m_out, k);
-  const int cuts = S > 1 ? S : llmi_gemm_tc_splits(n_tok, m_out, k);
+  const int W = tc_wide_cluster(n_tok, m_out, k);
+  const int S = W ? W : tc_cluster_size(n_tok, m_out, k);
+  const int cuts = (W || S > 1) ? S : llmi_gemm_tc_splits(n_tok, m_out, k);
   return (kblocks + cuts - 1) / cuts;
 }
 
@@ -932,7 +1341,28 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
   int splits = llmi_gemm_tc_splits(n_tok, m_out, k);
   if (splits > 1 && (need_ws > workspace_bytes || need_tickets > n_tickets || !workspace || !tickets)) splits = 1;
   CUtensorMap mw, mx;
-  int rc = make_map(&mw, w, m_out, k, ldw, TC_BM);
+  int rc;
+  const int W = tc_wide_cluster(n_tok, m_out, k);
+  if (W) {
+    const int boxed3d = (k % TC_BK) == 0;
+    rc = boxed3d ? make_map_3d(&mw, w, m_out, k, ldw, TC_BM, 2) : make_map(&mw, w, m_out, k, ldw, TC_BM);
+    if (rc != LLMI_OK) return rc;
+    rc = boxed3d ? make_map_3d(&mx, x, n_tok, k, ldx, bn, 2) : make_map(&mx, x, n_tok, k, ldx, bn);
+    if (rc != LLMI_OK) return rc;
+    TcParams pk{m_out, n_tok, k, y, ldy, bias, mode, 1, nullptr, nullptr, error_flag};
+    const int m_tiles = (m_out + TC_BM - 1) / TC_BM, n_tiles = (n_tok + bn - 1) / bn;
+    // the way out by TMA: a CTA of a cluster of W stores [bn tokens][128 / W rows] (gated: half as many features)
+    CUtensorMap mo = mw;
+    const int gated = mode == OUT_SWIGLU;
+    const int out_rc = make_wide_out_map(&mo, y, n_tok, gated ? m_out / 2 : m_out, ldy, (mode == OUT_STORE || gated) ? 2 : 4,
+                                         (TC_BM / W) >> gated, bn);
+    if (out_rc == LLMI_ERR_DRIVER) return out_rc;
+    const int out_tma = out_rc == LLMI_OK;
+    if (bn == 32) return launch_tc_wide<32>(mw, mx, mo, pk, m_tiles, n_tiles, W, boxed3d, out_tma, stream);
+    if (bn == 64) return launch_tc_wide<64>(mw, mx, mo, pk, m_tiles, n_tiles, W, boxed3d, out_tma, stream);
+    return launch_tc_wide<128>(mw, mx, mo, pk, m_tiles, n_tiles, W, boxed3d, out_tma, stream);
+  }
+  rc = make_map(&mw, w, m_out, k, ldw, TC_BM);
   if (rc != LLMI_OK) return rc;
   // long prompts: pairs of SMs share a 256-token tile (each loads 128 of its rows)
   static int pair_ok = -1;

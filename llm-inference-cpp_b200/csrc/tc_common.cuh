@@ -94,14 +94,13 @@ __device__ __forceinline__ void tc_epilogue_store(const TcParams& p, float* v, i
   if (m >= p.m_out) return;
   const float b = p.bias ? p.bias[m] : 0.f;
   if (p.mode == OUT_ADD_F32) {
-    // read the 16 old values together (one round trip instead of sixteen), then add and store
-    float old[16];
+    // One-way additions at the L2 (a reduction, nothing comes back): nobody else adds to these elements during the
+    // launch, so the result is the one of read, add, store — without the read's round trip, which costs microseconds
+    // while the next kernel's weight tiles already queue at the memory.
     float* o = (float*)p.out + (size_t)n_base * p.ldo + m;
 #pragma unroll
-    for (int c = 0; c < 16; ++c) old[c] = c < n_valid ? o[(size_t)c * p.ldo] : 0.f;
-#pragma unroll
     for (int c = 0; c < 16; ++c)
-      if (c < n_valid) o[(size_t)c * p.ldo] = old[c] + (v[c] + b);
+      if (c < n_valid) asm volatile("red.global.add.f32 [%0], %1;" ::"l"(o + (size_t)c * p.ldo), "f"(v[c] + b) : "memory");
     return;
   }
 #pragma unroll
