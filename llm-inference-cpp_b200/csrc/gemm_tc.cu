@@ -549,215 +549,14 @@ static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CU
 }
 
 // ------------------------------------------------------------------------------------------------
-// The same product for a few dozen tokens (a decode step at batch 17..128) with the k range cut over the
-// CTAs of a CLUSTER.
+// The same product for 17 to a few hundred tokens with no more output tiles than SMs (a decode step at batch 17..128,
+// a short prompt): the k range is cut over the CTAs of a CLUSTER, and the stages are WIDE.
 //
-// Such a product is a read of W, and with 128-row tiles it has few of them (2048 output rows: 16 tiles), so
-// k must be cut for every SM to stream.  Through a workspace, the CTA that comes last adds all the partial
-// tiles alone (16 splits of a 128x64 tile: half a megabyte read by one CTA — the o and down projections took
-// 18 and 29 us at 64 tokens).  Here the S CTAs that share an output tile form a cluster: each leaves its
-// partial tile (TMEM -> registers -> its own shared memory), and after a cluster barrier CTA r adds rows
-// r*128/S.. of all S partial tiles through distributed shared memory, in rank order, and runs the epilogue
-// for those rows.  Every CTA reduces and stores 1/S of the tile; nothing goes through global memory.
-template <int BN>
-struct KsConfig {
-  static constexpr int A_BYTES = TC_BM * TC_BK * 2;
-  static constexpr int B_BYTES = BN * TC_BK * 2;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = 4;
-  static constexpr int RED_STRIDE = BN + 4;                        // floats per row of the partial tile (16-byte skew)
-  static constexpr int RED_BYTES = TC_BM * RED_STRIDE * 4;
-  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int DATA_BYTES = RING_BYTES > RED_BYTES ? RING_BYTES : RED_BYTES;   // the partial tile reuses the ring
-  static constexpr int SMEM_BYTES = DATA_BYTES + 1024 + 8 * (2 * STAGES + 1) + 16;
-  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
-};
-
-__device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
-  float4 v;
-  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr));
-  return v;
-}
-
-// Part 2 of the cluster kernels' epilogue, run by NT threads (whole warps; `te` = 0..NT-1): rows rank*128/S .. of the
-// tile, added over the cluster's S partial tiles in rank order through distributed shared memory, and their epilogue.
-// A thread asks for everything it adds — BN*128/NT values, 16-byte loads — before it uses any of it: the loads are
-// round trips to other SMs, and a thread that waited for each batch before the next spent 8 to 11 us on a tile of
-// 128 tokens (more than the product's whole k loop).
-template <int BN, int RED_STRIDE, int NT, int S>
-__device__ __forceinline__ void ks_reduce_and_store_s(const TcParams& p, uint32_t base, int rank, int mt, int nt, int te) {
-  constexpr int ROWS_PER = TC_BM / S;
-  constexpr int GROUPS = NT / ROWS_PER;         // groups of columns (tokens)
-  constexpr int CPT = BN / GROUPS;              // columns per thread
-  static_assert(CPT >= 4 && CPT % 4 == 0, "a thread takes whole 16-byte pieces");
-  constexpr int NQ = CPT / 4;
-  const int row = rank * ROWS_PER + te % ROWS_PER;
-  const int cg = te / ROWS_PER;
-  const int m = mt * TC_BM + row;
-  const uint32_t my_addr = base + (uint32_t)(row * RED_STRIDE + cg * CPT) * 4u;
-  float4 t[NQ][S];
-#pragma unroll
-  for (int q = 0; q < NQ; ++q)
-#pragma unroll
-    for (int r = 0; r < S; ++r) {
-      const uint32_t addr = my_addr + (uint32_t)(4 * q) * 4u;
-      if (S == 1) asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(t[q][r].x), "=f"(t[q][r].y), "=f"(t[q][r].z), "=f"(t[q][r].w) : "r"(addr));
-      else t[q][r] = ld_cluster_f4(map_to_rank(addr, (uint32_t)r));
-    }
-  constexpr int CHUNKS = (CPT + 15) / 16;
-#pragma unroll
-  for (int ch = 0; ch < CHUNKS; ++ch) {
-    float v[16];
-#pragma unroll
-    for (int c = 0; c < 16; ++c) v[c] = 0.f;
-#pragma unroll
-    for (int qq = 0; qq < 4; ++qq) {
-      const int q = ch * 4 + qq;
-      if (q < NQ) {
-#pragma unroll
-        for (int r = 0; r < S; ++r) {      // rank order
-          v[4 * qq] += t[q][r].x;
-          v[4 * qq + 1] += t[q][r].y;
-          v[4 * qq + 2] += t[q][r].z;
-          v[4 * qq + 3] += t[q][r].w;
-        }
-      }
-    }
-    const int n_base = nt * BN + cg * CPT + ch * 16;
-    const int width = CPT - ch * 16 < 16 ? CPT - ch * 16 : 16;
-    tc_epilogue_store<BN>(p, v, m, n_base, min(width, p.n_tok - n_base));
-  }
-}
-template <int BN, int RED_STRIDE, int NT>
-__device__ __forceinline__ void ks_reduce_and_store(const TcParams& p, uint32_t base, int rank, int S, int mt, int nt, int te) {
-  if (S == 1) ks_reduce_and_store_s<BN, RED_STRIDE, NT, 1>(p, base, rank, mt, nt, te);
-  else if (S == 2) ks_reduce_and_store_s<BN, RED_STRIDE, NT, 2>(p, base, rank, mt, nt, te);
-  else if (S == 4) ks_reduce_and_store_s<BN, RED_STRIDE, NT, 4>(p, base, rank, mt, nt, te);
-  else ks_reduce_and_store_s<BN, RED_STRIDE, NT, 8>(p, base, rank, mt, nt, te);
-}
-
-template <int BN>
-__global__ void __launch_bounds__(TC_THREADS)
-gemm_tc_ksplit_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p,
-                      int m_tiles, int S) {   // gridDim.x = tiles * S, cluster (S, 1, 1); S in {1, 2, 4, 8}
-  using C = KsConfig<BN>;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bars = base + C::DATA_BYTES;
-  auto full_bar = [&](int s) { return bars + 8u * s; };
-  auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
-  const uint32_t acc_full = bars + 8u * (2 * C::STAGES);
-  const uint32_t tmem_slot = bars + 8u * (2 * C::STAGES + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int rank = (int)cluster_rank();
-  const int tile = blockIdx.x / S;
-  const int mt = tile % m_tiles, nt = tile / m_tiles;
-  const int kblocks = (p.k + TC_BK - 1) / TC_BK;
-  const int per = (kblocks + S - 1) / S;
-  const int kb0 = rank * per;
-  const int nkb = max(0, min(kblocks, kb0 + per) - kb0);
-
-  if (threadIdx.x == 0) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-    for (int s = 0; s < C::STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-    }
-    mbar_init(acc_full, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(C::TMEM_COLS));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-  }
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  uint32_t tmem_d;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_d) : "r"(tmem_slot));
-
-  pdl_launch_dependents();
-  if (warp == 0) {
-    if (lane == 0) {
-      // ---- TMA producer: the weight tiles of the first stages do not wait for the kernel before ----
-      const int ahead = nkb < C::STAGES ? nkb : C::STAGES;
-      if (ahead == 0) pdl_wait();
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % C::STAGES;
-        if (i >= C::STAGES && !mbar_wait(empty_bar(s), ((i / C::STAGES) - 1) & 1, p.error_flag, 21)) break;
-        mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
-        const uint32_t a_dst = base + s * C::STAGE_BYTES;
-        tma_load_2d(a_dst, &map_w, (kb0 + i) * TC_BK, mt * TC_BM, full_bar(s));
-        if (i < ahead) {
-          if (i == ahead - 1) {
-            pdl_wait();
-            for (int j = 0; j < ahead; ++j)
-              tma_load_2d(base + j * C::STAGE_BYTES + C::A_BYTES, &map_x, (kb0 + j) * TC_BK, nt * BN, full_bar(j));
-          }
-        } else {
-          tma_load_2d(a_dst + C::A_BYTES, &map_x, (kb0 + i) * TC_BK, nt * BN, full_bar(s));
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      // ---- MMA issuer ----
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-      bool ok = true;
-      for (int i = 0; i < nkb; ++i) {
-        const int s = i % C::STAGES;
-        ok = mbar_wait(full_bar(s), (i / C::STAGES) & 1, p.error_flag, 22);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = base + s * C::STAGE_BYTES;
-        const uint64_t a_desc = umma_desc(a_addr), b_desc = umma_desc(a_addr + C::A_BYTES);
-#pragma unroll
-        for (int k4 = 0; k4 < TC_BK / 16; ++k4)
-          umma_bf16(tmem_d, a_desc + 2 * k4, b_desc + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
-        umma_commit(empty_bar(s));
-      }
-      if (nkb > 0 && ok) umma_commit(acc_full);   // arrives when every product above has finished
-      else mbar_arrive(acc_full);
-    }
-  } else {
-    // ---- epilogue warps, part 1: this CTA's partial tile into its own shared memory (over the ring) ----
-    const int quad = warp & 3;
-    pdl_wait();
-    mbar_wait(acc_full, 0, p.error_flag, 23);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t row_addr = base + (uint32_t)((quad * 32 + lane) * C::RED_STRIDE) * 4u;
-    const uint32_t t_base = tmem_d + ((uint32_t)(quad * 32) << 16);
-#pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 16) {
-      float v[16];
-      if (nkb > 0) tmem_ld16(t_base + c0, v);
-      else {
-#pragma unroll
-        for (int c = 0; c < 16; ++c) v[c] = 0.f;
-      }
-#pragma unroll
-      for (int q = 0; q < 4; ++q)
-        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (uint32_t)(c0 + 4 * q) * 4u), "f"(v[4 * q]),
-                     "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3])
-                     : "memory");
-    }
-  }
-  // every CTA's partial tile is in place
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-
-  if (warp >= 2) ks_reduce_and_store<BN, C::RED_STRIDE, 128>(p, base, rank, S, mt, nt, threadIdx.x - 64);
-  // nobody leaves while a peer may still read its shared memory
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-  if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(C::TMEM_COLS));
-  }
-}
-
-// ------------------------------------------------------------------------------------------------
-// The cluster kernel with WIDE stages, for products whose output tiles are fewer than the SMs.
+// Such a product is a read of W, and with 128-row tiles it has few of them (2,048 output rows: 16 tiles), so k must be
+// cut for every SM to stream.  Through a workspace, the CTA that comes last adds all the partial tiles alone (16 splits
+// of a 128x64 tile: half a megabyte read by one CTA — the o and down projections took 18 and 29 us at 64 tokens).
+// Here the S CTAs that share an output tile form a cluster, each CTA finishes 1/S of the tile's rows, and nothing of
+// the partial sums goes through global memory.
 //
 // A thread that issues a tensor copy is busy with it for about half a microsecond whatever its size up to 32 KB, and
 // one thread's copies do not overlap (a block alone on its SM whose one producer thread requests 16 KB tiles takes in
@@ -1073,51 +872,14 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   }
 }
 
-// Cluster size for a product of `tiles` output tiles and `kblocks` 64-wide k blocks: the largest of 8, 4, 2
-// that leaves every CTA at least four k blocks and does not ask for more CTAs than are resident at once.  Tiles
-// of 128 tokens stop at clusters of four: eight CTAs of 130 KB each have few places on the device (measured,
-// 2,048 x 2,048 at 128 tokens: 24.4 us in clusters of eight, 14.1 us in clusters of four; 2,048 x 8,192: 34.2 / 22.1).
-static int ksplit_cluster(long tiles, int kblocks, long resident, int bn) {
-  for (int s = bn >= 128 ? 4 : 8; s >= 2; s >>= 1)
-    if (tiles * s <= resident && kblocks / s >= 4) return s;
+// Cluster size for a product of `tiles` output tiles and `kblocks` 64-wide k blocks: the larger of 4 and 2 that leaves
+// every CTA at least four k blocks and does not ask for more CTAs than SMs (one block per SM), else 1.  Clusters of
+// eight such blocks have few places on the device (measured, 2,048 x 2,048 at 128 tokens: 24.4 us in clusters of
+// eight, 14.1 us in clusters of four).
+static int wide_cluster(long tiles, int kblocks) {
+  for (int s = 4; s >= 2; s >>= 1)
+    if (tiles * s <= sm_count() && kblocks / s >= 4) return s;
   return 1;
-}
-
-// CTAs of the cluster kernel that one SM holds (shared memory and TMEM columns).
-template <int BN>
-constexpr int ksplit_per_sm() {
-  constexpr int by_smem = (227 * 1024) / (KsConfig<BN>::SMEM_BYTES + 1024);
-  constexpr int by_tmem = 512 / KsConfig<BN>::TMEM_COLS;
-  return by_smem < 1 ? 1 : (by_smem < by_tmem ? by_smem : by_tmem);
-}
-
-template <int BN>
-static int launch_tc_ksplit(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int m_tiles, int n_tiles, int S,
-                            cudaStream_t stream) {
-  using C = KsConfig<BN>;
-  static PerDevice<bool> configured_on;
-  bool& configured = configured_on.here();
-  if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tc_ksplit_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
-      return LLMI_ERR_LAUNCH;
-    configured = true;
-  }
-  const long tiles = (long)m_tiles * n_tiles;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(tiles * S));
-  cfg.blockDim = dim3(TC_THREADS);
-  cfg.dynamicSmemBytes = C::SMEM_BYTES;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = (unsigned)S;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled(PDL_GEMM) ? 1 : 0;
-  cfg.attrs = attr;
-  cfg.numAttrs = 2;
-  return cudaLaunchKernelEx(&cfg, gemm_tc_ksplit_kernel<BN>, mw, mx, p, m_tiles, S) == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH;
 }
 
 template <int BN>
@@ -1258,21 +1020,6 @@ LLMI_EXPORT int llmi_gemm_tc_splits(int n_tok, int m_out, int k) {
   return s < 1 ? 1 : s;
 }
 
-// Size of the cluster that shares an output tile (1: the product does not go to the cluster kernel): a few
-// dozen tokens, a k cut wanted, and a cluster of 2, 4 or 8 that is resident at once.
-static int tc_cluster_size(int n_tok, int m_out, int k) {
-  static int enabled = -1;
-  if (enabled < 0) {
-    const char* e = getenv("LLMI_TC_KSPLIT");
-    enabled = (e && e[0] == '0') ? 0 : 1;
-  }
-  const int bn = tc_bn(n_tok, m_out);
-  if (!enabled || bn < 32 || bn > 128 || llmi_gemm_tc_splits(n_tok, m_out, k) <= 1) return 1;
-  const long tiles = (long)((m_out + TC_BM - 1) / TC_BM) * ((n_tok + bn - 1) / bn);
-  const int per_sm = bn == 32 ? ksplit_per_sm<32>() : (bn == 64 ? ksplit_per_sm<64>() : ksplit_per_sm<128>());
-  return ksplit_cluster(tiles, (k + TC_BK - 1) / TC_BK, (long)sm_count() * per_sm, bn);
-}
-
 // The output of the wide-stage kernel as [n_tok][cols] of bf16 or fp32 with boxes of [box_tok tokens][box_cols]: the way
 // out by TMA.  LLMI_ERR_ALIGN if its base or pitch is not a multiple of 16 bytes (the caller then lets the threads store).
 static int make_wide_out_map(CUtensorMap* map, void* out, long n_tok, long cols, long ldo, int elem_bytes, int box_cols, int box_tok) {
@@ -1301,8 +1048,7 @@ static int tc_wide_cluster(int n_tok, int m_out, int k) {
   if (!enabled || bn < 32 || bn > 128) return 0;
   const long tiles = (long)((m_out + TC_BM - 1) / TC_BM) * ((n_tok + bn - 1) / bn);
   if (tiles > sm_count()) return 0;
-  // (one block per SM: clusters of eight have few places on the device, so four at most)
-  return ksplit_cluster(tiles, (k + TC_BK - 1) / TC_BK, sm_count(), 128);
+  return wide_cluster(tiles, (k + TC_BK - 1) / TC_BK);
 }
 
 // 64-wide k blocks that one CTA accumulates before partial sums are added across CTAs (the whole k range when
@@ -1310,8 +1056,7 @@ static int tc_wide_cluster(int n_tok, int m_out, int k) {
 LLMI_EXPORT int llmi_gemm_tc_k_per_cta(int n_tok, int m_out, int k) {
   const int kblocks = (k + TC_BK - 1) / TC_BK;
   const int W = tc_wide_cluster(n_tok, m_out, k);
-  const int S = W ? W : tc_cluster_size(n_tok, m_out, k);
-  const int cuts = (W || S > 1) ? S : llmi_gemm_tc_splits(n_tok, m_out, k);
+  const int cuts = W ? W : llmi_gemm_tc_splits(n_tok, m_out, k);
   return (kblocks + cuts - 1) / cuts;
 }
 
@@ -1372,9 +1117,8 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
   }
   // (the pair kernel adds into the residual stream by TMA: y must then be 16-byte aligned with a pitch of whole 16 bytes)
   const bool pair_out_ok = mode != OUT_ADD_F32 || (!((uintptr_t)y & 15) && !(ldy & 3));
-  // pairs of SMs: from 256 tokens on, where the shape has more 128-wide tiles than SMs (bn == 256) or nothing to cut
-  if (pair_ok && n_tok >= 256 && (bn == 256 || (n_tok >= 512 && tc_cluster_size(n_tok, m_out, k) == 1)) && splits == 1 &&
-      pair_out_ok) {
+  // pairs of SMs: from 256 tokens on, where the shape has more 128-wide tiles than SMs (bn == 256)
+  if (pair_ok && n_tok >= 256 && (bn == 256 || n_tok >= 512) && splits == 1 && pair_out_ok) {
     const int pbn = pair_token_tile(n_tok, m_out);
     rc = make_map(&mx, x, n_tok, k, ldx, pbn / 2);
     if (rc != LLMI_OK) return rc;
@@ -1391,14 +1135,6 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
   TcParams p{m_out, n_tok, k, y, ldy, bias, mode, splits, workspace, tickets, error_flag};
   const int m_tiles = (m_out + TC_BM - 1) / TC_BM, n_tiles = (n_tok + bn - 1) / bn;
   if ((long)m_tiles * n_tiles * splits > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
-  // a few dozen tokens and too few tiles for the GPU: the k range is cut over a cluster (LLMI_TC_KSPLIT=0: over a workspace)
-  const int S = tc_cluster_size(n_tok, m_out, k);
-  if (S > 1) {
-    TcParams pk{m_out, n_tok, k, y, ldy, bias, mode, 1, nullptr, nullptr, error_flag};
-    if (bn == 32) return launch_tc_ksplit<32>(mw, mx, pk, m_tiles, n_tiles, S, stream);
-    if (bn == 64) return launch_tc_ksplit<64>(mw, mx, pk, m_tiles, n_tiles, S, stream);
-    return launch_tc_ksplit<128>(mw, mx, pk, m_tiles, n_tiles, S, stream);
-  }
   switch (bn) {
     case 16: return launch_tc<16>(mw, mx, p, m_tiles, n_tiles, stream);
     case 32: return launch_tc<32>(mw, mx, p, m_tiles, n_tiles, stream);

@@ -305,22 +305,23 @@ _FUSE_NORM = os.environ.get("LLMI_FUSE_NORM", "1") != "0"
 
 
 SKINNY_SMALL_WEIGHT = 16 << 20    # elements: up to here the weight-streaming kernel also takes 17 to 32 tokens
-SKINNY_TINY_WEIGHT = 3 << 20      # and up to here 33 to 64 tokens,
-SKINNY_FEW_ROWS = 2048            # as it does for any matrix of at most this many rows
+SKINNY_TINY_WEIGHT = 3 << 20      # and up to here 33 to 64 tokens
 
 
 def skinny_applies(x: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether the product x·wᵀ goes to the weight-streaming kernel: up to 16 tokens always; beyond, where the tcgen05
-    kernel's fixed cost (cluster, TMEM, reduction over a cluster when there are few 128-row tiles: 6 to 9 us) is most
-    of its time.  Measured (us, weight-streaming against tcgen05), 32 tokens: 2,048 x 2,048 5.0 / 7.4, 6,144 x 2,048
-    10.8 / 11.2, 2,048 x 8,192 11.5 / 12.9, 4,096 x 4,096 12.5 / 12.5, but 16,384 x 2,048 21.5 / 17.2, 6,144 x 4,096
-    17.3 / 15.7; 64 tokens: 2,048 x 2,048 6.5 / 10.4, 2,048 x 8,192 15.2 / 15.9, 2,048 x 4,096 9.4 / 12.3, 960 x 2,560
-    6.9 / 9.5, but 3,072 x 3,072 14.4 / 13.2, 6,144 x 2,048 16.4 / 14.5, 16,384 x 2,048 32.6 / 20.4."""
+    kernel's fixed cost (cluster, TMEM, exchange of partial tiles over a cluster when there are few 128-row tiles: 4 to
+    5 us) is most of its time, or where the norm that rides on the weight-streaming products would cost a kernel of
+    its own.  Measured (us, weight-streaming against tcgen05), 32 tokens: 2,048 x 2,048 4.9 / 5.2, 6,144 x 2,048
+    10.7 / 8.8 (plus a norm of 3 us), 2,048 x 8,192 11.3 / 11.4, but 16,384 x 2,048 21.2 / 14.8, 6,144 x 4,096
+    17.2 / 13.0; 64 tokens: 576 x 1,536 5.3 / 5.5, 1,600 x 960 4.7 / 5.5, 960 x 2,560 6.9 / 6.5, but 2,048 x 2,048
+    6.5 / 6.2, 2,048 x 8,192 15.2 / 12.2, 6,144 x 2,048 16.2 / 9.4, 16,384 x 2,048 32.7 / 15.4 (a decode step of the
+    1.7B shape at batch 64 with the two 2,048-row products on the tcgen05 kernel: 9.61 -> 9.28 ms)."""
     n = x.shape[0]
     if _FORCE_SIMT or _NO_SKINNY or x.shape[1] % 64 or not gemm_tc_eligible(x, w):
         return False
     return bool(n <= SKINNY_MAX_TOKENS or (n <= 32 and w.numel() <= SKINNY_SMALL_WEIGHT)
-                or (n <= 64 and (w.numel() <= SKINNY_TINY_WEIGHT or w.shape[0] <= SKINNY_FEW_ROWS)))
+                or (n <= 64 and w.numel() <= SKINNY_TINY_WEIGHT))
 
 
 def norm_deferrable(n_tokens: int, width: int, dtype) -> bool:
