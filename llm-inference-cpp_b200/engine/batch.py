@@ -95,12 +95,15 @@ def _align(n: int, a: int = 4) -> int:
 
 
 def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: int = 0,
-              pad_pages_to: int = 0) -> StepContext:
+              pad_pages_to: int = 0, pad_tokens_to: int = 0, pad_want_to: int = 0) -> StepContext:
     """Validate a step, reserve its cache room, and upload its index arrays.
 
     ``pad_seqs_to`` / ``pad_pages_to`` round the decode batch and the page tables up (padding
     sequences have index -1 and are skipped by every kernel) so that recorded launches of one
-    shape can be replayed for smaller batches.
+    shape can be replayed for smaller batches.  ``pad_tokens_to`` (with ``pad_want_to``) does the same
+    for a prompt step: token rows up to that number belong to no sequence (id and sequence -1: the
+    embedding leaves zeros there and nothing of them reaches the cache or another row), padding
+    sequences bring no tokens, and wanted rows beyond the real ones point nowhere (-1).
     """
     if not seqs:
         raise StepError("step: no sequences")
@@ -128,11 +131,16 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
     bases = [cache.length(slot) for slot in slots]          # raises CacheError for a slot that is not live
     cache.extend_all(dict(zip(slots, lens)))       # raises with nothing reserved if the step does not fit (it first takes back what was reserved ahead)
 
-    n_seqs = max(n_real, pad_seqs_to) if decode else n_real
+    pad_prompt = (not decode) and pad_tokens_to > 0
+    n_seqs = max(n_real, pad_seqs_to) if (decode or pad_prompt) else n_real
     n_pad = n_seqs - n_real
-    n_tokens = sum(lens) + n_pad
     n_want_real = sum(len(s.want) for s in seqs)
-    n_want = n_want_real + (n_pad if pad_seqs_to else 0)   # a padded step also wants its padding rows
+    if decode:
+        n_tokens = sum(lens) + n_pad
+        n_want = n_want_real + (n_pad if pad_seqs_to else 0)   # a padded step also wants its padding rows
+    else:
+        n_tokens = max(sum(lens), pad_tokens_to)
+        n_want = max(n_want_real, pad_want_to) if pad_prompt else n_want_real
     kv_lens = [b + n for b, n in zip(bases, lens)]
     max_kv = max(kv_lens)
 
@@ -156,7 +164,7 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
         return h[a:a + n]
     tok, tseq, tpos = region("token_ids"), region("tok_seq"), region("tok_pos")
     want, qstart, kvlen, sslot = region("want_rows"), region("seq_q_start"), region("seq_kv_len"), region("seq_slot")
-    n_tok_real = n_tokens - n_pad
+    n_tok_real = sum(lens)
     tok[:n_tok_real] = all_tokens
     if decode:
         tseq[:n_real] = np.arange(n_real, dtype=np.int32)
@@ -176,7 +184,16 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
         for place in s.want:
             want[w] = qstart[i] + int(place)
             w += 1
-    if n_pad:                               # padding sequences: one token each that no kernel touches
+    if not decode and (n_tokens > n_tok_real or n_pad or n_want > n_want_real):
+        # a padded prompt step: rows of no sequence, sequences of no tokens, wanted rows that point nowhere
+        tok[n_tok_real:] = -1
+        tseq[n_tok_real:] = -1
+        tpos[n_tok_real:] = 0
+        qstart[n_real:n_seqs] = n_tok_real
+        kvlen[n_real:] = 0
+        sslot[n_real:] = -1
+        want[w:] = -1
+    if decode and n_pad:                    # padding sequences: one token each that no kernel touches
         t0 = n_tok_real
         tok[t0:] = -1
         tseq[t0:] = -1
@@ -186,7 +203,7 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
         sslot[n_real:] = -1
         if pad_seqs_to:
             want[w:w + n_pad] = np.arange(t0, t0 + n_pad, dtype=np.int32)
-    qstart[n_seqs] = n_tokens
+    qstart[n_seqs] = n_tokens if decode else n_tok_real
     slot_index = np.asarray(slots, dtype=np.int64)
     for g, start, P in page_layout:
         table = h[start:start + n_seqs * P].reshape(n_seqs, P)
@@ -208,8 +225,10 @@ def plan_step(cache, seqs, vocab_size: int, buffers: StepBuffers, pad_seqs_to: i
     ctx.max_q_len = max(lens)
     ctx.max_kv_len = max_kv
     ctx.decode = decode
-    ctx.n_q_blocks = sum((n + 127) // 128 for n in lens)     # 128-query blocks of the prompt kernel
-    ctx.host_q_lens, ctx.host_kv_lens = (None, None) if decode else (list(lens), list(kv_lens))   # for kernels that plan on the host
+    # 128-query blocks of the prompt kernel; a padded step launches the most that its shape can have (the rest find no work)
+    ctx.n_q_blocks = (n_tokens // 128 + n_seqs) if pad_prompt else sum((n + 127) // 128 for n in lens)
+    # for kernels that plan on the host (a padded step's launches must not depend on its lengths)
+    ctx.host_q_lens, ctx.host_kv_lens = (None, None) if (decode or pad_prompt) else (list(lens), list(kv_lens))
     ctx.h2d_bytes = cur * 4
 
     def view(name):

@@ -1,4 +1,5 @@
-"""Recorded decode steps: one CUDA graph per (batch bucket, page-table bucket, choice).
+"""Recorded steps: one CUDA graph per (batch bucket, page-table bucket, choice) for decode steps, and one per
+(token bucket, sequence bucket, wanted-rows bucket, page-table bucket) for short prompt steps.
 
 A decode step of a small model is a few hundred short kernels; launched one by one from
 Python, the launches cost more than the kernels.  A step's device work depends on the host
@@ -19,6 +20,13 @@ patched — while the device computes; when the caller comes back with exactly t
 tokens are filled in and the block is uploaded.  If another step comes instead (a sequence ended, a prompt
 in between), the reservation is taken back (``SequenceCache.settle``) and the step is planned the ordinary
 way.  ``LLMI_AHEAD=0`` switches it off.
+
+Prompt steps (:class:`PromptGraphs`).  A prompt of a few hundred tokens is bound by the host as well: about two
+hundred launches of 6 to 15 us each, 2.9 ms whether the prompt has 16 or 256 tokens, where the device needs a
+third of that.  Such steps are padded to a shape — token rows to 16, 32 or a multiple of 64 (128 from 512 on), sequences and
+wanted rows to a power of two, page tables as for decode steps; the padding rows belong to no sequence — and a
+shape that comes a second time is recorded and replayed from then on.  Prompts beyond 1,024 tokens keep the device
+busy for longer than their launches take and run launch by launch, unpadded.
 """
 from __future__ import annotations
 
@@ -160,3 +168,88 @@ class DecodeGraphs:
         except CacheError:
             return                              # no room (or the context's end): whatever comes next will say so
         self._pending = (weakref.ref(cache), P, ctx, step, (m.rt.generation, m.buffers.dev.data_ptr(), m.buffers.serial))
+
+
+def prompt_bucket(n_tokens: int) -> int:
+    """The padded number of token rows of a prompt step, 0 if such a step is not padded (and not recorded)."""
+    if n_tokens <= 32:
+        return 16 if n_tokens <= 16 else 32          # the weight-streaming products' range
+    if n_tokens <= 512:
+        return (n_tokens + 63) // 64 * 64
+    if n_tokens <= 1024:
+        return (n_tokens + 127) // 128 * 128
+    return 0
+
+
+class PromptGraphs:
+    """Prompt steps by shape: padded, run plainly the first time a shape comes, recorded the second time, replayed after."""
+    MAX_GRAPHS = 96          # per model; the oldest shapes go first
+
+    def __init__(self, model):
+        self.model = model
+        self.graphs = {}         # key -> (graph, logits, kernels launched)
+        self.seen = {}           # key -> times the shape has come without a graph
+        self.replays = 0
+        self._watched = set()
+
+    def _drop_cache(self, serial: int) -> None:
+        for table in (self.graphs, self.seen):
+            for key in [k for k in table if k[4] == serial]:
+                del table[key]
+        self._watched.discard(serial)
+
+    def _key(self, T, S, W, P, cache):
+        m = self.model
+        return (T, S, W, P, cache.serial, m.rt.generation, m.buffers.dev.data_ptr())
+
+    def step(self, cache, seqs):
+        """fp32 logits [wanted, vocab] of a prompt step (scratch: valid until the next step), or None if the step
+        is not one for this path (too long): the caller then runs it the plain way."""
+        from .batch import plan_step
+        from ..ops import kernels
+        m = self.model
+        T = prompt_bucket(sum(len(s.tokens) for s in seqs))
+        if T == 0:
+            return None
+        S = bucket(len(seqs))
+        n_want_real = sum(len(s.want) for s in seqs)
+        W = bucket(n_want_real) if n_want_real else 0
+        ps = cache.page_size
+        # (a slot that is not live, or a step that does not fit, is plan_step's to report)
+        try:
+            need_pages = max((cache.length(s.slot) + len(s.tokens) + ps - 1) // ps for s in seqs)
+        except Exception:
+            need_pages = 1
+        P = max(need_pages, min(bucket(need_pages), cache.max_pages_per_seq))
+        ctx = plan_step(cache, seqs, m.spec.vocab_size, m.buffers, pad_seqs_to=S, pad_pages_to=P, pad_tokens_to=T, pad_want_to=W)
+        m._last_h2d = ctx.h2d_bytes
+        key = self._key(T, S, W, P, cache)
+        entry = self.graphs.get(key)
+        if entry is not None:
+            g, rec_logits, n_kernels = entry
+            g.replay()
+            self.replays += 1
+            kernels.launch_count(n_kernels)
+            return rec_logits[:n_want_real]
+        logits = m.run(ctx, cache)
+        key = self._key(T, S, W, P, cache)          # the plain run may have grown a scratch buffer
+        self.seen[key] = self.seen.get(key, 0) + 1
+        if RECORD and self.seen[key] >= 2:
+            for table in (self.graphs, self.seen):   # shapes recorded or counted before a buffer moved never come again
+                for stale in [k for k in table if k[4] == cache.serial and k[5:] != key[5:]]:
+                    del table[stale]
+            while len(self.graphs) >= self.MAX_GRAPHS:
+                del self.graphs[next(iter(self.graphs))]
+            if cache.serial not in self._watched:
+                self._watched.add(cache.serial)
+                weakref.finalize(cache, _drop_graphs_of, weakref.ref(self), cache.serial)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            before = kernels.launch_count()
+            with torch.cuda.graph(g):
+                rec_logits = m.run(ctx, cache)
+            n_kernels = kernels.launch_count() - before
+            kernels.launch_count(-n_kernels)          # recording launches nothing
+            self.graphs[key] = (g, rec_logits, n_kernels)
+            self.seen.pop(key, None)
+        return logits[:n_want_real]

@@ -32,6 +32,13 @@ class Model:
                 raise ValueError(f"schedule call {i} reads the cache of call {call.cache_of}, which does not exist")
         self.buffers = StepBuffers(self.rt.device, self.rt)
         self._graphs = None
+        self._prompt_graphs = None
+        # Short prompt steps are padded to a shape and replayed from recorded graphs (engine/graphs.py) where every
+        # part says that rows of no sequence do it no harm (``takes_padding_rows``), in the compute type that serving uses.
+        parts = [self.embedding, self.final_norm, self.head]
+        for layer in self.layers:
+            parts += [layer.block, *layer.parts.values()]
+        self.pads_prompts = dtype == torch.bfloat16 and all(getattr(p, "takes_padding_rows", False) for p in parts)
         self.last_logits = None      # fp32 [rows, vocab] of the latest step_and_choose (scratch: valid until the next step)
         self.parameter_count = sum(int(torch.tensor(d.shape).prod()) for d in expected_tensors(spec).values())
 
@@ -108,6 +115,15 @@ class Model:
         """
         if getattr(cache, "owner", None) is not self:
             raise ValueError("step: cache was not created by this model")
+        if (self.pads_prompts and trace is None and not pad_seqs_to and not pad_pages_to and seqs
+                and max(len(s.tokens) for s in seqs) > 1):
+            from . import graphs
+            if graphs.RECORD:
+                if self._prompt_graphs is None:
+                    self._prompt_graphs = graphs.PromptGraphs(self)
+                logits = self._prompt_graphs.step(cache, seqs)
+                if logits is not None:
+                    return logits
         ctx = plan_step(cache, seqs, self.spec.vocab_size, self.buffers, pad_seqs_to, pad_pages_to)
         self._last_h2d = ctx.h2d_bytes
         return self.run(ctx, cache, trace)

@@ -60,6 +60,12 @@ class GQAttention:
 
     defers_norm = True
 
+    @property
+    def takes_padding_rows(self) -> bool:
+        """Token rows of no sequence (index -1) do no harm: the rotation skips them, attention gives them no job, and
+        the products treat rows alone — if the position part agrees."""
+        return bool(getattr(self.position, "takes_padding_rows", False))
+
     def forward(self, h, x, ctx, binding, then_norm=None) -> bool:
         T = h.shape[0]
         nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim

@@ -18,6 +18,7 @@ def _defers(p) -> bool:
 
 @part("block", "prenorm")
 class PreNormBlock:
+    takes_padding_rows = True       # token rows of no sequence (a step padded to a shape) do no harm: rows are treated alone
     def __init__(self, mixer_norm, mixer, ffn_norm, ffn):
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn = mixer_norm, mixer, ffn_norm, ffn
 

@@ -41,6 +41,7 @@ def _make(family: str, ps: PartSpec, tensors: dict, rt, **context):
 
 class NoMixer:
     """Stands in for the mixer of a layer that has none: it keeps no cache."""
+    takes_padding_rows = True       # token rows of no sequence (a step padded to a shape) do no harm: rows are treated alone
 
     def cache_request(self):
         return None

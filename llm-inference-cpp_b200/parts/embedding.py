@@ -16,6 +16,7 @@ from .registry import TensorDecl, nested_build, nested_declare, part
 class TokenTable:
     """params: ``vocab``, ``width``, optional ``position`` (a PartSpec of the position family whose
     ``at_embedding`` acts on the looked-up rows).  tensors: ``weight [vocab, width]`` and the position part's."""
+    takes_padding_rows = True       # token rows of no sequence (a step padded to a shape) do no harm: rows are treated alone
 
     @classmethod
     def declare(cls, spec):
@@ -48,6 +49,7 @@ class TokenTable:
 @part("head", "linear_head")
 class LinearHead:
     """params: ``vocab``, ``width``, ``tied``.  tensors: ``weight [vocab, width]`` unless tied."""
+    takes_padding_rows = True       # token rows of no sequence (a step padded to a shape) do no harm: rows are treated alone
 
     @classmethod
     def declare(cls, spec):

@@ -12,6 +12,7 @@ from .registry import TensorDecl, part
 @part("ffn", "swiglu")
 class SwiGLU:
     """params: ``width``, ``inner``."""
+    takes_padding_rows = True       # token rows of no sequence (a step padded to a shape) do no harm: rows are treated alone
 
     @classmethod
     def declare(cls, spec):

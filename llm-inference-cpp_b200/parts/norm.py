@@ -11,6 +11,7 @@ from .registry import TensorDecl, part
 @part("norm", "rms")
 class RMSNorm:
     """params: ``width``, ``eps``.  tensors: ``weight [width]`` (kept in fp32)."""
+    takes_padding_rows = True       # token rows of no sequence (a step padded to a shape) do no harm: rows are treated alone
 
     @classmethod
     def declare(cls, spec):

@@ -46,6 +46,8 @@ class PositionEncoding:
 
 @part("position", "none")
 class NoPosition(PositionEncoding):
+    takes_padding_rows = True       # (a step padded to a shape has token rows of no sequence: see engine/graphs.py)
+
     def __init__(self, spec, tensors, rt, **_):
         pass
 
@@ -53,6 +55,7 @@ class NoPosition(PositionEncoding):
 @part("position", "rotary_half")
 class RotaryHalf(PositionEncoding):
     """params: ``head_dim``, ``theta``, optional ``rotary_dim`` (default: the whole head)."""
+    takes_padding_rows = True       # the rotation kernel skips rows of no sequence
 
     def __init__(self, spec, tensors, rt, **_):
         d = int(spec.params.get("rotary_dim", spec.params["head_dim"]))

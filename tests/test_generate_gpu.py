@@ -250,6 +250,64 @@ def test_logits_of_recorded_padded_decode_steps(model_dirs, tmp_path, name, dtyp
     assert n_steps == max(t - p for t, p in zip(totals, prompt_lens))
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "width576"])
+def test_logits_of_padded_and_recorded_prompt_steps(model_dirs, tmp_path, name):
+    """Short prompt steps in bfloat16 are padded to a shape (token rows of no sequence up to a multiple of 64,
+    sequences and wanted rows to a power of two, page tables) and a shape that comes again is recorded and replayed.
+    The same batches of unequal prompts are run four times over fresh slots of one cache — plainly, plainly and
+    recorded, replayed, replayed — with EVERY row's logits compared with the plain implementation each time; then the
+    sequences go on in a portion of several tokens (a prompt step over a cache that is not empty) and one token at a
+    time, which shows that the padding rows left nothing in the cache.  A prompt longer than the padded range (more
+    than 1,024 tokens) runs beside them launch by launch."""
+    import torch
+    import helpers as H
+    import llmi_b200 as L
+    from llmi_b200.sampling import Sampler
+    if name == "width576":
+        d = str(tmp_path)
+        L.write_random_model(d, WIDTH_576, 8, torch.bfloat16)
+        batches = [[50, 3, 130], [200], [64, 64], [1100]]
+        more, tail = 9, 3
+    else:
+        d = model_dirs(name, STORAGE["bfloat16"])
+        ctx_len = TINY_CONFIGS[name]["max_position_embeddings"]
+        batches = [[50, 3, min(100, ctx_len - 16)], [min(120, ctx_len - 16)], [64, 64]]
+        more, tail = 9, 3
+    cfg, w = P.read_model(d)
+    model = L.load(d, "bfloat16")
+    assert model.pads_prompts
+    V = cfg["vocab_size"]
+    rng = np.random.default_rng(23)
+    sampler = Sampler(L.SamplingParams(), model.rt)
+    cache = model.new_cache(sum(H.round_up(n + more + tail) for b in batches for n in b), n_slots=8)
+    for round_ in range(4):
+        for lens in batches:
+            toks = [rng.integers(0, V, n + more + tail).tolist() for n in lens]
+            refs = [P.forward(cfg, w, t) for t in toks]
+            slots = [cache.alloc_slot() for _ in toks]
+            logits = model.step(cache, [L.SequenceStep(s, t[:n], list(range(n))) for s, t, n in zip(slots, toks, lens)]).cpu().numpy()
+            assert logits.shape == (sum(lens), V) and np.isfinite(logits).all()
+            row = 0
+            for t, n, ref in zip(toks, lens, refs):
+                for i in range(n):
+                    assert H.rel_to_max(logits[row + i], ref[i]) < H.TOL["bfloat16"], (name, round_, lens, i)
+                row += n
+            # the same sequences go on by several tokens at once (their last logits wanted), then one by one
+            logits = model.step(cache, [L.SequenceStep(s, t[n:n + more], [more - 1]) for s, t, n in zip(slots, toks, lens)]).cpu().numpy()
+            for r, (n, ref) in enumerate(zip(lens, refs)):
+                assert H.rel_to_max(logits[r], ref[n + more - 1]) < H.TOL["bfloat16"], (name, round_, lens, "portion")
+            for j in range(tail):
+                model.step_and_choose(cache, [L.SequenceStep(s, [t[n + more + j]], [0]) for s, t, n in zip(slots, toks, lens)], sampler)
+                logits = model.last_logits.cpu().numpy()
+                for r, (n, ref) in enumerate(zip(lens, refs)):
+                    assert H.rel_to_max(logits[r], ref[n + more + j]) < H.TOL["bfloat16"], (name, round_, lens, "decode", j)
+            for s in slots:
+                cache.free_slot(s)
+            cache.check()
+    g = model._prompt_graphs
+    assert g is not None and g.replays >= 2 * len([b for b in batches if sum(b) <= 1024]), (g.replays, len(g.graphs))
+
+
 def test_one_model_many_caches_of_different_sizes(model_dirs):
     """A model is reused across ``generate`` calls that each make a cache of their own, of different sizes but the same
     batch and page bucket: a recorded step must never be replayed against another cache's memory."""

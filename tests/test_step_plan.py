@@ -73,6 +73,31 @@ def test_block_of_a_step_that_continues_by_several_tokens():
     assert cache.length(a) == 65 and cache.length(b) == 11 and cache.length(c) == 2
 
 
+def test_block_of_a_prompt_step_padded_to_a_shape():
+    """A prompt step padded for replay: token rows of no sequence (-1) up to the asked number, padding sequences
+    without tokens, wanted rows that point nowhere, page tables of the asked width — and the real entries, the
+    cache's lengths and the last entry of the sequence starts as in the step without padding."""
+    cache = make_cache()
+    a, b, c = cache.alloc_slot(), cache.alloc_slot(), cache.alloc_slot()
+    buf = HostBuffers()
+    plan_step(cache, [SequenceStep(a, [1] * 70, [])], 50, buf)
+    ctx = plan_step(cache, [SequenceStep(a, [5, 6, 7], [0, 2]), SequenceStep(b, [9, 8], [1]), SequenceStep(c, [4], [])], 50, buf,
+                    pad_seqs_to=4, pad_pages_to=4, pad_tokens_to=64, pad_want_to=4)
+    assert not ctx.decode and ctx.n_tokens == 64 and ctx.n_seqs == 4 and ctx.n_want == 4 and ctx.n_want_real == 3
+    assert ctx.token_ids.tolist() == [5, 6, 7, 9, 8, 4] + [-1] * 58
+    assert ctx.tok_seq.tolist() == [0, 0, 0, 1, 1, 2] + [-1] * 58
+    assert ctx.tok_pos.tolist() == [70, 71, 72, 0, 1, 0] + [0] * 58
+    assert ctx.want_rows.tolist() == [0, 2, 4, -1]
+    assert ctx.seq_q_start.tolist() == [0, 3, 5, 6, 6]
+    assert ctx.seq_kv_len.tolist() == [73, 2, 1, 0]
+    assert ctx.seq_slot.tolist() == [a, b, c, -1]
+    assert ctx.host_q_lens is None and ctx.n_q_blocks == 64 // 128 + 4
+    pages = ctx.pages_of(cache.kv_groups[0])
+    assert pages.shape == (4, 4) and (pages[3] == -1).all() and pages[0, 1] >= 0 and pages[0, 2] == -1
+    assert cache.length(a) == 73 and cache.length(b) == 2 and cache.length(c) == 1
+    cache.check()
+
+
 @pytest.mark.parametrize("window", [0, 100])
 def test_continued_decode_step_equals_planning_anew(window):
     """Two caches in lockstep: one is stepped by plan_step every time, the other by continue_decode_step.
