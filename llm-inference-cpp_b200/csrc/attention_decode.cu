@@ -477,6 +477,7 @@ attention_decode_kernel(DecodeParams p, int n_items) {
           for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pr, vf[e], acc[g][e]);
         }
       }
+      fence_reads_before_async_writes();
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(s));
     }

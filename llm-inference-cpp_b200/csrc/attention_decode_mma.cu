@@ -459,6 +459,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         dm_mma(o[dc], pa, r0, r1);
         dm_mma(o[dc + 1], pa, r2, r3);
       }
+      fence_reads_before_async_writes();
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(s));
     }

@@ -259,6 +259,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
         mma_bf16(o[dc + 1], pa[kc], r2, r3);
       }
     }
+    fence_reads_before_async_writes();
     __syncthreads();   // every warp is done with stage s
   }
   if (!ok) return;

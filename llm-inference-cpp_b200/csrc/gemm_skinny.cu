@@ -216,6 +216,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           sk_mma(acc[n], a, b0, b1);
         }
       }
+      fence_reads_before_async_writes();
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(s));
     }

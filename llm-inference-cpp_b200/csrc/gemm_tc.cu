@@ -326,10 +326,12 @@ constexpr int TP_SMEM = TP_STAGES * TP_STAGE_BYTES + 2 * TP_OUT_BYTES + 1024 + 8
 
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                    const __grid_constant__ CUtensorMap map_out, TcParams p, int m_tiles, int n_tiles, int bn) {   // tiles of 256 weight rows x bn tokens (bn % 16 == 0, <= 256)
+                    const __grid_constant__ CUtensorMap map_out, TcParams p, int m_tiles, int n_tiles, int bn,
+                    int out_tma) {   // tiles of 256 weight rows x bn tokens (bn % 16 == 0, <= 256); out_tma: map_out describes the output
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t out_smem = base + TP_STAGES * TP_STAGE_BYTES;      // two buffers of TP_OUT_BYTES
+  uint8_t* const out_ptr = smem_raw + (out_smem - smem_u32(smem_raw));   // the same place as a generic address
   const uint32_t bars = out_smem + 2 * TP_OUT_BYTES;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (TP_STAGES + s); };
@@ -429,11 +431,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       if (!mbar_wait(acc_full(b), (j >> 1) & 1, p.error_flag, 8)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int nch = (min(bn, p.n_tok - n0) + 15) / 16;
-      if (p.mode == OUT_ADD_F32) {
-        // out += tile: the tile goes through shared memory ([16 tokens][128 rows] fp32, two buffers) and is ADDED to
-        // the residual stream by TMA (cp.reduce.async.bulk.tensor .add): nothing of the old values comes to the SM, so
-        // the epilogue is a stream of stores instead of a chain of read-modify-write round trips (it is not hidden
-        // behind a next tile when a pair has one tile only: the o and down projections of a 2,048-token prompt).
+      if (out_tma) {
+        // The tile goes out through shared memory, 16 tokens at a time ([16 tokens][128 rows] in the output's type,
+        // gated: [16][64 features]; two buffers), and is stored by TMA — for the residual stream ADDED by TMA
+        // (cp.reduce.async.bulk.tensor .add): nothing of the old values comes to the SM.  The epilogue is a stream of
+        // shared-memory stores instead of a chain of read-modify-write round trips or of 2-byte stores to global memory
+        // (gated, the stores of the threads cost 7 to 10 us a product that the next tile's MMAs did not hide; it is
+        // not hidden at all when a pair has one tile only: the o and down projections of a 2,048-token prompt).
         // Rows and tokens past the ends of `out` are clipped by the copy.
         const float bias = (p.bias && m < p.m_out) ? p.bias[m] : 0.f;
         const int row_in_cta = quad * 32 + lane;
@@ -445,22 +449,51 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(leader_empty);
           }
-          const uint32_t buf = out_smem + (uint32_t)((n_out & 1) * TP_OUT_BYTES);
+          const uint32_t buf_off = (uint32_t)((n_out & 1) * TP_OUT_BYTES);
+          const uint32_t buf = out_smem + buf_off;
+          uint8_t* const bufp = out_ptr + buf_off;
           if (n_out >= 2) {
             // the copy that read this buffer two chunks ago has to be done with it
             if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             asm volatile("bar.sync 1, 128;" ::: "memory");
           }
+          if (p.mode == OUT_SWIGLU) {
+            // rows alternate gate and up (src/model/transformer.cpp:290; src/model/kernels.cpp:148): the even lane finishes
+            // tokens 0..7 of feature row / 2, the odd lane tokens 8..15
+            const bool is_gate = (row_in_cta & 1) == 0;
+            float g[8], u[8];
 #pragma unroll
-          for (int c = 0; c < 16; ++c)
-            asm volatile("st.shared.f32 [%0], %1;" ::"r"(buf + (uint32_t)((c * TC_BM + row_in_cta) * 4)), "f"(v[c] + bias) : "memory");
+            for (int c = 0; c < 8; ++c) {
+              const float recv = __shfl_xor_sync(0xffffffffu, is_gate ? v[c + 8] : v[c], 1);
+              g[c] = is_gate ? v[c] : recv;
+              u[c] = is_gate ? recv : v[c + 8];
+            }
+            __nv_bfloat16* o = (__nv_bfloat16*)bufp + (is_gate ? 0 : 8) * (TC_BM / 2) + (row_in_cta >> 1);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) o[c * (TC_BM / 2)] = __float2bfloat16_rn(__fdividef(g[c], 1.0f + __expf(-g[c])) * u[c]);
+          } else if (p.mode == OUT_STORE) {
+            __nv_bfloat16* o = (__nv_bfloat16*)bufp + row_in_cta;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) o[c * TC_BM] = __float2bfloat16_rn(v[c] + bias);
+          } else {
+            float* o = (float*)bufp + row_in_cta;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) o[c * TC_BM] = v[c] + bias;
+          }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           asm volatile("bar.sync 1, 128;" ::: "memory");
           if (warp == 2 && lane == 0) {
-            asm volatile(
-                "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
-                ::"l"(&map_out), "r"(mt * 256 + (int)rank * TC_BM), "r"(n0 + ci * 16), "r"(buf)
-                : "memory");
+            const int r0 = mt * 256 + (int)rank * TC_BM;
+            const int c0 = p.mode == OUT_SWIGLU ? (r0 >> 1) : r0;
+            if (p.mode == OUT_ADD_F32)
+              asm volatile(
+                  "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                  ::"l"(&map_out), "r"(c0), "r"(n0 + ci * 16), "r"(buf)
+                  : "memory");
+            else
+              asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                           ::"l"(&map_out), "r"(c0), "r"(n0 + ci * 16), "r"(buf)
+                           : "memory");
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
           ++n_out;
@@ -520,7 +553,7 @@ static int pair_token_tile(int n_tok, int m_out) {
 }
 
 static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, TcParams p, int m_tiles,
-                          int n_tiles, int bn, cudaStream_t stream) {
+                          int n_tiles, int bn, int out_tma, cudaStream_t stream) {
   static PerDevice<bool> configured_on;
   bool& configured = configured_on.here();
   if (!configured) {
@@ -545,7 +578,7 @@ static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CU
   attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled(PDL_GEMM) ? 1 : 0;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mw, mx, mo, p, m_tiles, n_tiles, bn) == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH;
+  return cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, mw, mx, mo, p, m_tiles, n_tiles, bn, out_tma) == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -960,19 +993,6 @@ static int make_map_3d(CUtensorMap* map, const void* ptr, long rows, long k, lon
   return r == CUDA_SUCCESS ? LLMI_OK : LLMI_ERR_DRIVER;
 }
 
-// out [n_tok, m_out] fp32 with row pitch ldo, as [16 tokens][128 rows] boxes for the residual-add epilogue.
-static int make_out_map(CUtensorMap* map, void* out, long n_tok, long m_out, long ldo) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return LLMI_ERR_DRIVER;
-  const cuuint64_t dims[2] = {(cuuint64_t)m_out, (cuuint64_t)n_tok};
-  const cuuint64_t strides[1] = {(cuuint64_t)ldo * 4};
-  const cuuint32_t box[2] = {(cuuint32_t)TC_BM, 16};
-  const cuuint32_t elem[2] = {1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? LLMI_OK : LLMI_ERR_DRIVER;
-}
-
 template <int BN>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, TcParams p, int m_tiles, int n_tiles,
                      cudaStream_t stream) {
@@ -1020,9 +1040,9 @@ LLMI_EXPORT int llmi_gemm_tc_splits(int n_tok, int m_out, int k) {
   return s < 1 ? 1 : s;
 }
 
-// The output of the wide-stage kernel as [n_tok][cols] of bf16 or fp32 with boxes of [box_tok tokens][box_cols]: the way
-// out by TMA.  LLMI_ERR_ALIGN if its base or pitch is not a multiple of 16 bytes (the caller then lets the threads store).
-static int make_wide_out_map(CUtensorMap* map, void* out, long n_tok, long cols, long ldo, int elem_bytes, int box_cols, int box_tok) {
+// The output as [n_tok][cols] of bf16 or fp32 with boxes of [box_tok tokens][box_cols]: the way out by TMA of the
+// cluster kernel and of the kernel on pairs of SMs.  LLMI_ERR_ALIGN if its base or pitch is not a multiple of 16 bytes (the caller then lets the threads store).
+static int make_out_map(CUtensorMap* map, void* out, long n_tok, long cols, long ldo, int elem_bytes, int box_cols, int box_tok) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return LLMI_ERR_DRIVER;
   if (((uintptr_t)out & 15) || ((ldo * elem_bytes) & 15) || ((box_cols * elem_bytes) & 15)) return LLMI_ERR_ALIGN;
@@ -1099,7 +1119,7 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
     // the way out by TMA: a CTA of a cluster of W stores [bn tokens][128 / W rows] (gated: half as many features)
     CUtensorMap mo = mw;
     const int gated = mode == OUT_SWIGLU;
-    const int out_rc = make_wide_out_map(&mo, y, n_tok, gated ? m_out / 2 : m_out, ldy, (mode == OUT_STORE || gated) ? 2 : 4,
+    const int out_rc = make_out_map(&mo, y, n_tok, gated ? m_out / 2 : m_out, ldy, (mode == OUT_STORE || gated) ? 2 : 4,
                                          (TC_BM / W) >> gated, bn);
     if (out_rc == LLMI_ERR_DRIVER) return out_rc;
     const int out_tma = out_rc == LLMI_OK;
@@ -1115,20 +1135,23 @@ LLMI_EXPORT int llmi_gemm_tc(const void* x, long ldx, const void* w, long ldw, c
     const char* e = getenv("LLMI_TC_PAIR");
     pair_ok = (e && e[0] == '0') ? 0 : 1;
   }
-  // (the pair kernel adds into the residual stream by TMA: y must then be 16-byte aligned with a pitch of whole 16 bytes)
-  const bool pair_out_ok = mode != OUT_ADD_F32 || (!((uintptr_t)y & 15) && !(ldy & 3));
+  // The pair kernel's tiles leave by TMA, 16 tokens at a time ([16][128 rows] in the output's type, gated [16][64]):
+  // the output must then be 16-byte aligned with a pitch of whole 16 bytes.  If it is not, the threads store — except
+  // into the residual stream, which the pair kernel only adds to by TMA (such a product takes the single-SM kernel).
   // pairs of SMs: from 256 tokens on, where the shape has more 128-wide tiles than SMs (bn == 256)
-  if (pair_ok && n_tok >= 256 && (bn == 256 || n_tok >= 512) && splits == 1 && pair_out_ok) {
-    const int pbn = pair_token_tile(n_tok, m_out);
-    rc = make_map(&mx, x, n_tok, k, ldx, pbn / 2);
-    if (rc != LLMI_OK) return rc;
-    TcParams pp{m_out, n_tok, k, y, ldy, bias, mode, 1, workspace, tickets, error_flag};
-    CUtensorMap mo = mx;      // only the residual-add epilogue uses it
-    if (mode == OUT_ADD_F32) {
-      rc = make_out_map(&mo, y, n_tok, m_out, ldy);
+  if (pair_ok && n_tok >= 256 && (bn == 256 || n_tok >= 512) && splits == 1) {
+    const int gated = mode == OUT_SWIGLU;
+    CUtensorMap mo = mw;
+    const int out_rc = make_out_map(&mo, y, n_tok, gated ? m_out / 2 : m_out, ldy, (mode == OUT_STORE || gated) ? 2 : 4,
+                                         TC_BM >> gated, 16);
+    if (out_rc == LLMI_ERR_DRIVER) return out_rc;
+    if (out_rc == LLMI_OK || mode != OUT_ADD_F32) {
+      const int pbn = pair_token_tile(n_tok, m_out);
+      rc = make_map(&mx, x, n_tok, k, ldx, pbn / 2);
       if (rc != LLMI_OK) return rc;
+      TcParams pp{m_out, n_tok, k, y, ldy, bias, mode, 1, workspace, tickets, error_flag};
+      return launch_tc_pair(mw, mx, mo, pp, (m_out + 255) / 256, (n_tok + pbn - 1) / pbn, pbn, out_rc == LLMI_OK, stream);
     }
-    return launch_tc_pair(mw, mx, mo, pp, (m_out + 255) / 256, (n_tok + pbn - 1) / pbn, pbn, stream);
   }
   rc = make_map(&mx, x, n_tok, k, ldx, bn);
   if (rc != LLMI_OK) return rc;

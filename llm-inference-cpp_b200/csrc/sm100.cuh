@@ -52,6 +52,14 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// A buffer that threads have READ (ld.shared, ldmatrix: the generic proxy) and that a bulk or tensor copy (the async
+// proxy) will fill again: every reading thread calls this before it says that the buffer is free.  The arrive on the
+// mbarrier alone does not order the reads before a write of the other proxy.  (Measured on the weight-streaming product
+// without it: with two blocks on an SM, 9 to 16 tokens and two or three stages a row tile, one row tile in three
+// thousand came out with a few rows wrong in 3 to 90 % of the launches — rows of the tile that the next copy brought.)
+__device__ __forceinline__ void fence_reads_before_async_writes() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
 
 // ---- thread-block clusters ----
 __device__ __forceinline__ uint32_t cluster_rank() {

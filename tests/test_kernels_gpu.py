@@ -660,6 +660,28 @@ def test_gemm_tc_gated_epilogue(n_tok, inner, k):
     kk.check_device_errors("cuda:0")
 
 
+@pytest.mark.parametrize("n_tok,m_out,k", [(16, 49152, 512), (12, 49152, 576), (16, 16384, 768), (8, 49152, 512), (32, 49152, 512)])
+def test_gemm_skinny_many_short_row_tiles_again_and_again(n_tok, m_out, k):
+    """Many row tiles per block, each of two or three stages, so that the ring of stages wraps around all the time
+    while a block's warps are still reading: every launch of many must be right in every element.  (A stage that is
+    handed back without ordering the warps' reads before the next copy's writes gave one wrong row tile in thousands
+    in a third of the launches of the first shape — a head of 49,152 rows over a narrow model at batch 16.)"""
+    kk = K()
+    torch.manual_seed(k + n_tok)
+    x = torch.randn(n_tok, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(m_out, k, device="cuda") * 0.05).to(torch.bfloat16)
+    ref = x.float() @ w.float().T
+    scale = float(ref.abs().max())
+    y = torch.empty(n_tok, m_out, device="cuda")
+    worst = torch.zeros((), device="cuda")
+    for _ in range(120):
+        y.fill_(float("nan"))
+        kk.gemm_skinny(x, w, y, None, kk.OUT_STORE_F32)
+        worst = torch.maximum(worst, torch.nan_to_num((y - ref).abs().max(), nan=float("inf")))
+    assert float(worst) / scale < 2e-5
+    kk.check_device_errors("cuda:0")
+
+
 @pytest.mark.parametrize("n_tok,m_out,k", [(1, 200, 64), (5, 64, 64), (8, 2048, 2048), (8, 130, 8192), (16, 384, 192),
                                            (17, 6144, 2048), (32, 520, 960), (3, 16, 320), (33, 1728, 576), (64, 576, 1536),
                                            (50, 130, 960), (64, 3072, 576)])
