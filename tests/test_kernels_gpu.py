@@ -418,7 +418,8 @@ def test_sample_distribution():
                                            (300, 520, 136), (64, 2048, 8192), (8, 256, 4096), (1000, 136, 264),
                                            (33, 300, 2048), (100, 2048, 2048), (20, 640, 512), (128, 136, 1024),
                                            (600, 1100, 320), (1500, 700, 1088), (512, 256, 64), (256, 2048, 2048),
-                                           (300, 2048, 1024), (511, 6144, 512), (256, 16384, 256), (384, 1024, 4096)])
+                                           (300, 2048, 1024), (511, 6144, 512), (256, 16384, 256), (384, 1024, 4096),
+                                           (511, 6150, 512), (130, 2048, 8192), (48, 6144, 2048)])
 def test_gemm_tc_all_modes(n_tok, m_out, k):
     """The tcgen05 product against fp64 on ragged shapes, with and without split-K."""
     kk = K()
@@ -644,7 +645,8 @@ def test_attention_prefill_ragged(nh, nkv, hd, window, kernel):
 
 
 @pytest.mark.parametrize("n_tok,inner,k", [(1, 100, 72), (8, 8192, 2048), (70, 176, 64), (300, 320, 120), (2048, 512, 256),
-                                           (40, 1024, 1024), (24, 72, 2048), (100, 300, 768)])
+                                           (40, 1024, 1024), (24, 72, 2048), (100, 300, 768),
+                                           (300, 9728, 128), (300, 9604, 128), (64, 8192, 2048)])
 def test_gemm_tc_gated_epilogue(n_tok, inner, k):
     """silu(gate)·up finished inside the product, rows alternating gate and up; with and without split-K."""
     kk = K()
