@@ -372,19 +372,26 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const float2 t = __fadd2_rn(a, b);
         l_run += t.x + t.y;
       }
-      if (j >= 1 && __any_sync(0xffffffffu, corr != 1.f)) {
-        // this half's O is rescaled in place: O += P_{j-1} V_{j-1} has to be finished (it may still run beside this softmax)
+      if (j >= 1) {
+        // O += P_{j-1} V_{j-1} (it may still run beside this softmax) is waited for on EVERY page, needed or not: a
+        // wait on a phase's parity is right only for a thread that is at most one phase behind, and o_done completes a
+        // phase per page.  (With the wait only where O is rescaled, a thread could reach the wait behind the loop two
+        // phases behind, where it passes at once: when the MMAs lagged — head size 128, blocks that start beside busy
+        // ones — the first query block, two pages, now and then read its O before the products had finished.)
         ok = mbar_wait(o_done, (j - 1) & 1, p.error_flag, 49);
         if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (__any_sync(0xffffffffu, corr != 1.f)) {
+          // this half's O is rescaled in place
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int c = 0; c < HD; c += 16) {
-          float t[16];
-          ft_ld16(t_o + (uint32_t)c, t);
-          ft_ld_wait();
+          for (int c = 0; c < HD; c += 16) {
+            float t[16];
+            ft_ld16(t_o + (uint32_t)c, t);
+            ft_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 16; ++e) t[e] *= corr;
-          ft_st16(t_o + (uint32_t)c, t);
+            for (int e = 0; e < 16; ++e) t[e] *= corr;
+            ft_st16(t_o + (uint32_t)c, t);
+          }
         }
       }
       // P -> TMEM, over the first half of the S columns this thread has just read: bf16 pairs, 16 columns at a time

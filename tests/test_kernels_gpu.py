@@ -462,6 +462,50 @@ def test_gemm_tc_strided_input_and_refusals():
                    torch.empty(4, 8, device="cuda"), None, kk.OUT_STORE_F32)
 
 
+@pytest.mark.parametrize("lens,nh,nkv,hd", [([2048], 32, 8, 128), ([1500, 548], 32, 8, 128), ([2048], 32, 32, 64)])
+def test_attention_prefill_many_blocks_again_and_again(lens, nh, nkv, hd):
+    """More (query block, head) jobs than blocks are resident, so that the short query blocks start beside busy
+    ones: every launch of many gives the bits of the first, and the first query block (two pages, the job that came
+    out wrong now and then when a softmax thread's wait on the finished products could pass two phases behind)
+    agrees with the plain formula."""
+    kk = K()
+    torch.manual_seed(5)
+    T, S = sum(lens), len(lens)
+    Pg = max((n + 63) // 64 for n in lens)
+    kc, vc = paged(S * Pg, nkv, hd, "bfloat16")
+    pages = torch.randperm(S * Pg, dtype=torch.int32).reshape(S, Pg)
+    keys = [torch.randn(n, nkv, hd).to(torch.bfloat16) for n in lens]
+    vals = [torch.randn(n, nkv, hd).to(torch.bfloat16) for n in lens]
+    for s_, n in enumerate(lens):
+        for pg_i in range((n + 63) // 64):
+            m_ = min(64, n - 64 * pg_i)
+            kc[pages[s_, pg_i], :, :m_] = keys[s_][64 * pg_i:64 * pg_i + m_].transpose(0, 1).cuda()
+            vc[pages[s_, pg_i], :, :m_] = vals[s_][64 * pg_i:64 * pg_i + m_].transpose(0, 1).cuda()
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd).to(torch.bfloat16).cuda()
+    out = torch.zeros(T, nh * hd, device="cuda", dtype=torch.bfloat16)
+    starts = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    qstart = torch.from_numpy(starts).cuda()
+    kvlen = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    nqb = sum((n + 127) // 128 for n in lens)
+    scale = 1 / math.sqrt(hd)
+
+    def launch():
+        kk.attention_prefill_tc(qkv, out, kc, vc, pages.cuda(), qstart, kvlen, nqb, nh, nkv, hd, scale, 0, None)
+    launch()
+    first = out.clone()
+    for _ in range(60):
+        out.zero_()
+        launch()
+        assert torch.equal(out, first)
+    kk.check_device_errors("cuda:0")
+    for s_, n in enumerate(lens):          # the first query block of every sequence against the plain formula
+        rows = min(128, n)
+        for r in (0, 1, 63, 64, rows - 1):
+            q = qkv[starts[s_] + r, :nh * hd].double().cpu().numpy().reshape(nh, hd)
+            ref = plain_attention_rows(q, keys[s_][:r + 1].double().numpy(), vals[s_][:r + 1].double().numpy(), nh // nkv, scale, 0)
+            assert rel(first[starts[s_] + r].reshape(nh, hd), torch.from_numpy(ref)) < 1e-2, (s_, r)
+
+
 DECODE_SHAPES = [("simt", 32, 32, 64), ("simt", 15, 5, 64), ("simt", 8, 2, 128), ("simt", 8, 8, 32), ("simt", 16, 2, 64),
                  ("mma", 15, 5, 64), ("mma", 8, 2, 128), ("mma", 16, 2, 64), ("mma", 28, 4, 128), ("mma", 32, 2, 64),
                  ("mma", 12, 1, 128), ("mma", 10, 5, 64), ("mma", 3, 3, 64)]
