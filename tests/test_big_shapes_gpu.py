@@ -108,3 +108,35 @@ def test_full_width_layers_follow_the_plain_implementation(shape, dtype):
         g = np.stack(got[i])
         assert np.isfinite(g).all()
         assert H.rel_to_max(g, refs[i]) < H.TOL[dtype], (shape, dtype, i)
+
+
+@pytest.mark.parametrize("config", [CONFIG, WIDE], ids=["width-2048", "width-4096-heads-of-128"])
+def test_the_same_step_again_and_again_gives_the_same_bits(config):
+    """Steps of full-width layers run repeatedly on the same context — a long prompt, unequal prompts, decode steps at
+    batch sizes that reach every product kernel — must give the bits of the first run every time: a race between a
+    copy engine and the threads, or a wait that passes a phase too early, shows as a result that differs now and then
+    (two such faults were found this way), long before it is large enough to fail a comparison with a tolerance."""
+    import torch
+    import llmi_b200 as L
+    from llmi_b200.engine.batch import plan_step
+    from llmi_b200.ops import kernels
+    model = L.random_model(dict(config, num_hidden_layers=2), seed=4, dtype="bfloat16", on_device=True)
+    V = config["vocab_size"]
+    rng = np.random.default_rng(2)
+    for what, lens, reps in (("prompt", [2048], 8), ("prompt", [300, 40, 1000], 8), ("prompt", [17], 12), ("decode", [500] * 16, 20),
+                             ("decode", [700] * 40, 20), ("decode", [3000] * 8, 20)):
+        cache = model.new_cache(sum((n + 1 + 63) // 64 * 64 for n in lens) + 64, n_slots=64)
+        slots = [cache.alloc_slot() for _ in lens]
+        toks = [rng.integers(0, V, n + 1).tolist() for n in lens]
+        if what == "decode":
+            for s, t, n in zip(slots, toks, lens):
+                model.step(cache, [L.SequenceStep(s, t[:n], [])])
+            ctx = plan_step(cache, [L.SequenceStep(s, [t[n]], [0]) for s, t, n in zip(slots, toks, lens)], V, model.buffers)
+        else:
+            ctx = plan_step(cache, [L.SequenceStep(s, t[:n], [n - 1, n // 2]) for s, t, n in zip(slots, toks, lens)], V, model.buffers)
+        first = model.run(ctx, cache).clone()
+        assert torch.isfinite(first).all()
+        for _ in range(reps):
+            assert torch.equal(model.run(ctx, cache), first), (what, lens)
+        kernels.check_device_errors("cuda:0")
+        del cache
