@@ -574,7 +574,7 @@ int launch_decode(const DecodeParams& p, int n_seqs, cudaStream_t stream) {
   const long n_items = (long)n_seqs * p.n_kv_heads * p.max_splits;
   if (n_items > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
   const int resident = decode_resident<HD, G>();
-  const int grid = (int)(n_items < resident ? n_items : resident);
+  const int grid = coprime_grid(n_items, resident, p.max_splits);
   return launch_pdl(PDL_ATTENTION, attention_decode_kernel<HD, G>, grid, DEC_THREADS, C::SMEM_BYTES, stream, p, (int)n_items);
 }
 

@@ -584,7 +584,7 @@ static int dm_launch(const CUtensorMap& mk, const CUtensorMap& mv, const DecodeM
   if (resident <= 0) return LLMI_ERR_LAUNCH;
   const long n_items = (long)n_seqs * p.n_kv_heads * p.max_splits;
   if (n_items > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
-  const int grid = (int)(n_items < resident ? n_items : resident);
+  const int grid = coprime_grid(n_items, resident, p.max_splits);
   return launch_pdl(PDL_ATTENTION, attention_decode_mma_kernel<HD>, grid, DM_THREADS, C::smem_bytes(p.group), stream, mk, mv,
                     p, (int)n_items);
 }
