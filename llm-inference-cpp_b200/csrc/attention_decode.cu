@@ -37,6 +37,13 @@ namespace llmi {
 constexpr int DEC_PAGE = 64;          // positions per cache page (the cache's page size)
 constexpr int DEC_CONSUMERS = 4;      // consumer warps; each takes 16 keys of a page
 constexpr int DEC_THREADS = (DEC_CONSUMERS + 2) * 32;   // + producer warp + epilogue warp
+// The variant for few sequence-heads has one warp more, whose first lane asks for the value tiles (a thread is busy
+// with a copy for about half a microsecond and its copies do not overlap: with two issuing threads a block streams
+// fast enough for a sequence-head to need fewer splits, or none).  Seven warps of its 92 registers fit an SM twice,
+// six warps of 72 three times: with more sequence-heads than two blocks per SM hold, three blocks with one
+// producer each are the faster ones (measured, 32 kv heads of 64 at 4,096 positions, this variant against the
+// other: batch 8 46.9 / 49.6 us, batch 24 to 48 3 to 10 % slower).
+template <bool VP> struct DecThreads { static constexpr int value = DEC_THREADS + (VP ? 32 : 0); };
 
 struct DecodeParams {
   const __nv_bfloat16* q;   // [tokens, >= n_heads*HD], row pitch ldq
@@ -103,8 +110,8 @@ struct DecItem {
 // warp takes a finished item's merged (max, sum, values) from shared memory and does the slow,
 // latency-bound part — partial to the workspace, fence, ticket, and the final merge if it drew the
 // last ticket — while the consumers are already on the next item.
-template <int HD, int G>
-__global__ void __launch_bounds__(DEC_THREADS)
+template <int HD, int G, bool VP>
+__global__ void __launch_bounds__(DecThreads<VP>::value)
 attention_decode_kernel(DecodeParams p, int n_items) {
   using C = DecCfg<HD>;
   static_assert(C::LPR >= 2 && C::LPR <= 32 && C::NI >= 1, "head size not supported by this layout");
@@ -232,10 +239,34 @@ attention_decode_kernel(DecodeParams p, int n_items) {
             const size_t tile = ((size_t)pages[d.pg0 + i] * p.n_kv_heads + d.kvh) * (size_t)(DEC_PAGE * HD);
             mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
             bulk_load(base + s * C::STAGE_BYTES, p.k_cache + tile, C::TILE_BYTES, full_bar(s));
-            bulk_load(base + s * C::STAGE_BYTES + C::TILE_BYTES, p.v_cache + tile, C::TILE_BYTES, full_bar(s));
+            // (with the value tiles' own producer, only the newest page's value tile is asked for here)
+            if (!VP || newest) bulk_load(base + s * C::STAGE_BYTES + C::TILE_BYTES, p.v_cache + tile, C::TILE_BYTES, full_bar(s));
           }
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      }
+    }
+    return;
+  }
+
+  if (VP && warp == DEC_CONSUMERS + 2) {
+    // ---- the value tiles' producer: the same walk over items and stages, the value tile of every page but a
+    // sequence-head's newest one (that page is written in this step: its tiles follow the producer warp's wait and
+    // append).  A stage's full barrier is in its new phase once its empty barrier has completed, so these bytes
+    // count for the right phase even when they land before the producer warp has announced the stage.
+    if (lane == 0) {
+      int it = 0;
+      DecItem d;
+      bool ok = true;
+      for (int item = next_item(blockIdx.x, d); item < n_items && ok; item = next_item(item + gridDim.x, d)) {
+        const int32_t* pages = p.seq_pages + (size_t)d.seq * p.pages_stride;
+        for (int i = 0; i < d.n_pages; ++i, ++it) {
+          if ((d.pg0 + i + 1) * DEC_PAGE > d.pos) continue;          // the newest page
+          const int s = it % C::STAGES;
+          if (it >= C::STAGES && !mbar_wait(empty_bar(s), ((it / C::STAGES) - 1) & 1, p.error_flag, 16)) { ok = false; break; }
+          const size_t tile = ((size_t)pages[d.pg0 + i] * p.n_kv_heads + d.kvh) * (size_t)(DEC_PAGE * HD);
+          bulk_load(base + s * C::STAGE_BYTES + C::TILE_BYTES, p.v_cache + tile, C::TILE_BYTES, full_bar(s));
+        }
       }
     }
     return;
@@ -544,15 +575,15 @@ attention_decode_kernel(DecodeParams p, int n_items) {
 }
 
 // Blocks of this kernel that fit on the device at once.
-template <int HD, int G>
+template <int HD, int G, bool VP = false>
 int decode_resident() {
   using C = DecCfg<HD>;
   static PerDevice<int> resident_on;
   int& resident = resident_on.here();
   if (!resident) {
-    cudaFuncSetAttribute(attention_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    cudaFuncSetAttribute(attention_decode_kernel<HD, G, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     int per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<HD, G>, DEC_THREADS,
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_kernel<HD, G, VP>, DecThreads<VP>::value,
                                                       C::SMEM_BYTES) != cudaSuccess || per_sm < 1)
       per_sm = 1;
     resident = per_sm * sm_count();
@@ -560,22 +591,42 @@ int decode_resident() {
   return resident;
 }
 
-template <int HD, int G>
-int launch_decode(const DecodeParams& p, int n_seqs, cudaStream_t stream) {
+template <int HD, int G, bool VP>
+int launch_decode_variant(const DecodeParams& p, int n_seqs, cudaStream_t stream) {
   using C = DecCfg<HD>;
   static PerDevice<bool> configured_on;
   bool& configured = configured_on.here();
   if (!configured) {
-    if (cudaFuncSetAttribute(attention_decode_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(attention_decode_kernel<HD, G, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              C::SMEM_BYTES) != cudaSuccess)
       return LLMI_ERR_LAUNCH;
     configured = true;
   }
   const long n_items = (long)n_seqs * p.n_kv_heads * p.max_splits;
   if (n_items > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
-  const int resident = decode_resident<HD, G>();
+  const int resident = decode_resident<HD, G, VP>();
   const int grid = coprime_grid(n_items, resident, p.max_splits);
-  return launch_pdl(PDL_ATTENTION, attention_decode_kernel<HD, G>, grid, DEC_THREADS, C::SMEM_BYTES, stream, p, (int)n_items);
+  return launch_pdl(PDL_ATTENTION, attention_decode_kernel<HD, G, VP>, grid, DecThreads<VP>::value, C::SMEM_BYTES, stream, p,
+                    (int)n_items);
+}
+
+// The variant with a producer of its own for the value tiles: ungrouped queries (the grouped ones have the tensor-core
+// kernel) and no more sequence-heads than its blocks hold at once.
+template <int HD, int G>
+bool decode_two_producers(int n_seqs, int n_kv_heads) {
+  if (G != 1) return false;
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("LLMI_DECODE_VALUE_PRODUCER");
+    enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  return enabled && (long)n_seqs * n_kv_heads <= decode_resident<HD, 1, true>();
+}
+
+template <int HD, int G>
+int launch_decode(const DecodeParams& p, int n_seqs, cudaStream_t stream) {
+  if (G == 1 && decode_two_producers<HD, G>(n_seqs, p.n_kv_heads)) return launch_decode_variant<HD, 1, true>(p, n_seqs, stream);
+  return launch_decode_variant<HD, G, false>(p, n_seqs, stream);
 }
 
 static int dispatch_decode(const DecodeParams& p, int n_seqs, int head_dim, int group, cudaStream_t stream) {
@@ -657,6 +708,20 @@ LLMI_EXPORT int llmi_attention_decode_fused(const void* qkv, long ldq, void* out
                  scale * 1.4426950408889634f, window, pages_per_split, splits, partials, tickets, error_flag,
                  1, inv_freq, rotary_dim, n_heads, write_kv ? 1 : 0, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache};
   return dispatch_decode(p, n_seqs, head_dim, group, stream);
+}
+
+// Blocks of the kernel that a step of n_seqs sequences would run that are resident at once, and whether that is the
+// variant with two producer threads (its items may be longer: see ops/kernels.py decode_pages_per_split).
+LLMI_EXPORT int llmi_attention_decode_plan(int head_dim, int group, int n_seqs, int n_kv_heads, int* two_producers) {
+  if (two_producers) *two_producers = 0;
+#define LLMI_DEC(HD) \
+  if (head_dim == HD && group == 1 && decode_two_producers<HD, 1>(n_seqs, n_kv_heads)) { \
+    if (two_producers) *two_producers = 1; \
+    return decode_resident<HD, 1, true>(); \
+  }
+  LLMI_DEC(64); LLMI_DEC(128); LLMI_DEC(32);
+#undef LLMI_DEC
+  return llmi_attention_decode_resident(head_dim, group);
 }
 
 LLMI_EXPORT int llmi_attention_decode_resident(int head_dim, int group) {

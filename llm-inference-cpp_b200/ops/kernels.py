@@ -437,13 +437,12 @@ def decode_pages_per_split(n_seqs: int, n_kv_heads: int, max_pages: int, head_di
     (at least 8 pages unless the batch is tiny) that its fixed cost — first load, merge, ticket —
     is small beside its streaming time.  Large batches get no split at all.
     """
-    key = (head_dim, group)
-    if key not in _resident_cache:
-        fn = lib().llmi_attention_decode_mma_resident if decode_uses_mma(head_dim, group) else lib().llmi_attention_decode_resident
-        _resident_cache[key] = max(1, int(fn(c_int(head_dim), c_int(group))))
-    resident = _resident_cache[key]
     pairs = max(1, n_seqs * n_kv_heads)
     if decode_uses_mma(head_dim, group):
+        key = (head_dim, group)
+        if key not in _resident_cache:
+            _resident_cache[key] = max(1, int(lib().llmi_attention_decode_mma_resident(c_int(head_dim), c_int(group))))
+        resident = _resident_cache[key]
         # The tensor-core kernel: the end of an item that is one of several splits costs about six pages of streaming
         # (four warps merged, the partial result written, a ticket), of a whole sequence-head two; the last split to
         # arrive merges two heads and NZ splits per round trip to L2 (about 1.5 pages of head size 64 each).
@@ -461,13 +460,26 @@ def decode_pages_per_split(n_seqs: int, n_kv_heads: int, max_pages: int, head_di
             if cost < best_cost - 1e-9:
                 best, best_cost = pps, cost
         return best
+    # The CUDA-core kernel has two variants (csrc/attention_decode.cu): with few sequence-heads the one with a producer
+    # thread for the key tiles and one for the value tiles, two blocks per SM, whose items may be long.
+    key = (head_dim, group, n_seqs, n_kv_heads)
+    if key not in _resident_cache:
+        two = ctypes.c_int(0)
+        resident = int(lib().llmi_attention_decode_plan(c_int(head_dim), c_int(group), c_int(n_seqs), c_int(n_kv_heads), ctypes.byref(two)))
+        _resident_cache[key] = (max(1, resident), bool(two.value))
+    resident, two_producers = _resident_cache[key]
     best, best_score = max_pages, -1.0
-    for splits in range(1, max(1, max_pages // 4) + 1):
+    for splits in range(1, max(1, max_pages // (2 if two_producers else 4)) + 1):
         pps = -(-max_pages // splits)
-        items = pairs * -(-max_pages // pps)
+        n_parts = -(-max_pages // pps)
+        items = pairs * n_parts
         rounds = -(-items // resident)
         fill = items / (rounds * resident)                 # how full the rounds are
-        score = fill * pps / (pps + 2.0)                   # an item costs about two pages of streaming on top
+        # An item costs about two pages of streaming on top; with two producers, where items are read twice as fast,
+        # one of several splits about four (partial result, fence, ticket, the last one's merge).  The latter fitted
+        # to measurements (32 kv heads of 64; best split measured = chosen): 4,096 positions at batch 1 / 2 / 4 / 8:
+        # 8 / 16 / 32 pages / none; 8,192 positions: 16 / 32 / 64 / none; 1,024 positions: 2 / 4 / 8 / none.
+        score = fill * pps / (pps + (4.0 if (two_producers and n_parts > 1) else 2.0))
         if score > best_score + 1e-9:
             best, best_score = pps, score
     return best
