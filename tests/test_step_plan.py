@@ -300,3 +300,14 @@ def test_reservations_ahead_and_everything_else_that_touches_the_cache():
     assert not w.can_speculate()
     with pytest.raises(CacheError, match="windowed"):
         prepare_continue(w, ctx, buf)
+
+
+def test_shapes_that_prompt_steps_are_padded_to():
+    """Token rows go up to 16, 32, a multiple of 64 (of 128 from 512 tokens on); longer prompts are not padded."""
+    from llmi_b200.engine.graphs import bucket, prompt_bucket
+    assert [prompt_bucket(n) for n in (1, 16, 17, 32, 33, 64, 65, 500, 512, 513, 640, 641, 1024)] == \
+        [16, 16, 32, 32, 64, 64, 128, 512, 512, 640, 640, 768, 1024]
+    assert prompt_bucket(1025) == 0 and prompt_bucket(4096) == 0
+    for n in range(1, 1025):
+        assert prompt_bucket(n) >= n and prompt_bucket(n) - n < 128
+    assert [bucket(n) for n in (1, 2, 3, 5, 8, 9, 64, 65)] == [1, 2, 4, 8, 8, 16, 64, 128]
