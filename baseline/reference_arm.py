@@ -19,7 +19,7 @@ one run over 2,048 ids with ``--max-new 1``.  There is no device boundary: ``e2e
 
 Every run loads the model and prefills its whole prompt on the CPU first (minutes at this size), so after the
 prefill run the arm estimates what the two decode runs will cost and, if that exceeds what is left of its time
-budget (``LLMI_REFERENCE_BUDGET_S``, default 1600), gives up with an ``unavailable`` line that carries what it
+limit (``LLMI_REFERENCE_LIMIT_S``, default 1600 seconds), gives up with an ``unavailable`` line that carries what it
 has measured.
 """
 from __future__ import annotations
@@ -34,7 +34,8 @@ import time
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
-SRC_CANDIDATES = (os.path.join(REF_DIR, "src"), "/root/reference")
+# the copy under baseline/_ref/src, else a checkout named by LLMI_REFERENCE_SRC
+SRC_CANDIDATES = tuple(c for c in (os.path.join(REF_DIR, "src"), os.environ.get("LLMI_REFERENCE_SRC")) if c)
 
 
 class Unavailable(Exception):
@@ -51,7 +52,7 @@ def find_sources() -> str:
     for src in SRC_CANDIDATES:
         if os.path.exists(os.path.join(src, "CMakeLists.txt")) and os.path.exists(os.path.join(src, "apps", "llmi-generate")):
             return src
-    raise Unavailable("the reference's sources are neither under baseline/_ref/src nor at /root/reference")
+    raise Unavailable("the reference's sources are neither under baseline/_ref/src nor where LLMI_REFERENCE_SRC points")
 
 
 def _runs(binary: str) -> bool:
@@ -135,9 +136,9 @@ def random_ids(n: int, vocab: int, seed: int):
 
 def run(config: dict, batch: int, context: int, prefill_tokens: int, steps: int, warmup: int, layers_full: int) -> dict:
     """The benchmark line of the reference arm (raises :class:`Unavailable` with what was measured so far)."""
-    budget = float(os.environ.get("LLMI_REFERENCE_BUDGET_S", "1600"))
+    limit = float(os.environ.get("LLMI_REFERENCE_LIMIT_S", "1600"))
     t_start = time.time()
-    left = lambda: budget - (time.time() - t_start)
+    left = lambda: limit - (time.time() - t_start)
     steps = max(steps, 128)           # fewer decode steps would drown in the run-to-run spread of the long prefills
     warmup = max(warmup, 3)
     binary = ensure_binary()
@@ -161,7 +162,7 @@ def run(config: dict, batch: int, context: int, prefill_tokens: int, steps: int,
     partial["estimated_seconds_for_decode_runs"] = round(est)
     if est > left():
         raise Unavailable(f"the reference runs on the CPU: its two decode runs at context {context} are estimated at "
-                          f"{est:.0f} s, over the {left():.0f} s left of the budget (LLMI_REFERENCE_BUDGET_S={budget:.0f})",
+                          f"{est:.0f} s, over the {left():.0f} s left of its time limit (LLMI_REFERENCE_LIMIT_S={limit:.0f})",
                           partial)
 
     # 3. decode at the benchmark's context: the same prompt, ending `warmup` and `warmup + steps` tokens later
