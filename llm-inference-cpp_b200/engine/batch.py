@@ -66,8 +66,9 @@ class StepBuffers:
         return self.hosts[i], self.dev
 
     def upload(self, n_int32: int) -> None:
+        from ..ops import kernels
         i = self.turn
-        self.dev[:n_int32].copy_(self.hosts[i][:n_int32], non_blocking=True)
+        kernels.copy_to_device(self.dev.data_ptr(), self.hosts[i].data_ptr(), 4 * n_int32)
         if self.events[i] is None:
             self.events[i] = torch.cuda.Event()
         self.events[i].record()

@@ -82,6 +82,14 @@ def _stream_int() -> int:
     return _stream().value or 0
 
 
+def copy_to_device(dst_ptr: int, src_ptr: int, n_bytes: int) -> None:
+    """``n_bytes`` from pinned host memory at ``src_ptr`` to device memory at ``dst_ptr`` on the current stream (the
+    caller keeps both alive and does not touch the host bytes until the copy is done)."""
+    code = lib().llmi_copy_to_device(c_void_p(dst_ptr), c_void_p(src_ptr), c_long(n_bytes), _stream())
+    if code != 0:
+        raise KernelError(f"copy_to_device: {_ERRORS.get(code, f'error {code}')}")
+
+
 def _addr(t) -> int | None:
     return None if t is None else t.data_ptr()
 
