@@ -37,7 +37,7 @@ namespace llmi {
 constexpr int SK_ROWS = 16;          // output rows per tile
 constexpr int SK_BK = 256;           // k per stage: four 64-wide slices, one per consumer warp
 // stages of the ring: six, three for the widest token tile (64 tokens: 40 KB a stage)
-template <int NT> struct SkStages { static constexpr int value = NT >= 8 ? 3 : 6; };
+template <int NT> struct SkStages { static constexpr int value = NT >= 8 ? 3 : (NT == 1 ? 9 : 6); };
 constexpr int SK_CONSUMERS = 4;
 constexpr int SK_THREADS = (SK_CONSUMERS + 1) * 32;
 
