@@ -205,10 +205,32 @@ LLMI_EXPORT int llmi_sm_count() { return sm_count(); }
 
 // A step's index block from pinned host memory to the device, on the stream: one plain asynchronous copy, here so
 // that the host pays one call for it instead of a tensor operation (22 us of a decode step's 55 us of host time
-// before its launches).
-LLMI_EXPORT int llmi_copy_to_device(void* dst, const void* src, long bytes, cudaStream_t stream) {
+// before its launches).  `done` (or null) is a mark from llmi_mark_new, set behind the copy: llmi_mark_wait returns
+// once the copy has read the host bytes, so that they can be written again (copy and mark in one call: marking by a
+// call of its own cost 10 us more).
+LLMI_EXPORT int llmi_copy_to_device(void* dst, const void* src, long bytes, void* done, cudaStream_t stream) {
   if (bytes <= 0) return LLMI_ERR_BAD_SIZE;
-  return cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyHostToDevice, stream) == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH;
+  if (cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyHostToDevice, stream) != cudaSuccess) return LLMI_ERR_LAUNCH;
+  if (done && cudaEventRecord((cudaEvent_t)done, stream) != cudaSuccess) return LLMI_ERR_LAUNCH;
+  return LLMI_OK;
+}
+LLMI_EXPORT void* llmi_mark_new() {
+  cudaEvent_t e = nullptr;
+  return cudaEventCreateWithFlags(&e, cudaEventDisableTiming) == cudaSuccess ? (void*)e : nullptr;
+}
+LLMI_EXPORT int llmi_mark_wait(void* mark) {
+  return mark && cudaEventSynchronize((cudaEvent_t)mark) == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH;
+}
+LLMI_EXPORT void llmi_mark_free(void* mark) {
+  if (mark) cudaEventDestroy((cudaEvent_t)mark);
+}
+
+// A step's result (the chosen ids, a few bytes) to pinned host memory, waited for: one call for the copy and the wait.
+// A tensor's own way to the host goes through pageable memory and costs about 27 us after the device is done.
+LLMI_EXPORT int llmi_copy_to_host(void* dst, const void* src, long bytes, cudaStream_t stream) {
+  if (bytes <= 0) return LLMI_ERR_BAD_SIZE;
+  if (cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToHost, stream) != cudaSuccess) return LLMI_ERR_LAUNCH;
+  return cudaStreamSynchronize(stream) == cudaSuccess ? LLMI_OK : LLMI_ERR_LAUNCH;
 }
 
 LLMI_EXPORT int llmi_swiglu(int dtype, const void* gate_up, void* out, int n_rows, int inner, cudaStream_t stream) {

@@ -37,7 +37,7 @@ class SequenceStep:
 class StepBuffers:
     """Pinned host blocks and a device twin for the index arrays of steps; grow on demand.
 
-    Two host blocks alternate, each guarded by an event, so that writing the next step's
+    Two host blocks alternate, each guarded by a mark behind its copy, so that writing the next step's
     arrays never overtakes a copy that is still queued on the stream.
     """
 
@@ -56,7 +56,7 @@ class StepBuffers:
         self.serial += 1
         i = self.turn
         if self.events[i] is not None:
-            self.events[i].synchronize()
+            self.events[i].wait()
         if self.hosts[i] is None or self.hosts[i].numel() < n_int32:
             self.hosts[i] = torch.empty(max(4096, 2 * n_int32), dtype=torch.int32, pin_memory=True)
         if self.dev is None or self.dev.numel() < n_int32:
@@ -68,10 +68,9 @@ class StepBuffers:
     def upload(self, n_int32: int) -> None:
         from ..ops import kernels
         i = self.turn
-        kernels.copy_to_device(self.dev.data_ptr(), self.hosts[i].data_ptr(), 4 * n_int32)
         if self.events[i] is None:
-            self.events[i] = torch.cuda.Event()
-        self.events[i].record()
+            self.events[i] = kernels.Mark()
+        kernels.copy_to_device(self.dev.data_ptr(), self.hosts[i].data_ptr(), 4 * n_int32, self.events[i])
 
 
 class StepContext:

@@ -82,12 +82,44 @@ def _stream_int() -> int:
     return _stream().value or 0
 
 
-def copy_to_device(dst_ptr: int, src_ptr: int, n_bytes: int) -> None:
+def copy_to_device(dst_ptr: int, src_ptr: int, n_bytes: int, done: "Mark | None" = None) -> None:
     """``n_bytes`` from pinned host memory at ``src_ptr`` to device memory at ``dst_ptr`` on the current stream (the
-    caller keeps both alive and does not touch the host bytes until the copy is done)."""
-    code = lib().llmi_copy_to_device(c_void_p(dst_ptr), c_void_p(src_ptr), c_long(n_bytes), _stream())
+    caller keeps both alive and does not touch the host bytes until the copy is done: ``done.wait()`` tells)."""
+    code = lib().llmi_copy_to_device(c_void_p(dst_ptr), c_void_p(src_ptr), c_long(n_bytes),
+                                     c_void_p(done.handle if done is not None else 0), _stream())
     if code != 0:
         raise KernelError(f"copy_to_device: {_ERRORS.get(code, f'error {code}')}")
+
+
+class Mark:
+    """A point in a stream's work that the host can wait for (set by :func:`copy_to_device`)."""
+
+    def __init__(self):
+        fn = lib().llmi_mark_new
+        fn.restype = c_void_p
+        self.handle = fn()
+        if not self.handle:
+            raise KernelError("mark: the device gave none")
+
+    def wait(self) -> None:
+        if lib().llmi_mark_wait(c_void_p(self.handle)) != 0:
+            raise KernelError("mark: the wait failed")
+
+    def __del__(self):
+        try:
+            if self.handle:
+                lib().llmi_mark_free(c_void_p(self.handle))
+                self.handle = None
+        except Exception:
+            pass
+
+
+def copy_to_host(dst_ptr: int, src_ptr: int, n_bytes: int) -> None:
+    """``n_bytes`` from device memory at ``src_ptr`` to pinned host memory at ``dst_ptr`` on the current stream; returns
+    when they are there."""
+    code = lib().llmi_copy_to_host(c_void_p(dst_ptr), c_void_p(src_ptr), c_long(n_bytes), _stream())
+    if code != 0:
+        raise KernelError(f"copy_to_host: {_ERRORS.get(code, f'error {code}')}")
 
 
 def _addr(t) -> int | None:
