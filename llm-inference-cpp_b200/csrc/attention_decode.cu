@@ -77,11 +77,12 @@ struct DecodeParams {
   __nv_bfloat16* v_cache_w;
 };
 
-template <int HD>
+// (VP: the variant with a second producer thread; registers leave it two blocks per SM, so its ring may be deeper)
+template <int HD, bool VP = false>
 struct DecCfg {
   static constexpr int TILE_BYTES = DEC_PAGE * HD * 2;
   static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-  static constexpr int STAGES = HD <= 64 ? 4 : (HD <= 128 ? 4 : 3);
+  static constexpr int STAGES = (VP && HD <= 64) ? 6 : (HD <= 128 ? 4 : 3);
   static constexpr int LPR = HD / 8;          // lanes per key row (16 bytes each)
   static constexpr int RPI = 32 / LPR;        // rows per warp instruction
   static constexpr int NI = 16 / RPI;         // instructions per warp per page (16 keys per warp)
@@ -113,7 +114,7 @@ struct DecItem {
 template <int HD, int G, bool VP>
 __global__ void __launch_bounds__(DecThreads<VP>::value)
 attention_decode_kernel(DecodeParams p, int n_items) {
-  using C = DecCfg<HD>;
+  using C = DecCfg<HD, VP>;
   static_assert(C::LPR >= 2 && C::LPR <= 32 && C::NI >= 1, "head size not supported by this layout");
   extern __shared__ uint8_t smem_raw[];
   __shared__ float s_m[DEC_CONSUMERS][G], s_l[DEC_CONSUMERS][G];
@@ -577,7 +578,7 @@ attention_decode_kernel(DecodeParams p, int n_items) {
 // Blocks of this kernel that fit on the device at once.
 template <int HD, int G, bool VP = false>
 int decode_resident() {
-  using C = DecCfg<HD>;
+  using C = DecCfg<HD, VP>;
   static PerDevice<int> resident_on;
   int& resident = resident_on.here();
   if (!resident) {
@@ -593,7 +594,7 @@ int decode_resident() {
 
 template <int HD, int G, bool VP>
 int launch_decode_variant(const DecodeParams& p, int n_seqs, cudaStream_t stream) {
-  using C = DecCfg<HD>;
+  using C = DecCfg<HD, VP>;
   static PerDevice<bool> configured_on;
   bool& configured = configured_on.here();
   if (!configured) {
