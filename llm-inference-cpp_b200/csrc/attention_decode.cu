@@ -628,14 +628,16 @@ bool decode_two_producers(int n_seqs, int n_kv_heads) {
 }
 
 template <int HD, int G>
-int launch_decode(const DecodeParams& p, int n_seqs, cudaStream_t stream) {
-  if (G == 1 && decode_two_producers<HD, G>(n_seqs, p.n_kv_heads)) return launch_decode_variant<HD, 1, true>(p, n_seqs, stream);
+int launch_decode(const DecodeParams& p, int n_seqs, int n_live, cudaStream_t stream) {
+  // (n_live: how many of the n_seqs sequences are not padding, when the caller knows; it decides the variant only)
+  if (G == 1 && decode_two_producers<HD, G>(n_live > 0 && n_live < n_seqs ? n_live : n_seqs, p.n_kv_heads))
+    return launch_decode_variant<HD, 1, true>(p, n_seqs, stream);
   return launch_decode_variant<HD, G, false>(p, n_seqs, stream);
 }
 
-static int dispatch_decode(const DecodeParams& p, int n_seqs, int head_dim, int group, cudaStream_t stream) {
+static int dispatch_decode(const DecodeParams& p, int n_seqs, int n_live, int head_dim, int group, cudaStream_t stream) {
 #define LLMI_DEC(HD, G) \
-  if (head_dim == HD && group == G) return launch_decode<HD, G>(p, n_seqs, stream)
+  if (head_dim == HD && group == G) return launch_decode<HD, G>(p, n_seqs, n_live, stream)
   LLMI_DEC(64, 1); LLMI_DEC(64, 2); LLMI_DEC(64, 3); LLMI_DEC(64, 4); LLMI_DEC(64, 8);
   LLMI_DEC(128, 1); LLMI_DEC(128, 2); LLMI_DEC(128, 3); LLMI_DEC(128, 4); LLMI_DEC(128, 8);
   LLMI_DEC(32, 1); LLMI_DEC(32, 2); LLMI_DEC(32, 4);
@@ -669,7 +671,7 @@ LLMI_EXPORT int llmi_attention_decode(const void* q, long ldq, void* out, long l
                                       const int32_t* seq_kv_len, const int32_t* seq_q_start, int n_seqs, int n_heads,
                                       int n_kv_heads, int head_dim, float scale, int window, int max_pages,
                                       int pages_per_split, float* partials, long partials_floats, int* tickets,
-                                      int n_tickets, int* error_flag, cudaStream_t stream) {
+                                      int n_tickets, int* error_flag, int n_live, cudaStream_t stream) {
   if (n_seqs <= 0 || n_heads <= 0 || n_kv_heads <= 0 || max_pages <= 0 || pages_per_split <= 0) return LLMI_ERR_BAD_SIZE;
   if (n_heads % n_kv_heads) return LLMI_ERR_BAD_SIZE;
   const int group = n_heads / n_kv_heads;
@@ -683,7 +685,7 @@ LLMI_EXPORT int llmi_attention_decode(const void* q, long ldq, void* out, long l
                  (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads,
                  scale * 1.4426950408889634f, window, pages_per_split, splits, partials, tickets, error_flag,
                  0, nullptr, 0, n_heads, 0, nullptr, nullptr};
-  return dispatch_decode(p, n_seqs, head_dim, group, stream);
+  return dispatch_decode(p, n_seqs, n_live, head_dim, group, stream);
 }
 
 // The same with the step's position encoding fused in: `qkv` holds the un-rotated [q | k | v] rows of the
@@ -696,7 +698,7 @@ LLMI_EXPORT int llmi_attention_decode_fused(const void* qkv, long ldq, void* out
                                             int head_dim, float scale, int window, int max_pages, int pages_per_split,
                                             const float* inv_freq, int rotary_dim, int write_kv, float* partials,
                                             long partials_floats, int* tickets, int n_tickets, int* error_flag,
-                                            cudaStream_t stream) {
+                                            int n_live, cudaStream_t stream) {
   if (n_seqs <= 0 || n_heads <= 0 || n_kv_heads <= 0 || max_pages <= 0 || pages_per_split <= 0) return LLMI_ERR_BAD_SIZE;
   if (n_heads % n_kv_heads) return LLMI_ERR_BAD_SIZE;
   const int group = n_heads / n_kv_heads;
@@ -711,7 +713,7 @@ LLMI_EXPORT int llmi_attention_decode_fused(const void* qkv, long ldq, void* out
                  (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads,
                  scale * 1.4426950408889634f, window, pages_per_split, splits, partials, tickets, error_flag,
                  1, inv_freq, rotary_dim, n_heads, write_kv ? 1 : 0, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache};
-  return dispatch_decode(p, n_seqs, head_dim, group, stream);
+  return dispatch_decode(p, n_seqs, n_live, head_dim, group, stream);
 }
 
 // Blocks of the kernel that a step of n_seqs sequences would run that are resident at once, and whether that is the
@@ -798,7 +800,7 @@ LLMI_EXPORT int llmi_attention_decode_static(const void* q, long ldq, void* out,
                  (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads,
                  scale * 1.4426950408889634f, window, pages_per_split, splits, sc->partials, sc->tickets, &sc->error,
                  0, nullptr, 0, n_heads, 0, nullptr, nullptr};
-  const int rc = dispatch_decode(p, n_seqs, head_dim, group, stream);
+  const int rc = dispatch_decode(p, n_seqs, 0, head_dim, group, stream);
   if (rc != LLMI_OK) return rc;
   if (error_out && cudaMemcpyAsync(error_out, &sc->error, sizeof(int), cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
     return LLMI_ERR_LAUNCH;

@@ -73,9 +73,9 @@ class DecodeGraphs:
         if self._last is not None and self._last[0]() is None:
             self._last = None        # its context holds the dead cache's groups
 
-    def _key(self, B, P, choice, cache):
+    def _key(self, B, P, choice, cache, plan=()):
         m = self.model
-        return (B, P, choice, cache.serial, m.rt.generation, m.buffers.dev.data_ptr())
+        return (B, P, choice, cache.serial, m.rt.generation, m.buffers.dev.data_ptr(), plan)
 
     def step(self, cache, seqs, sampler, streams=None):
         """A decode step (one token per sequence) followed by the choice; returns device int32 ids
@@ -116,17 +116,18 @@ class DecodeGraphs:
         m._last_h2d = ctx.h2d_bytes
         sampler.prepare(B, streams)
         choice = (sampler.params.temperature, sampler.params.top_k, sampler.params.top_p)
-        key = self._key(B, P, choice, cache)
+        plan = m.step_plan_token(ctx, cache)      # (a decode kernel's split follows the live sequences)
+        key = self._key(B, P, choice, cache, plan)
         entry = self.graphs.get(key)
         if entry is None:
             # first time for this shape: run it plainly (this also sizes every scratch buffer), then record
             logits = m.run(ctx, cache)
             ids = sampler.launch(logits, B)
             m.last_logits = logits[:n_real]
-            key = self._key(B, P, choice, cache)     # the plain run may have grown a scratch buffer
+            key = self._key(B, P, choice, cache, plan)     # the plain run may have grown a scratch buffer
             if RECORD and key not in self.graphs:
                 # graphs of shapes recorded before a buffer moved can never be replayed again
-                for stale in [k for k in self.graphs if k[3] == cache.serial and k[4:] != key[4:]]:
+                for stale in [k for k in self.graphs if k[3] == cache.serial and k[4:6] != key[4:6]]:
                     del self.graphs[stale]
                     self.kernels_per_graph.pop(stale, None)
                 if cache.serial not in self._watched:

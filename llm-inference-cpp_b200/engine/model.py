@@ -105,7 +105,23 @@ class Model:
             bindings.append(CacheBinding(group, idx, writes=call.cache_of is None))
         cache.bindings = bindings
         cache.owner = self
+        # the (mixer, binding) pairs whose launches may depend on more than a step's padded shape, one of a kind
+        planners = {}
+        for call, binding in zip(self.spec.schedule, bindings):
+            mixer = self.layers[call.layer].mixer
+            if hasattr(mixer, "step_plan"):
+                planners.setdefault((id(binding.group), mixer.cache_request(), getattr(mixer, "n_heads", None)),
+                                    (mixer, binding))
+        cache.planners = list(planners.values())
         return cache
+
+    def step_plan_token(self, ctx, cache) -> tuple:
+        """What a recorded step depends on beside its padded shape: the mixers' own plans for this step (a decode
+        kernel's split follows the live sequences)."""
+        token = getattr(ctx, "plan_token", None)      # a context that is continued keeps its sizes, so its token too
+        if token is None:
+            token = ctx.plan_token = tuple(m.step_plan(ctx, b) for m, b in getattr(cache, "planners", ()))
+        return token
 
     # -- the step --------------------------------------------------------------------------
     def step(self, cache: SequenceCache, seqs, pad_seqs_to: int = 0, pad_pages_to: int = 0,

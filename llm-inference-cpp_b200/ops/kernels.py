@@ -525,6 +525,42 @@ def decode_pages_per_split(n_seqs: int, n_kv_heads: int, max_pages: int, head_di
     return best
 
 
+_PLAN_BY_LIVE = os.environ.get("LLMI_DECODE_PLAN", "live") != "padded"
+_plan_cache: dict = {}
+
+
+def decode_plan(ctx, n_seqs: int, n_pages: int, page_size: int, n_kv_heads: int, head_dim: int, group: int):
+    """(pages per item, live sequences) for the decode kernel of a step whose page tables are [n_seqs, n_pages].
+
+    A recorded step is padded to a power of two of sequences.  The kernel skips the padding, but a split chosen for
+    16 sequences is a poor one for 9 or 12: so the split (and the kernel's variant) follow the step's LIVE sequences
+    (:func:`decode_plan_token` tells recorded steps with different answers apart).  Measured, a decode step of 32
+    heads of 64 at 4,096 positions, planned by the padded and by the live number: batch 3 1.334 -> 1.291 ms, 5
+    1.754 -> 1.597, 9 2.145 -> 2.025, 12 2.594 -> 2.403, 24 4.264 -> 4.165; 14 and 40 unchanged.  The page tables'
+    padded width stays the measure of length: following the live pages too changed the split every few hundred
+    tokens (a new recording each time) for no gain at batch 1 to 3.  ``LLMI_DECODE_PLAN=padded`` plans by the
+    padded number."""
+    n_live = n_seqs
+    if _PLAN_BY_LIVE:
+        n_live = min(n_seqs, max(1, int(getattr(ctx, "n_real_seqs", 0) or n_seqs)))
+    key = (n_live, n_pages, n_kv_heads, head_dim, group)
+    pps = _plan_cache.get(key)
+    if pps is None:
+        pps = _plan_cache[key] = decode_pages_per_split(n_live, n_kv_heads, n_pages, head_dim, group)
+    return pps, n_live
+
+
+def decode_plan_token(ctx, n_seqs: int, n_pages: int, page_size: int, n_kv_heads: int, head_dim: int, group: int):
+    """What tells two recorded decode steps of the same padded shape apart: the split and the kernel's variant."""
+    pps, n_live = decode_plan(ctx, n_seqs, n_pages, page_size, n_kv_heads, head_dim, group)
+    if decode_uses_mma(head_dim, group):
+        return (pps,)
+    key = (head_dim, group, n_live, n_kv_heads)
+    if key not in _resident_cache:
+        decode_pages_per_split(n_live, n_kv_heads, n_pages, head_dim, group)
+    return (pps, _resident_cache[key][1])
+
+
 def attention_decode_supported(head_dim: int, group: int) -> bool:
     return decode_uses_mma(head_dim, group) or bool(lib().llmi_attention_decode_supported(c_int(head_dim), c_int(group)))
 
@@ -553,10 +589,11 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, s
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start,
                      n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int, partials: torch.Tensor,
-                     pages_per_split: int = DECODE_PAGES_PER_SPLIT) -> None:
+                     pages_per_split: int = DECODE_PAGES_PER_SPLIT, n_live: int = 0) -> None:
     """One token per sequence over its cache pages (bf16, page size 64), split over positions.
 
-    ``partials``: fp32 scratch of at least ``attention_decode_workspace(...)`` floats.
+    ``partials``: fp32 scratch of at least ``attention_decode_workspace(...)`` floats.  ``n_live``: how many of
+    the sequences are not padding, if the caller knows (it decides which variant of the kernel runs, nothing else).
     """
     _need_cuda(q, out, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start, partials)
     S, P = seq_pages.shape
@@ -567,7 +604,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_p
         _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(seq_pages),
         c_int(seq_pages.stride(0)), _ptr(seq_kv_len), _ptr(seq_q_start), c_int(S), c_int(n_heads), c_int(n_kv_heads),
         c_int(head_dim), c_float(scale), c_int(window), c_int(P), c_int(pages_per_split), _ptr(partials),
-        c_long(partials.numel()), _ptr(sc.attn_tickets), c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), _stream()))
+        c_long(partials.numel()), _ptr(sc.attn_tickets), c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), c_int(n_live), _stream()))
 
 
 def attention_decode_workspace(n_seqs: int, n_heads: int, head_dim: int, max_pages: int,
@@ -652,7 +689,7 @@ _PREFILL_SPLIT = os.environ.get("LLMI_PREFILL_SPLIT", "1") != "0"
 
 def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start,
                            n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int, partials: torch.Tensor,
-                           pages_per_split: int, inv_freq, rotary_dim: int, write_kv: bool) -> None:
+                           pages_per_split: int, inv_freq, rotary_dim: int, write_kv: bool, n_live: int = 0) -> None:
     """:func:`attention_decode` with the step's position encoding done by the same kernel: ``qkv`` holds the
     un-rotated [q | k | v] row of each sequence's token; the new k (rotated) and v are appended to the cache."""
     _need_cuda(qkv, out, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start, partials)
@@ -666,7 +703,7 @@ def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cach
         c_int(seq_pages.stride(0)), _ptr(seq_kv_len), _ptr(seq_q_start), c_int(S), c_int(n_heads), c_int(n_kv_heads),
         c_int(head_dim), c_float(scale), c_int(window), c_int(P), c_int(pages_per_split),
         _ptr(inv_freq) if rotary_dim else None, c_int(rotary_dim), c_int(1 if write_kv else 0), _ptr(partials),
-        c_long(partials.numel()), _ptr(sc.attn_tickets), c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), _stream()))
+        c_long(partials.numel()), _ptr(sc.attn_tickets), c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), c_int(n_live), _stream()))
 
 
 _FUSE_ROPE = os.environ.get("LLMI_FUSE_ROPE", "1") != "0"
@@ -696,17 +733,17 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
     """
     if _decode_kernel_applies(qkv, ctx, seq_pages, page_size, n_heads, n_kv_heads, head_dim, rt):
         S, P = seq_pages.shape
-        pps = decode_pages_per_split(S, n_kv_heads, P, head_dim, n_heads // n_kv_heads)
+        pps, n_live = decode_plan(ctx, S, P, page_size, n_kv_heads, head_dim, n_heads // n_kv_heads)
         partials = rt.scratch("attn_partials", (attention_decode_workspace(S, n_heads, head_dim, P, pps),), torch.float32)
         if decode_uses_mma(head_dim, n_heads // n_kv_heads):
             attention_decode_mma(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_kv_len, ctx.seq_q_start, n_heads,
                                  n_kv_heads, head_dim, scale, window, partials, pps, rope)
         elif rope is not None:
             attention_decode_fused(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_kv_len, ctx.seq_q_start, n_heads,
-                                   n_kv_heads, head_dim, scale, window, partials, pps, rope[0], rope[1], rope[2])
+                                   n_kv_heads, head_dim, scale, window, partials, pps, rope[0], rope[1], rope[2], n_live)
         else:
             attention_decode(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_kv_len, ctx.seq_q_start, n_heads, n_kv_heads,
-                             head_dim, scale, window, partials, pps)
+                             head_dim, scale, window, partials, pps, n_live)
         return
     if rope is not None:
         raise RuntimeError("attention: rotation can only be fused into the decode kernel (ask attention_fuses_rotation)")

@@ -66,6 +66,18 @@ class GQAttention:
         the products treat rows alone — if the position part agrees."""
         return bool(getattr(self.position, "takes_padding_rows", False))
 
+    def step_plan(self, ctx, binding):
+        """What of this step's launches depends on more than the step's padded shape (a recorded step is replayed
+        only for a step with the same answer): the decode kernel's split and variant."""
+        if not ctx.decode or self.rt.dtype != torch.bfloat16:
+            return None
+        g = binding.group
+        S, P = ctx.pages_of(g).shape
+        nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        if g.page_size != 64 or not kernels.attention_decode_supported(hd, nh // nkv):
+            return None
+        return kernels.decode_plan_token(ctx, S, P, g.page_size, nkv, hd, nh // nkv)
+
     def forward(self, h, x, ctx, binding, then_norm=None) -> bool:
         T = h.shape[0]
         nh, nkv, hd = self.n_heads, self.n_kv_heads, self.head_dim

@@ -324,3 +324,54 @@ def test_one_model_many_caches_of_different_sizes(model_dirs):
         gc.collect()
         serials = {k[3] for k in model._graphs.graphs}
         assert len(serials) <= 1, "graphs of dead caches must be dropped"
+
+
+MANY_HEADS = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 1, "hidden_size": 128, "num_attention_heads": 32,
+              "num_key_value_heads": 32, "head_dim": 64, "intermediate_size": 192, "vocab_size": 320, "rope_theta": 10000.0,
+              "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 1024, "hidden_act": "silu"}
+
+
+def test_recorded_decode_steps_of_one_shape_are_told_apart_by_their_plan(tmp_path):
+    """16, then 9, then 5 live sequences: the first two are padded to the same shape (16), but their decode kernels
+    are cut into items differently (9 x 32 sequence-heads fit the variant with whole sequence-heads as items, 16 x 32
+    do not), so they are recorded apart; every step's logits are the plain implementation's."""
+    import torch
+    import helpers as H
+    import llmi_b200 as L
+    from llmi_b200.ops import kernels
+    from llmi_b200.sampling import Sampler
+    d = str(tmp_path)
+    L.write_random_model(d, MANY_HEADS, 3, torch.bfloat16)
+    cfg, w = P.read_model(d)
+    model = L.load(d, "bfloat16")
+    V = cfg["vocab_size"]
+    rng = np.random.default_rng(5)
+    n_seqs, prompt, steps = 16, 250, 9          # the decode steps cross a page's end (256)
+    toks = [rng.integers(0, V, prompt + steps).tolist() for _ in range(n_seqs)]
+    refs = [P.forward(cfg, w, t) for t in toks]
+    sampler = Sampler(L.SamplingParams(), model.rt)
+    cache = model.new_cache(n_seqs * 320, n_slots=16)
+    slots = [cache.alloc_slot() for _ in toks]
+    model.step(cache, [L.SequenceStep(s, t[:prompt], []) for s, t in zip(slots, toks)])
+    live, fed, tokens_seen = list(range(n_seqs)), prompt, set()
+    for step in range(steps):
+        if step == 3:
+            for i in live[9:]:
+                cache.free_slot(slots[i])
+            live = live[:9]
+        if step == 6:
+            for i in live[5:]:
+                cache.free_slot(slots[i])
+            live = live[:5]
+        model.step_and_choose(cache, [L.SequenceStep(slots[i], [toks[i][fed]], [0]) for i in live], sampler)
+        logits = model.last_logits.cpu().numpy()
+        for row, i in enumerate(live):
+            assert H.rel_to_max(logits[row], refs[i][fed]) < H.TOL["bfloat16"], (step, i)
+        fed += 1
+        tokens_seen.add((len(live), model.step_plan_token(model._graphs._last[2], cache)))
+    cache.check()
+    plans = {n: t for n, t in tokens_seen}
+    assert len(tokens_seen) == 3 and plans[16] != plans[9], plans       # 16 and 9 share a padded shape, not a plan
+    keys = [k for k in model._graphs.graphs if k[0] == 16]
+    assert len({k[-1] for k in keys}) == 2, keys
+    assert model._graphs.replays >= 3
