@@ -37,6 +37,11 @@ back to the plain path.
                residual-adding product) and returns whether it filled it.
 ``block``      property ``entry_norm`` (the norm it applies first, if the block before may fill its deferred
                form) and ``forward(x, ctx, binding, entry=None, next_norm=None) -> DeferredNorm | None``.
+``mixer``      ``step_plan(ctx, binding) -> hashable | None``: what the part's launches for this step depend on
+               beside the step's padded shape (its attention kernel's split, which follows the live sequences).
+               A recorded decode step is replayed only for a step whose mixers give the same answers.
+any part       class attribute ``takes_padding_rows = True``: token rows that belong to no sequence (index -1)
+               do it no harm, so its model's short prompt steps may be padded to a shape and replayed.
 """
 from __future__ import annotations
 
