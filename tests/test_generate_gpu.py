@@ -12,6 +12,10 @@ from conftest import ROOT, TINY_CONFIGS
 
 pytestmark = pytest.mark.gpu
 STORAGE = {"float32": "F32", "bfloat16": "BF16"}
+# what the tests say about recorded steps holds with the library's switches at their defaults
+RECORDING = os.environ.get("LLMI_GRAPHS", "1") != "0"
+DEFAULT_DECODE_PLAN = (os.environ.get("LLMI_DECODE_PLAN", "live") != "padded"
+                       and os.environ.get("LLMI_DECODE_VALUE_PRODUCER", "1") != "0")
 
 
 def prompts_for(name, lens, seed=21):
@@ -246,7 +250,8 @@ def test_logits_of_recorded_padded_decode_steps(model_dirs, tmp_path, name, dtyp
                 live.remove(i)
             n_steps += 1
         cache.check()
-        assert model._graphs is not None and model._graphs.replays > 0
+        if RECORDING:
+            assert model._graphs is not None and model._graphs.replays > 0
     assert n_steps == max(t - p for t, p in zip(totals, prompt_lens))
 
 
@@ -305,7 +310,8 @@ def test_logits_of_padded_and_recorded_prompt_steps(model_dirs, tmp_path, name):
                 cache.free_slot(s)
             cache.check()
     g = model._prompt_graphs
-    assert g is not None and g.replays >= 2 * len([b for b in batches if sum(b) <= 1024]), (g.replays, len(g.graphs))
+    if RECORDING:
+        assert g is not None and g.replays >= 2 * len([b for b in batches if sum(b) <= 1024]), (g.replays, len(g.graphs))
 
 
 def test_one_model_many_caches_of_different_sizes(model_dirs):
@@ -370,8 +376,9 @@ def test_recorded_decode_steps_of_one_shape_are_told_apart_by_their_plan(tmp_pat
         fed += 1
         tokens_seen.add((len(live), model.step_plan_token(model._graphs._last[2], cache)))
     cache.check()
-    plans = {n: t for n, t in tokens_seen}
-    assert len(tokens_seen) == 3 and plans[16] != plans[9], plans       # 16 and 9 share a padded shape, not a plan
-    keys = [k for k in model._graphs.graphs if k[0] == 16]
-    assert len({k[-1] for k in keys}) == 2, keys
-    assert model._graphs.replays >= 3
+    if RECORDING and DEFAULT_DECODE_PLAN:
+        plans = {n: t for n, t in tokens_seen}
+        assert len(tokens_seen) == 3 and plans[16] != plans[9], plans       # 16 and 9 share a padded shape, not a plan
+        keys = [k for k in model._graphs.graphs if k[0] == 16]
+        assert len({k[-1] for k in keys}) == 2, keys
+        assert model._graphs.replays >= 3

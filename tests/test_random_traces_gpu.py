@@ -4,6 +4,8 @@ or portions of them, go on by 1, 2, 7, 63, 64, 65, 100 or 300 tokens or by one t
 leave their slots to the next — against the plain implementation, in both types, over a cache whose pages start out
 as NaN.  Each trace runs three times over, so that in bfloat16 the padded prompt steps come again, are recorded and
 replayed (GPU)."""
+import os
+
 import numpy as np
 import pytest
 
@@ -81,5 +83,5 @@ def test_random_configuration_and_trace(tmp_path, seed, dtype):
             assert off == out.shape[0]
         rp.cache.check()
         assert not rp.slots
-    if dtype == "bfloat16" and model.pads_prompts:
+    if dtype == "bfloat16" and model.pads_prompts and os.environ.get("LLMI_GRAPHS", "1") != "0":
         assert model._prompt_graphs is not None and model._prompt_graphs.replays > 0
