@@ -101,6 +101,8 @@ __device__ __forceinline__ void bf16x8_to_f32(const uint4& raw, float* f) {
   }
 }
 
+constexpr int DEC_MAX_CLUSTER = 8;
+
 struct DecItem {
   int seq, kvh, part, n_parts, lo, pos, pg0, n_pages, tok;
 };
@@ -111,15 +113,25 @@ struct DecItem {
 // warp takes a finished item's merged (max, sum, values) from shared memory and does the slow,
 // latency-bound part — partial to the workspace, fence, ticket, and the final merge if it drew the
 // last ticket — while the consumers are already on the next item.
-template <int HD, int G, bool VP>
+//
+// CL: the kernel is launched as clusters of p.max_splits blocks (2, 4 or 8), one block per item and one cluster
+// per sequence-head, all resident at once.  A block sends its split's (values, maximum, sum) into the shared memory
+// of the cluster's first block, which adds them in split order and writes the head's output: no partial results
+// in global memory, no fence, no ticket, no round trips to L2 behind the last page.  For few sequence-heads, where
+// the kernel is as long as that chain, not as its bytes (batch 1, 4,096 positions: 10 us for 33 MB).
+template <int HD, int G, bool VP, bool CL = false>
 __global__ void __launch_bounds__(DecThreads<VP>::value)
 attention_decode_kernel(DecodeParams p, int n_items) {
   using C = DecCfg<HD, VP>;
   static_assert(C::LPR >= 2 && C::LPR <= 32 && C::NI >= 1, "head size not supported by this layout");
+  static_assert(!(VP && CL), "the cluster form has one producer thread");
   extern __shared__ uint8_t smem_raw[];
   __shared__ float s_m[DEC_CONSUMERS][G], s_l[DEC_CONSUMERS][G];
   __shared__ float s_acc[DEC_CONSUMERS][G][HD];
   __shared__ float r_buf[2][G][HD + 2];     // merged results on their way to the epilogue warp
+  __shared__ float cl_recv[CL ? DEC_MAX_CLUSTER : 1][CL ? G : 1][CL ? HD + 2 : 1];   // first block of a cluster: the splits' results
+  __shared__ __align__(8) uint64_t cl_bar_word;
+  const uint32_t cl_bar = smem_u32(&cl_bar_word);
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -140,9 +152,11 @@ attention_decode_kernel(DecodeParams p, int n_items) {
       mbar_init(rfull_bar(b), 1);
       mbar_init(rempty_bar(b), 1);
     }
+    if (CL) mbar_init(cl_bar, cluster_size());     // every block of the cluster arrives once, the first included
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  if (CL) cluster_sync_all();     // nobody arrives on the first block's barrier before it is set up
 
   // The first non-empty item at or after `item` in this block's sequence of items (stride gridDim.x);
   // returns n_items when there is none.  Every warp role walks the same sequence.
@@ -275,6 +289,7 @@ attention_decode_kernel(DecodeParams p, int n_items) {
 
   if (warp == DEC_CONSUMERS + 1) {
     // ---- epilogue warp: items cut into several splits pass through here ----
+    if (CL) return;               // (a cluster's results meet in its first block's shared memory instead)
     int n_split_items = 0;
     DecItem d;
     pdl_wait();
@@ -381,7 +396,7 @@ attention_decode_kernel(DecodeParams p, int n_items) {
   const int c = lane % C::LPR, r = lane / C::LPR;
   const int ctid = threadIdx.x;   // 0..127
   int it = 0, n_split_items = 0;
-  bool ok = true;
+  bool ok = true, sent = false;
   DecItem d, dn;
   int item = next_item(blockIdx.x, d);
   uint4 q_raw[G], q_next[G];
@@ -537,7 +552,7 @@ attention_decode_kernel(DecodeParams p, int n_items) {
     // merge the four consumer warps (fixed order); a whole sequence-head is written at once, a split
     // goes to the epilogue warp
     const int b = n_split_items & 1;
-    if (d.n_parts > 1) {
+    if (!CL && d.n_parts > 1) {
       if (n_split_items >= 2) ok = mbar_wait(rempty_bar(b), ((n_split_items >> 1) - 1) & 1, p.error_flag, 14);
       if (!ok) break;
     }
@@ -553,7 +568,15 @@ attention_decode_kernel(DecodeParams p, int n_items) {
         L += s_l[w][g] * f;
         A += s_acc[w][g][dd] * f;
       }
-      if (d.n_parts == 1) {
+      if (CL) {
+        // to the cluster's first block, into the row of this block's rank
+        const uint32_t dst = map_to_rank(smem_u32(&cl_recv[cluster_rank()][g][0]), 0);
+        st_cluster_f32(dst + 4u * dd, A);
+        if (dd == 0) {
+          st_cluster_f32(dst + 4u * HD, M);
+          st_cluster_f32(dst + 4u * (HD + 1), L);
+        }
+      } else if (d.n_parts == 1) {
         p.out[(size_t)d.tok * p.ldo + (size_t)(d.kvh * G + g) * HD + dd] = __float2bfloat16_rn(A / L);
       } else {
         r_buf[b][g][dd] = A;
@@ -564,7 +587,9 @@ attention_decode_kernel(DecodeParams p, int n_items) {
       }
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");   // r_buf is complete; s_m / s_acc are free again
-    if (d.n_parts > 1) {
+    if (CL) {
+      sent = true;
+    } else if (d.n_parts > 1) {
       if (ctid == 0) mbar_arrive(rfull_bar(b));
       ++n_split_items;
     }
@@ -572,6 +597,40 @@ attention_decode_kernel(DecodeParams p, int n_items) {
     d = dn;
 #pragma unroll
     for (int g = 0; g < G; ++g) q_raw[g] = q_next[g];
+  }
+  if (CL) {
+    // One item a block.  A block whose split holds nothing of its sequence (or whose sequence is padding, or whose
+    // wait gave up) sends an empty result, so that the first block always hears from the whole cluster.
+    const uint32_t rank = cluster_rank(), n_ranks = cluster_size();
+    if (!sent) {
+      const uint32_t dst = map_to_rank(smem_u32(&cl_recv[rank][0][0]), 0);
+      for (int idx = ctid; idx < G * (HD + 2); idx += DEC_CONSUMERS * 32) {
+        const int dd = idx % (HD + 2);
+        st_cluster_f32(dst + 4u * idx, dd == HD ? -INFINITY : 0.f);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+    if (ctid == 0) mbar_arrive_remote(map_to_rank(cl_bar, 0));   // (after the bar.sync: the block's stores come first)
+    if (rank != 0) return;
+    if (!mbar_wait_cluster(cl_bar, 0, p.error_flag, 17)) return;
+    // the sequence-head of this cluster (the first block's own split may be empty: not from `d`)
+    const int sh = blockIdx.x / p.max_splits;
+    const int kvh = sh % p.n_kv_heads, seq = sh / p.n_kv_heads;
+    if (p.seq_kv_len[seq] <= 0) return;                            // padding sequence
+    const int tok = p.seq_q_start[seq];
+    for (int idx = ctid; idx < G * HD; idx += DEC_CONSUMERS * 32) {
+      const int g = idx / HD, dd = idx - g * HD;
+      float M = -INFINITY;
+      for (uint32_t z = 0; z < n_ranks; ++z) M = fmaxf(M, cl_recv[z][g][HD]);
+      float L = 0.f, A = 0.f;
+      for (uint32_t z = 0; z < n_ranks; ++z) {                     // in split order
+        const float mz = cl_recv[z][g][HD];
+        const float w = (mz == -INFINITY) ? 0.f : fast_exp2(mz - M);
+        L = fmaf(cl_recv[z][g][HD + 1], w, L);
+        A = fmaf(w, cl_recv[z][g][dd], A);
+      }
+      p.out[(size_t)tok * p.ldo + (size_t)(kvh * G + g) * HD + dd] = __float2bfloat16_rn(A / L);
+    }
   }
 }
 
@@ -611,6 +670,62 @@ int launch_decode_variant(const DecodeParams& p, int n_seqs, cudaStream_t stream
                     (int)n_items);
 }
 
+// The cluster form: clusters of `cluster` blocks, one block per item.
+template <int HD>
+int launch_decode_cluster(const DecodeParams& p, int n_seqs, int cluster, cudaStream_t stream) {
+  using C = DecCfg<HD, false>;
+  static PerDevice<bool> configured_on;
+  bool& configured = configured_on.here();
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_decode_kernel<HD, 1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             C::SMEM_BYTES) != cudaSuccess)
+      return LLMI_ERR_LAUNCH;
+    configured = true;
+  }
+  const long n_items = (long)n_seqs * p.n_kv_heads * cluster;
+  if (n_items > 0x7fffffffL) return LLMI_ERR_BAD_SIZE;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)n_items);
+  cfg.blockDim = dim3(DecThreads<false>::value);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = pdl_enabled(PDL_ATTENTION) ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  return cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD, 1, false, true>, p, (int)n_items) == cudaSuccess ? LLMI_OK
+                                                                                                              : LLMI_ERR_LAUNCH;
+}
+
+// How many clusters of `cluster` blocks of the cluster form the device holds at once (0: none, or no such kernel).
+template <int HD>
+int decode_clusters_resident(int cluster) {
+  using C = DecCfg<HD, false>;
+  cudaFuncSetAttribute(attention_decode_kernel<HD, 1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(cluster * 1024));
+  cfg.blockDim = dim3(DecThreads<false>::value);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, attention_decode_kernel<HD, 1, false, true>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
 // The variant with a producer of its own for the value tiles: ungrouped queries (the grouped ones have the tensor-core
 // kernel) and between half as many and as many sequence-heads as its blocks hold at once.
 template <int HD, int G>
@@ -628,16 +743,24 @@ bool decode_two_producers(int n_seqs, int n_kv_heads) {
 }
 
 template <int HD, int G>
-int launch_decode(const DecodeParams& p, int n_seqs, int n_live, cudaStream_t stream) {
+int launch_decode(const DecodeParams& p, int n_seqs, int n_live, int cluster, cudaStream_t stream) {
+  if (cluster) {
+    // (the clusters' blocks number the splits: those beyond the page tables' width find nothing to do)
+    if (G != 1 || (cluster != 2 && cluster != 4 && cluster != 8) || p.max_splits > cluster) return LLMI_ERR_BAD_SIZE;
+    DecodeParams q = p;
+    q.max_splits = cluster;
+    return launch_decode_cluster<HD>(q, n_seqs, cluster, stream);
+  }
   // (n_live: how many of the n_seqs sequences are not padding, when the caller knows; it decides the variant only)
   if (G == 1 && decode_two_producers<HD, G>(n_live > 0 && n_live < n_seqs ? n_live : n_seqs, p.n_kv_heads))
     return launch_decode_variant<HD, 1, true>(p, n_seqs, stream);
   return launch_decode_variant<HD, G, false>(p, n_seqs, stream);
 }
 
-static int dispatch_decode(const DecodeParams& p, int n_seqs, int n_live, int head_dim, int group, cudaStream_t stream) {
+static int dispatch_decode(const DecodeParams& p, int n_seqs, int n_live, int cluster, int head_dim, int group,
+                           cudaStream_t stream) {
 #define LLMI_DEC(HD, G) \
-  if (head_dim == HD && group == G) return launch_decode<HD, G>(p, n_seqs, n_live, stream)
+  if (head_dim == HD && group == G) return launch_decode<HD, G>(p, n_seqs, n_live, cluster, stream)
   LLMI_DEC(64, 1); LLMI_DEC(64, 2); LLMI_DEC(64, 3); LLMI_DEC(64, 4); LLMI_DEC(64, 8);
   LLMI_DEC(128, 1); LLMI_DEC(128, 2); LLMI_DEC(128, 3); LLMI_DEC(128, 4); LLMI_DEC(128, 8);
   LLMI_DEC(32, 1); LLMI_DEC(32, 2); LLMI_DEC(32, 4);
@@ -671,7 +794,7 @@ LLMI_EXPORT int llmi_attention_decode(const void* q, long ldq, void* out, long l
                                       const int32_t* seq_kv_len, const int32_t* seq_q_start, int n_seqs, int n_heads,
                                       int n_kv_heads, int head_dim, float scale, int window, int max_pages,
                                       int pages_per_split, float* partials, long partials_floats, int* tickets,
-                                      int n_tickets, int* error_flag, int n_live, cudaStream_t stream) {
+                                      int n_tickets, int* error_flag, int n_live, int cluster, cudaStream_t stream) {
   if (n_seqs <= 0 || n_heads <= 0 || n_kv_heads <= 0 || max_pages <= 0 || pages_per_split <= 0) return LLMI_ERR_BAD_SIZE;
   if (n_heads % n_kv_heads) return LLMI_ERR_BAD_SIZE;
   const int group = n_heads / n_kv_heads;
@@ -685,7 +808,7 @@ LLMI_EXPORT int llmi_attention_decode(const void* q, long ldq, void* out, long l
                  (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads,
                  scale * 1.4426950408889634f, window, pages_per_split, splits, partials, tickets, error_flag,
                  0, nullptr, 0, n_heads, 0, nullptr, nullptr};
-  return dispatch_decode(p, n_seqs, n_live, head_dim, group, stream);
+  return dispatch_decode(p, n_seqs, n_live, cluster, head_dim, group, stream);
 }
 
 // The same with the step's position encoding fused in: `qkv` holds the un-rotated [q | k | v] rows of the
@@ -698,7 +821,7 @@ LLMI_EXPORT int llmi_attention_decode_fused(const void* qkv, long ldq, void* out
                                             int head_dim, float scale, int window, int max_pages, int pages_per_split,
                                             const float* inv_freq, int rotary_dim, int write_kv, float* partials,
                                             long partials_floats, int* tickets, int n_tickets, int* error_flag,
-                                            int n_live, cudaStream_t stream) {
+                                            int n_live, int cluster, cudaStream_t stream) {
   if (n_seqs <= 0 || n_heads <= 0 || n_kv_heads <= 0 || max_pages <= 0 || pages_per_split <= 0) return LLMI_ERR_BAD_SIZE;
   if (n_heads % n_kv_heads) return LLMI_ERR_BAD_SIZE;
   const int group = n_heads / n_kv_heads;
@@ -713,7 +836,7 @@ LLMI_EXPORT int llmi_attention_decode_fused(const void* qkv, long ldq, void* out
                  (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads,
                  scale * 1.4426950408889634f, window, pages_per_split, splits, partials, tickets, error_flag,
                  1, inv_freq, rotary_dim, n_heads, write_kv ? 1 : 0, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache};
-  return dispatch_decode(p, n_seqs, n_live, head_dim, group, stream);
+  return dispatch_decode(p, n_seqs, n_live, cluster, head_dim, group, stream);
 }
 
 // Blocks of the kernel that a step of n_seqs sequences would run that are resident at once, and whether that is the
@@ -728,6 +851,15 @@ LLMI_EXPORT int llmi_attention_decode_plan(int head_dim, int group, int n_seqs, 
   LLMI_DEC(64); LLMI_DEC(128); LLMI_DEC(32);
 #undef LLMI_DEC
   return llmi_attention_decode_resident(head_dim, group);
+}
+
+// Clusters of `cluster` blocks of the cluster form (ungrouped queries only) that the device holds at once; 0 if none.
+LLMI_EXPORT int llmi_attention_decode_clusters_resident(int head_dim, int group, int cluster) {
+  if (group != 1 || (cluster != 2 && cluster != 4 && cluster != 8)) return 0;
+  if (head_dim == 64) return decode_clusters_resident<64>(cluster);
+  if (head_dim == 128) return decode_clusters_resident<128>(cluster);
+  if (head_dim == 32) return decode_clusters_resident<32>(cluster);
+  return 0;
 }
 
 LLMI_EXPORT int llmi_attention_decode_resident(int head_dim, int group) {
@@ -800,7 +932,7 @@ LLMI_EXPORT int llmi_attention_decode_static(const void* q, long ldq, void* out,
                  (const __nv_bfloat16*)v_cache, seq_pages, seq_kv_len, seq_q_start, pages_stride, n_kv_heads,
                  scale * 1.4426950408889634f, window, pages_per_split, splits, sc->partials, sc->tickets, &sc->error,
                  0, nullptr, 0, n_heads, 0, nullptr, nullptr};
-  const int rc = dispatch_decode(p, n_seqs, 0, head_dim, group, stream);
+  const int rc = dispatch_decode(p, n_seqs, 0, 0, head_dim, group, stream);
   if (rc != LLMI_OK) return rc;
   if (error_out && cudaMemcpyAsync(error_out, &sc->error, sizeof(int), cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
     return LLMI_ERR_LAUNCH;

@@ -83,6 +83,38 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr));
   return v;
 }
+// an arrive on an mbarrier of another CTA of the cluster (its address from map_to_rank); what this thread wrote, or
+// saw written, before is visible to whoever waits on that barrier with mbar_wait_cluster
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+// mbar_wait for a barrier that other CTAs of the cluster arrive on after plain stores into this CTA's shared memory
+// (acquire at cluster scope); bounded like mbar_wait
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* error_flag, int code) {
+  uint32_t done = 0;
+  uint64_t t0 = 0;
+  for (uint32_t spins = 0;; ++spins) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if ((spins & 1023u) == 1023u) {
+      const uint64_t now = global_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 1000000000ull) {
+        if (error_flag) atomicCAS(error_flag, 0, code);
+        return false;
+      }
+    }
+  }
+}
 // every thread of every CTA of the cluster arrives and waits (what was written to shared memory before is
 // visible to the cluster's other CTAs after)
 __device__ __forceinline__ void cluster_sync_all() {

@@ -131,8 +131,5 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {   // arrives on
                ::"r"(bar), "h"((uint16_t)3)
                : "memory");
 }
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
 
 }  // namespace llmi

@@ -147,7 +147,7 @@ def lib():
                      "llmi_attention_generic", "llmi_argmax", "llmi_sample", "llmi_gemm_tc", "llmi_gemm_tc_splits",
                      "llmi_attention_decode", "llmi_attention_decode_supported", "llmi_attention_decode_resident",
                      "llmi_attention_decode_fused", "llmi_attention_decode_mma", "llmi_attention_decode_mma_supported",
-                     "llmi_attention_decode_mma_resident",
+                     "llmi_attention_decode_mma_resident", "llmi_attention_decode_clusters_resident",
                      "llmi_attention_prefill", "llmi_attention_prefill_supported", "llmi_gemm_skinny",
                      "llmi_gemm_skinny_max_tokens", "llmi_attention_prefill_tc", "llmi_attention_prefill_tc_supported",
                      "llmi_sm_count"):
@@ -544,21 +544,55 @@ def decode_plan(ctx, n_seqs: int, n_pages: int, page_size: int, n_kv_heads: int,
     if _PLAN_BY_LIVE:
         n_live = min(n_seqs, max(1, int(getattr(ctx, "n_real_seqs", 0) or n_seqs)))
     key = (n_live, n_pages, n_kv_heads, head_dim, group)
-    pps = _plan_cache.get(key)
-    if pps is None:
-        pps = _plan_cache[key] = decode_pages_per_split(n_live, n_kv_heads, n_pages, head_dim, group)
-    return pps, n_live
+    plan = _plan_cache.get(key)
+    if plan is None:
+        pps = decode_pages_per_split(n_live, n_kv_heads, n_pages, head_dim, group)
+        cluster = decode_cluster(n_live, n_kv_heads, n_pages, head_dim, group) if pps < n_pages else 0
+        if cluster:
+            pps = -(-n_pages // cluster)
+        plan = _plan_cache[key] = (pps, cluster)
+    return plan[0], n_live, plan[1]
+
+
+_CLUSTER = os.environ.get("LLMI_DECODE_CLUSTER", "1") != "0"
+_CLUSTER_MAX_PAGES = int(os.environ.get("LLMI_DECODE_CLUSTER_PAGES", "4"))
+_clusters_resident: dict = {}
+
+
+def decode_cluster(n_live: int, n_kv_heads: int, n_pages: int, head_dim: int, group: int) -> int:
+    """The size of the clusters (8, 4 or 2 blocks, one cluster per sequence-head) in which the decode kernel runs a
+    step of few sequence-heads and short sequences, or 0 for its persistent form: the largest size whose clusters are
+    all resident at once and give a block two to four pages (``LLMI_DECODE_CLUSTER_PAGES``).  Ungrouped queries on the
+    CUDA-core kernel only.  With so few pages a block the kernel is as long as the chain behind its last page —
+    partial result to memory, fence, ticket, the last block's loads of all partial results — and the clusters replace
+    that chain by stores into the first block's shared memory.  A decode step of 32 heads of 64 (24 layers, 2,048
+    wide), persistent form -> clusters: batch 1 at 512 / 1,024 / 2,048 positions 0.985 -> 0.933 / 0.999 -> 0.964 /
+    1.020 -> 0.995 ms; batch 2 at 512 / 1,024: 0.968 -> 0.941 / 0.997 -> 0.980; batch 4 at 512: 0.994 -> 0.984.  With
+    more pages a block it loses (one producer thread a block, few blocks: batch 1 at 4,096 positions, 8 pages a
+    block: 1.060 -> 1.084 ms; batch 4: 1.402 -> 1.547), so there the persistent form with its shorter items stays.
+    ``LLMI_DECODE_CLUSTER=0`` switches the clusters off."""
+    if not _CLUSTER or group != 1 or decode_uses_mma(head_dim, group):
+        return 0
+    for size in (8, 4, 2):
+        if n_pages < 2 * size or -(-n_pages // size) > _CLUSTER_MAX_PAGES:
+            continue
+        key = (head_dim, size)
+        if key not in _clusters_resident:
+            _clusters_resident[key] = int(lib().llmi_attention_decode_clusters_resident(c_int(head_dim), c_int(group), c_int(size)))
+        if n_live * n_kv_heads <= _clusters_resident[key]:
+            return size
+    return 0
 
 
 def decode_plan_token(ctx, n_seqs: int, n_pages: int, page_size: int, n_kv_heads: int, head_dim: int, group: int):
     """What tells two recorded decode steps of the same padded shape apart: the split and the kernel's variant."""
-    pps, n_live = decode_plan(ctx, n_seqs, n_pages, page_size, n_kv_heads, head_dim, group)
+    pps, n_live, cluster = decode_plan(ctx, n_seqs, n_pages, page_size, n_kv_heads, head_dim, group)
     if decode_uses_mma(head_dim, group):
         return (pps,)
     key = (head_dim, group, n_live, n_kv_heads)
     if key not in _resident_cache:
         decode_pages_per_split(n_live, n_kv_heads, n_pages, head_dim, group)
-    return (pps, _resident_cache[key][1])
+    return (pps, _resident_cache[key][1], cluster)
 
 
 def attention_decode_supported(head_dim: int, group: int) -> bool:
@@ -589,11 +623,13 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, s
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start,
                      n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int, partials: torch.Tensor,
-                     pages_per_split: int = DECODE_PAGES_PER_SPLIT, n_live: int = 0) -> None:
+                     pages_per_split: int = DECODE_PAGES_PER_SPLIT, n_live: int = 0, cluster: int = 0) -> None:
     """One token per sequence over its cache pages (bf16, page size 64), split over positions.
 
     ``partials``: fp32 scratch of at least ``attention_decode_workspace(...)`` floats.  ``n_live``: how many of
     the sequences are not padding, if the caller knows (it decides which variant of the kernel runs, nothing else).
+    ``cluster`` (2, 4, 8; ungrouped queries): the form of the kernel with one cluster of that many blocks per
+    sequence-head, whose splits meet in shared memory; ``pages_per_split`` x ``cluster`` must cover the page tables.
     """
     _need_cuda(q, out, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start, partials)
     S, P = seq_pages.shape
@@ -604,7 +640,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_p
         _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(seq_pages),
         c_int(seq_pages.stride(0)), _ptr(seq_kv_len), _ptr(seq_q_start), c_int(S), c_int(n_heads), c_int(n_kv_heads),
         c_int(head_dim), c_float(scale), c_int(window), c_int(P), c_int(pages_per_split), _ptr(partials),
-        c_long(partials.numel()), _ptr(sc.attn_tickets), c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), c_int(n_live), _stream()))
+        c_long(partials.numel()), _ptr(sc.attn_tickets), c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), c_int(n_live),
+        c_int(cluster), _stream()))
 
 
 def attention_decode_workspace(n_seqs: int, n_heads: int, head_dim: int, max_pages: int,
@@ -689,7 +726,8 @@ _PREFILL_SPLIT = os.environ.get("LLMI_PREFILL_SPLIT", "1") != "0"
 
 def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start,
                            n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int, partials: torch.Tensor,
-                           pages_per_split: int, inv_freq, rotary_dim: int, write_kv: bool, n_live: int = 0) -> None:
+                           pages_per_split: int, inv_freq, rotary_dim: int, write_kv: bool, n_live: int = 0,
+                           cluster: int = 0) -> None:
     """:func:`attention_decode` with the step's position encoding done by the same kernel: ``qkv`` holds the
     un-rotated [q | k | v] row of each sequence's token; the new k (rotated) and v are appended to the cache."""
     _need_cuda(qkv, out, k_cache, v_cache, seq_pages, seq_kv_len, seq_q_start, partials)
@@ -703,7 +741,8 @@ def attention_decode_fused(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cach
         c_int(seq_pages.stride(0)), _ptr(seq_kv_len), _ptr(seq_q_start), c_int(S), c_int(n_heads), c_int(n_kv_heads),
         c_int(head_dim), c_float(scale), c_int(window), c_int(P), c_int(pages_per_split),
         _ptr(inv_freq) if rotary_dim else None, c_int(rotary_dim), c_int(1 if write_kv else 0), _ptr(partials),
-        c_long(partials.numel()), _ptr(sc.attn_tickets), c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), c_int(n_live), _stream()))
+        c_long(partials.numel()), _ptr(sc.attn_tickets), c_int(sc.N_ATTN_TICKETS), _ptr(sc.error), c_int(n_live),
+        c_int(cluster), _stream()))
 
 
 _FUSE_ROPE = os.environ.get("LLMI_FUSE_ROPE", "1") != "0"
@@ -733,17 +772,18 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_cache, v_cache, ctx, seq_p
     """
     if _decode_kernel_applies(qkv, ctx, seq_pages, page_size, n_heads, n_kv_heads, head_dim, rt):
         S, P = seq_pages.shape
-        pps, n_live = decode_plan(ctx, S, P, page_size, n_kv_heads, head_dim, n_heads // n_kv_heads)
+        pps, n_live, cluster = decode_plan(ctx, S, P, page_size, n_kv_heads, head_dim, n_heads // n_kv_heads)
         partials = rt.scratch("attn_partials", (attention_decode_workspace(S, n_heads, head_dim, P, pps),), torch.float32)
         if decode_uses_mma(head_dim, n_heads // n_kv_heads):
             attention_decode_mma(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_kv_len, ctx.seq_q_start, n_heads,
                                  n_kv_heads, head_dim, scale, window, partials, pps, rope)
         elif rope is not None:
             attention_decode_fused(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_kv_len, ctx.seq_q_start, n_heads,
-                                   n_kv_heads, head_dim, scale, window, partials, pps, rope[0], rope[1], rope[2], n_live)
+                                   n_kv_heads, head_dim, scale, window, partials, pps, rope[0], rope[1], rope[2], n_live,
+                                   cluster)
         else:
             attention_decode(qkv, out, k_cache, v_cache, seq_pages, ctx.seq_kv_len, ctx.seq_q_start, n_heads, n_kv_heads,
-                             head_dim, scale, window, partials, pps, n_live)
+                             head_dim, scale, window, partials, pps, n_live, cluster)
         return
     if rope is not None:
         raise RuntimeError("attention: rotation can only be fused into the decode kernel (ask attention_fuses_rotation)")

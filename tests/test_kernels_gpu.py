@@ -572,6 +572,75 @@ def test_attention_decode_ragged(kernel, nh, nkv, hd, pps, window):
         assert rel(out[s_].reshape(nh, hd), torch.from_numpy(ref)) < 1e-2, (s_, n)
 
 
+@pytest.mark.parametrize("nh,hd", [(4, 64), (3, 128), (6, 32), (32, 64)])
+@pytest.mark.parametrize("cluster,window", [(2, 0), (4, 0), (8, 0), (4, 200), (8, 300)])
+def test_attention_decode_cluster_form_same_bits(nh, hd, cluster, window):
+    """The decode kernel run as clusters (one cluster of 2, 4 or 8 blocks per sequence-head, the splits' results
+    meeting in the first block's shared memory) gives the bits of its persistent form with the same split: sequences of
+    very different lengths (splits that hold nothing, also the FIRST one under a window), a padding sequence,
+    position encoding fused in or not; and the plain formula's values."""
+    kk = K()
+    rng = np.random.default_rng(4)
+    lens = [1, 64, 65, 700, 0, 129, 1000, 128, 1024]       # lengths AFTER this step (0: padding)
+    P, n_pages = 16, 80
+    pps = P // cluster
+    gen = torch.Generator().manual_seed(5)
+    kc, vc = paged(n_pages, nh, hd, "bfloat16")
+    perm = rng.permutation(n_pages).tolist()
+    pages = torch.full((len(lens), P), -1, dtype=torch.int32)
+    for s_, n in enumerate(lens):
+        for pg_i in range((n + 63) // 64):
+            pg = perm.pop()
+            pages[s_, pg_i] = pg
+            m_ = min(64, n - 1 - 64 * pg_i)
+            if m_ > 0:
+                kc[pg, :, :m_] = torch.randn(nh, m_, hd, generator=gen).to(torch.bfloat16).cuda()
+                vc[pg, :, :m_] = torch.randn(nh, m_, hd, generator=gen).to(torch.bfloat16).cuda()
+    S = len(lens)
+    qkv = torch.randn(S, 3 * nh * hd, generator=gen).to(torch.bfloat16).cuda()
+    kvlen = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    qstart = torch.arange(S, dtype=torch.int32, device="cuda")
+    inv = torch.from_numpy(P_inv(hd)).cuda()
+    scale = 1 / math.sqrt(hd)
+    part = torch.empty(kk.attention_decode_workspace(S, nh, hd, P, pps), device="cuda")
+    pages_d = pages.cuda()
+    outs, caches = [], []
+    for form in (0, cluster):
+        k1, v1 = kc.clone(), vc.clone()
+        out = torch.full((S, nh * hd), 7.0, device="cuda", dtype=torch.bfloat16)
+        for _ in range(2):
+            kk.attention_decode_fused(qkv, out, k1, v1, pages_d, kvlen, qstart, nh, nh, hd, scale, window, part, pps, inv, hd,
+                                      True, cluster=form)
+        kk.check_device_errors("cuda:0")
+        outs.append(out)
+        caches.append((k1, v1))
+    assert torch.equal(outs[0], outs[1])
+    for a, b in zip(caches[0], caches[1]):
+        assert torch.equal(torch.nan_to_num(a.float(), nan=-7.0), torch.nan_to_num(b.float(), nan=-7.0))
+    assert (outs[1][4] == 7.0).all()                        # the padding sequence is not touched
+    # without the fused position encoding, over the caches that the run above has filled
+    k1, v1 = caches[1]
+    q_rot = qkv.clone()
+    tok_seq = torch.tensor([i if n > 0 else -1 for i, n in enumerate(lens)], dtype=torch.int32, device="cuda")
+    tok_pos = torch.tensor([max(n - 1, 0) for n in lens], dtype=torch.int32, device="cuda")
+    kk.rope_store(q_rot, inv, hd, tok_seq, tok_pos, pages_d, 64, k1.clone(), v1.clone(), nh, nh, hd, True)
+    plain = []
+    for form in (0, cluster):
+        out = torch.full((S, nh * hd), 7.0, device="cuda", dtype=torch.bfloat16)
+        kk.attention_decode(q_rot, out, k1, v1, pages_d, kvlen, qstart, nh, nh, hd, scale, window, part, pps, cluster=form)
+        plain.append(out)
+    kk.check_device_errors("cuda:0")
+    assert torch.equal(plain[0], plain[1]) and torch.equal(plain[1], outs[1])
+    assert int(kk.tc_scratch("cuda:0").attn_tickets.abs().sum()) == 0
+    for s_, n in enumerate(lens):                           # and the plain formula
+        if n == 0:
+            continue
+        keys = torch.stack([k1[pages[s_, i // 64], :, i % 64] for i in range(n)]).double().cpu().numpy()
+        vals = torch.stack([v1[pages[s_, i // 64], :, i % 64] for i in range(n)]).double().cpu().numpy()
+        ref = plain_attention_rows(q_rot[s_, :nh * hd].double().cpu().numpy().reshape(nh, hd), keys, vals, 1, scale, window)
+        assert rel(outs[1][s_].reshape(nh, hd), torch.from_numpy(ref)) < 1e-2, (s_, n)
+
+
 @pytest.mark.parametrize("kernel,nh,nkv,hd", DECODE_SHAPES)
 @pytest.mark.parametrize("pps,window,rot,write", [(1, 0, True, True), (4, 0, True, True), (64, 0, False, True),
                                                   (2, 200, True, True), (4, 0, True, False)])

@@ -71,7 +71,7 @@ def _call_ordinary(lib, pr, out, pps):
         _ptr(pr["q"]), c_long(pr["q"].stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(pr["kc"]), _ptr(pr["vc"]),
         _ptr(pr["pages"]), c_int(pr["pages"].stride(0)), _ptr(pr["kvlen"]), _ptr(pr["qstart"]), c_int(pr["S"]),
         c_int(pr["nh"]), c_int(pr["nkv"]), c_int(pr["hd"]), c_float(1 / math.sqrt(pr["hd"])), c_int(0), c_int(pr["P"]),
-        c_int(pps), _ptr(partials), c_long(partials.numel()), _ptr(tickets), c_int(tickets.numel()), _ptr(err), c_int(0), stream)
+        c_int(pps), _ptr(partials), c_long(partials.numel()), _ptr(tickets), c_int(tickets.numel()), _ptr(err), c_int(0), c_int(0), stream)
     torch.cuda.synchronize()
     assert rc == 0 and int(err.item()) == 0
     return out
