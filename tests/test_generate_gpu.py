@@ -340,7 +340,8 @@ MANY_HEADS = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 1, "hi
 def test_recorded_decode_steps_of_one_shape_are_told_apart_by_their_plan(tmp_path):
     """16, then 9, then 5 live sequences: the first two are padded to the same shape (16), but their decode kernels
     are cut into items differently (9 x 32 sequence-heads fit the variant with whole sequence-heads as items, 16 x 32
-    do not), so they are recorded apart; every step's logits are the plain implementation's."""
+    do not), so they are recorded apart; the 5 run the kernel's cluster form; every step's logits are the plain
+    implementation's."""
     import torch
     import helpers as H
     import llmi_b200 as L
@@ -382,3 +383,5 @@ def test_recorded_decode_steps_of_one_shape_are_told_apart_by_their_plan(tmp_pat
         keys = [k for k in model._graphs.graphs if k[0] == 16]
         assert len({k[-1] for k in keys}) == 2, keys
         assert model._graphs.replays >= 3
+        if os.environ.get("LLMI_DECODE_CLUSTER", "1") != "0" and kernels.sm_count() >= 132:
+            assert plans[5][0][2] in (2, 4), plans      # 5 x 32 sequence-heads of 4 pages: the kernel's cluster form
