@@ -338,9 +338,9 @@ MANY_HEADS = {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 1, "hi
 
 
 def test_recorded_decode_steps_of_one_shape_are_told_apart_by_their_plan(tmp_path):
-    """16, then 9, then 5 live sequences: the first two are padded to the same shape (16), but their decode kernels
+    """16, then 9, then 2 live sequences: the first two are padded to the same shape (16), but their decode kernels
     are cut into items differently (9 x 32 sequence-heads fit the variant with whole sequence-heads as items, 16 x 32
-    do not), so they are recorded apart; the 5 run the kernel's cluster form; every step's logits are the plain
+    do not), so they are recorded apart; the 2 run the kernel's cluster form; every step's logits are the plain
     implementation's."""
     import torch
     import helpers as H
@@ -367,9 +367,9 @@ def test_recorded_decode_steps_of_one_shape_are_told_apart_by_their_plan(tmp_pat
                 cache.free_slot(slots[i])
             live = live[:9]
         if step == 6:
-            for i in live[5:]:
+            for i in live[2:]:
                 cache.free_slot(slots[i])
-            live = live[:5]
+            live = live[:2]
         model.step_and_choose(cache, [L.SequenceStep(slots[i], [toks[i][fed]], [0]) for i in live], sampler)
         logits = model.last_logits.cpu().numpy()
         for row, i in enumerate(live):
@@ -384,4 +384,4 @@ def test_recorded_decode_steps_of_one_shape_are_told_apart_by_their_plan(tmp_pat
         assert len({k[-1] for k in keys}) == 2, keys
         assert model._graphs.replays >= 3
         if os.environ.get("LLMI_DECODE_CLUSTER", "1") != "0" and kernels.sm_count() >= 132:
-            assert plans[5][0][2] in (2, 4), plans      # 5 x 32 sequence-heads of 4 pages: the kernel's cluster form
+            assert plans[2][0][2] in (2, 4), plans      # 2 x 32 sequence-heads of 5 pages: the kernel's cluster form
