@@ -16,6 +16,12 @@
 //    the block that takes a sequence-head's last ticket merges the splits in split order and writes
 //    the output.  Nothing waits for another block.
 //
+// Two other forms of the same kernel (template parameters): VP, with a second producer thread for the value tiles
+// and a deeper ring, two blocks per SM, for steps whose sequence-heads about fill those blocks as whole items; and
+// CL, launched as one cluster of 2, 4 or 8 blocks per sequence-head (one block per split) whose results meet in the
+// first block's shared memory instead of the workspace, for few sequence-heads of few pages.  The host chooses
+// (ops/kernels.py: decode_pages_per_split, decode_cluster); all forms give the same bits for the same split.
+//
 // Softmax runs in fp32 with a running maximum, in base 2 (scores are scaled by scale*log2(e) and the
 // exponential is one ex2 instruction); the merge order is fixed, so a sequence's result does not depend
 // on its batch-mates.  `window` > 0 keeps keys pos-window+1..pos.
