@@ -641,6 +641,40 @@ def test_attention_decode_cluster_form_same_bits(nh, hd, cluster, window):
         assert rel(outs[1][s_].reshape(nh, hd), torch.from_numpy(ref)) < 1e-2, (s_, n)
 
 
+@pytest.mark.parametrize("nh,hd,S,P,cluster", [(32, 64, 1, 16, 8), (32, 64, 3, 8, 4), (8, 128, 2, 32, 8)])
+def test_attention_decode_cluster_form_again_and_again(nh, hd, S, P, cluster):
+    """The cluster form launched 120 times between other kernels (programmatic dependents, so neighbours overlap):
+    every launch gives the first one's bits."""
+    kk = K()
+    torch.manual_seed(0)
+    pps = -(-P // cluster)
+    n_pages = S * P + 3
+    kc = torch.randn(n_pages, nh, 64, hd, device="cuda").to(torch.bfloat16)
+    vc = torch.randn(n_pages, nh, 64, hd, device="cuda").to(torch.bfloat16)
+    pages = torch.randperm(n_pages)[:S * P].to(torch.int32).reshape(S, P).cuda()
+    kvlen = torch.tensor([P * 64 - 7 * i - 1 for i in range(S)], dtype=torch.int32, device="cuda")
+    qstart = torch.arange(S, dtype=torch.int32, device="cuda")
+    qkv = torch.randn(S, 3 * nh * hd, device="cuda").to(torch.bfloat16)
+    inv = torch.from_numpy(P_inv(hd)).cuda()
+    part = torch.empty(kk.attention_decode_workspace(S, nh, hd, P, pps), device="cuda")
+    x = torch.randn(8, 2048, device="cuda").to(torch.bfloat16)
+    w = torch.randn(2048, 2048, device="cuda").to(torch.bfloat16)
+    y = torch.empty(8, 2048, device="cuda", dtype=torch.bfloat16)
+    first, differ = None, 0
+    for _ in range(120):
+        out = torch.full((S, nh * hd), 7.0, device="cuda", dtype=torch.bfloat16)
+        kk.gemm_skinny(x, w, y)
+        kk.attention_decode_fused(qkv, out, kc, vc, pages, kvlen, qstart, nh, nh, hd, 1 / math.sqrt(hd), 0, part, pps, inv, hd,
+                                  True, cluster=cluster)
+        kk.gemm_skinny(x, w, y)
+        if first is None:
+            first = out.clone()
+        elif not torch.equal(out, first):
+            differ += 1
+    kk.check_device_errors("cuda:0")
+    assert differ == 0 and bool(torch.isfinite(first.float()).all())
+
+
 @pytest.mark.parametrize("kernel,nh,nkv,hd", DECODE_SHAPES)
 @pytest.mark.parametrize("pps,window,rot,write", [(1, 0, True, True), (4, 0, True, True), (64, 0, False, True),
                                                   (2, 200, True, True), (4, 0, True, False)])
